@@ -1,0 +1,145 @@
+/*
+ * oeq_b200 -- C ABI of the B200 (sm_100a) tensor-product / fused-convolution kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; no torch or C++ types cross this
+ * boundary.  All functions return 0 on success or one of the OEQB_E* codes; oeqb_last_error() then holds a
+ * message for the calling thread.  Nothing here terminates the process (the reference's backend calls
+ * exit(1) on driver / NVRTC failures: extension/backend/backend_cuda.hpp:14-44).
+ *
+ * A problem is identified by its descriptor text (see openequivariance_b200/core/descriptor.py for the
+ * grammar) and a 64-bit key chosen by the caller; the library parses the descriptor once per key,
+ * specialises its kernel templates for it with NVRTC (sm_100a) on first use and caches the result, under
+ * one mutex -- the role of compile_tp_with_caching / compile_conv_with_caching in
+ * extension/torch_core.hpp:180-270.
+ *
+ * Feature rows are contiguous: x [B|N, L1_dim], y [B|E, L2_dim], z [B|N, L3_dim]; weights are in kernel
+ * ("OEQ") order, [weight_numel] when shared else [B|E, weight_numel]; indices are int64 (or int32 when
+ * the descriptor says so).  Element type is the descriptor's dtype (float or double).
+ */
+#ifndef OEQ_B200_H
+#define OEQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define OEQB_API __attribute__((visibility("default")))
+#else
+#define OEQB_API
+#endif
+
+#define OEQB_OK 0
+#define OEQB_EINVAL 1      /* bad argument (null pointer, negative size, workspace too small, misalignment) */
+#define OEQB_EPARSE 2      /* malformed descriptor */
+#define OEQB_ECOMPILE 3    /* NVRTC / module load failure; message holds the compiler log */
+#define OEQB_ECUDA 4       /* CUDA runtime error */
+#define OEQB_EUNSUPPORTED 5
+#define OEQB_EKERNEL 6     /* a kernel reported a bounded wait that ran out (device status word non-zero) */
+
+/* Mirrors KernelProp of extension/torch_core.hpp:144-178 (sizes and dtype tags the op layer validates
+ * tensors against), plus which kernel family will serve the problem. */
+typedef struct oeqb_kernel_prop {
+    int64_t L1_dim, L2_dim, L3_dim, weight_numel;
+    int32_t shared_weights;
+    int32_t irrep_dtype;   /* 1 = float32, 2 = float64 */
+    int32_t weight_dtype;
+    int32_t idx_dtype;     /* 3 = int32, 4 = int64 */
+    int32_t is_conv, deterministic, kahan;
+    int32_t is_uvw;
+    int32_t fast_path;     /* 1 when the channel-parallel TMA-pipelined kernels apply */
+    int32_t reserved;
+} oeqb_kernel_prop;
+
+/* Parse (and cache) a descriptor; fills *out.  Replaces the kernel_prop JSON block parsed in
+ * extension/torch_core.hpp:136-178. */
+OEQB_API int oeqb_query(const void* desc, size_t desc_len, int64_t key, oeqb_kernel_prop* out);
+
+/* z = TP(x, y, W).  Replaces JITTPImpl::exec_tensor_product (extension/tensorproducts.hpp:75-85) behind
+ * jit_tp_forward (extension/torch_core.hpp:274-310).  Every element of z is written. */
+OEQB_API int oeqb_tp_forward(const void* desc, size_t desc_len, int64_t key, int64_t batch,
+                    const void* x, const void* y, const void* W, void* z, void* stream);
+
+/* (dx, dy, dW) for cotangent g.  Replaces JITTPImpl::backward (tensorproducts.hpp:87-95) behind
+ * jit_tp_backward (torch_core.hpp:312-352).  All outputs are fully written (shared dW is zeroed here). */
+OEQB_API int oeqb_tp_backward(const void* desc, size_t desc_len, int64_t key, int64_t batch,
+                     const void* x, const void* y, const void* W, const void* g,
+                     void* dx, void* dy, void* dW, void* stream);
+
+/* Second-order pass.  Inputs (x, y, W, g) and the cotangents (x2, y2, W2) of (dx, dy, dW); outputs the
+ * gradients w.r.t. (x, y, W, g).  Replaces JITTPImpl::double_backward (tensorproducts.hpp:97-110) behind
+ * jit_tp_double_backward (torch_core.hpp:354-418). */
+OEQB_API int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int64_t batch,
+                            const void* x, const void* y, const void* W, const void* g,
+                            const void* x2, const void* y2, const void* W2,
+                            void* dx, void* dy, void* dW, void* dg, void* stream);
+
+/* Bytes of scratch the convolution entry points need for a graph of n_nodes / n_edges.
+ * direction: 0 forward, 1 backward, 2 double backward.  The reference sizes its workspace at construction
+ * from its launch geometry (core/LoopUnrollConv.py:142-185); here it depends on the graph size, so the
+ * caller asks per call.  Returns a negative OEQB_E* code on error. */
+OEQB_API int64_t oeqb_conv_workspace_bytes(const void* desc, size_t desc_len, int64_t key, int direction,
+                                  int64_t n_nodes, int64_t n_edges);
+
+/* Z[n] = sum over edges e with rows[e] == n of TP(X[cols[e]], Y[e], W[e]).
+ * Atomic descriptors: any edge order, Z must be zero on entry.  Deterministic descriptors: edges sorted by
+ * (row, col); every row of Z is written exactly once (no zeroing needed), results are bitwise reproducible
+ * and independent of launch geometry.  Replaces JITConvImpl::exec_conv + fixup_forward
+ * (extension/convolution.hpp:78-107) behind jit_conv_forward (torch_core.hpp:422-476). */
+OEQB_API int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                      const void* X, const void* Y, const void* W, void* Z,
+                      const void* rows, const void* cols, const void* transpose_perm,
+                      void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Gradients of the convolution.  G is dL/dZ [n_nodes, L3_dim].  dX [n_nodes, L1_dim], dY, dW like Y, W.
+ * Deterministic descriptors need transpose_perm (position in the row-major edge list of the k-th edge in
+ * column-major order) and a symmetric edge set is NOT required by this library.  All outputs are fully
+ * written.  Replaces JITConvImpl::backward + fixup_backward (convolution.hpp:109-136) behind
+ * jit_conv_backward (torch_core.hpp:478-540). */
+OEQB_API int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                       const void* X, const void* Y, const void* W, const void* G,
+                       void* dX, void* dY, void* dW,
+                       const void* rows, const void* cols, const void* transpose_perm,
+                       void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Second-order pass of the convolution; argument meaning as oeqb_tp_double_backward with node-level X, X2,
+ * dX, G, dG.  Replaces JITConvImpl::double_backward (convolution.hpp:138-176) behind
+ * jit_conv_double_backward (torch_core.hpp:542-622). */
+OEQB_API int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                              const void* X, const void* Y, const void* W, const void* G,
+                              const void* X2, const void* Y2, const void* W2,
+                              void* dX, void* dY, void* dW, void* dG,
+                              const void* rows, const void* cols, const void* transpose_perm,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Writes the CUDA source the library would hand to NVRTC for `kind` (a kernel-family name such as
+ * "generic_forward") into buf (NUL-terminated, truncated to cap); *needed receives the full length
+ * including the NUL.  Lets the specialised source be inspected or compiled offline with nvcc.  Plays the
+ * part of the kernel string the reference exposes as TensorProduct.jit_kernel (core/LoopUnrollTP.py:93-99). */
+OEQB_API int oeqb_emit_source(const void* desc, size_t desc_len, const char* kind, char* buf, size_t cap, size_t* needed);
+
+/* Compile every kernel family of a descriptor now (works without a GPU) and keep the cubins in the on-disk
+ * cache directory, so later processes skip NVRTC.  Returns the number of programs compiled, or a negative
+ * OEQB_E* code.  Equivalent in purpose to the reference's eager JIT in the JITTPImpl / JITConvImpl
+ * constructors (tensorproducts.hpp:32-46, convolution.hpp:36-56). */
+OEQB_API int oeqb_precompile(const void* desc, size_t desc_len, int64_t key);
+
+/* String options: "cache_dir" (cubin cache directory), "force_generic" ("0"/"1"), "log" ("0"/"1"). */
+OEQB_API int oeqb_set_option(const char* name, const char* value);
+
+/* Number of kernel launches issued by this library since load (all threads). */
+OEQB_API int64_t oeqb_launch_count(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+OEQB_API const char* oeqb_last_error(void);
+
+/* Library version string. */
+OEQB_API const char* oeqb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OEQ_B200_H */

@@ -1,0 +1,700 @@
+// Host side of the oeq_b200 C ABI (declared in include/oeq_b200.h):
+//   descriptor parser -> problem header emitter -> NVRTC (sm_100a) -> cubin cache -> launches.
+//
+// The device code lives in kernels/*.cuh (hand-written templates).  The only generated text is the short
+// "problem header": constexpr tables for the irreps / instructions and one straight-line function per
+// instruction holding its sparse Clebsch-Gordan contraction with the coefficients as literals.
+//
+// Counterparts in the reference: extension/backend/backend_cuda.hpp:154-361 (CUJITKernel: NVRTC, module
+// load, launch), extension/tensorproducts.hpp:10-113 and extension/convolution.hpp:15-179 (kernel lists and
+// launch sequences), extension/torch_core.hpp:180-270 (hash-keyed caches under a mutex).
+
+#include <cuda_runtime.h>
+#include <nvrtc.h>
+#include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/oeq_b200.h"
+#include "kernels_embed.inc"  // generated at build time: K_COMMON, K_GENERIC, K_FAST_UVU as raw strings
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------ errors
+thread_local std::string g_err;
+std::atomic<long long> g_launches{0};
+bool g_log = false;
+bool g_force_generic = false;
+std::string g_cache_dir;
+std::mutex g_mutex;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[4096];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    if (g_log) fprintf(stderr, "[oeq_b200] error %d: %s\n", code, buf);
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t _e = (expr);                                                                    \
+        if (_e != cudaSuccess) return fail(OEQB_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+// -------------------------------------------------------------------------------------------- descriptor
+struct Block { int mul, l, p, off; int d() const { return 2 * l + 1; } };
+struct Nz { int i, j, k; double c; };
+struct Instr { int a, b, o; long long woff; std::vector<Nz> nz; };
+struct Desc {
+    int dtype = 1, layout = 0, shared = 0, uvw = 0, conv = 0, det = 0, kahan = 0, idx = 4;
+    std::vector<Block> L[3];
+    long long dim[3] = {0, 0, 0};
+    long long wn = 0;
+    std::vector<Instr> ins;
+    bool fast = false;   // channel-parallel pipelined kernels applicable
+    int fast_U = 0;      // common multiplicity on the fast path
+    size_t elt() const { return dtype == 2 ? 8 : 4; }
+    size_t idx_bytes() const { return idx == 3 ? 4 : 8; }
+};
+
+bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
+    std::istringstream in(std::string(text, len));
+    std::string tok;
+    auto bad = [&](const char* m) { why = m; return false; };
+    int version = 0;
+    if (!(in >> tok >> version) || tok != "OEQB" || version != 1) return bad("missing 'OEQB 1' header");
+    std::string mode;
+    if (!(in >> tok >> d.dtype) || tok != "dtype" || (d.dtype != 1 && d.dtype != 2)) return bad("bad dtype");
+    if (!(in >> tok >> d.layout) || tok != "layout") return bad("bad layout");
+    if (!(in >> tok >> d.shared) || tok != "shared") return bad("bad shared");
+    if (!(in >> tok >> mode) || tok != "mode" || (mode != "uvu" && mode != "uvw")) return bad("bad mode");
+    d.uvw = mode == "uvw";
+    if (!(in >> tok >> d.conv >> d.det >> d.kahan >> d.idx) || tok != "conv" || (d.idx != 3 && d.idx != 4))
+        return bad("bad conv line");
+    const char* tags[3] = {"L1", "L2", "L3"};
+    for (int r = 0; r < 3; ++r) {
+        int n = 0;
+        if (!(in >> tok >> n >> d.dim[r]) || tok != tags[r] || n < 0 || n > 4096) return bad("bad irreps header");
+        long long off = 0;
+        for (int b = 0; b < n; ++b) {
+            Block blk{};
+            if (!(in >> blk.mul >> blk.l >> blk.p >> blk.off) || blk.mul < 0 || blk.l < 0 || blk.l > 32)
+                return bad("bad irreps block");
+            if (blk.off != off) return bad("irreps offsets are not contiguous");
+            off += (long long)blk.mul * blk.d();
+            d.L[r].push_back(blk);
+        }
+        if (off != d.dim[r]) return bad("irreps dim mismatch");
+    }
+    if (!(in >> tok >> d.wn) || tok != "wn" || d.wn < 0) return bad("bad wn");
+    int nins = 0;
+    if (!(in >> tok >> nins) || tok != "ins" || nins <= 0 || nins > 65536) return bad("bad ins count");
+    long long wsum = 0;
+    for (int n = 0; n < nins; ++n) {
+        Instr I{};
+        int nnz = 0;
+        if (!(in >> tok >> I.a >> I.b >> I.o >> I.woff >> nnz) || tok != "I") return bad("bad instruction line");
+        if (I.a < 0 || I.a >= (int)d.L[0].size() || I.b < 0 || I.b >= (int)d.L[1].size() || I.o < 0 ||
+            I.o >= (int)d.L[2].size() || nnz < 0)
+            return bad("instruction index out of range");
+        const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
+        if (!d.uvw && A.mul != O.mul) return bad("uvu needs mul(in1) == mul(out)");
+        if (I.woff != wsum) return bad("weight offsets are not contiguous");
+        wsum += (long long)A.mul * B.mul * (d.uvw ? O.mul : 1);
+        for (int z = 0; z < nnz; ++z) {
+            Nz q{};
+            std::string hex;
+            if (!(in >> q.i >> q.j >> q.k >> hex)) return bad("bad CG entry");
+            if (q.i < 0 || q.i >= A.d() || q.j < 0 || q.j >= B.d() || q.k < 0 || q.k >= O.d()) return bad("CG index out of range");
+            q.c = strtod(hex.c_str(), nullptr);
+            I.nz.push_back(q);
+        }
+        d.ins.push_back(std::move(I));
+    }
+    if (wsum != d.wn) return bad("weight_numel mismatch");
+    if (!(in >> tok) || tok != "end") return bad("missing 'end'");
+    if (d.layout == 1 && d.uvw) return bad("ir_mul layout with uvw");
+    if (d.dim[0] * 1LL > (1LL << 24) || d.dim[2] > (1LL << 24) || d.wn > (1LL << 30)) return bad("problem too large");
+
+    // Fast path: fp32, mul_ir, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
+    // that is a multiple of 32, l <= 4 everywhere, no Kahan.
+    d.fast = false;
+    if (d.dtype == 1 && d.layout == 0 && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
+        bool ok = true;
+        int U = d.L[0][0].mul;
+        for (auto& b : d.L[0]) ok = ok && b.mul == U && b.l <= 4;
+        for (auto& b : d.L[1]) ok = ok && b.mul == 1 && b.l <= 4;
+        for (auto& b : d.L[2]) ok = ok && b.mul == U && b.l <= 4;
+        ok = ok && U >= 32 && U % 32 == 0 && U <= 512;
+        d.fast = ok;
+        d.fast_U = U;
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------------------------------ header emit
+std::string hexf(double v) {
+    char b[64];
+    snprintf(b, sizeof b, "%a", v);
+    return b;
+}
+
+// Straight-line contraction  out[oidx] += c * (p[pidx] * q[qidx])  grouped so each product is formed once.
+void emit_contraction(std::ostringstream& s, const char* name, const char* pn, const char* qn, const char* on,
+                      const std::vector<Nz>& nz, int which /*0 fwd, 1 dx, 2 dy*/) {
+    s << "  template <class R> static OEQ_DEV void " << name << "(const R* " << pn << ", const R* " << qn << ", R* "
+      << on << ") {\n";
+    struct E { int p, q, o; double c; };
+    std::vector<E> es;
+    for (auto& z : nz) {
+        if (which == 0) es.push_back({z.i, z.j, z.k, z.c});        // t[k] += c x[i] y[j]
+        else if (which == 1) es.push_back({z.j, z.k, z.i, z.c});   // dx[i] += c y[j] g[k]
+        else es.push_back({z.i, z.k, z.j, z.c});                   // dy[j] += c x[i] g[k]
+    }
+    std::stable_sort(es.begin(), es.end(), [](const E& a, const E& b) { return a.p != b.p ? a.p < b.p : a.q < b.q; });
+    for (size_t n = 0; n < es.size();) {
+        size_t m = n;
+        s << "    { const R pr = " << pn << "[" << es[n].p << "] * " << qn << "[" << es[n].q << "];";
+        while (m < es.size() && es[m].p == es[n].p && es[m].q == es[n].q) {
+            s << " " << on << "[" << es[m].o << "] += R(" << hexf(es[m].c) << ") * pr;";
+            ++m;
+        }
+        s << " }\n";
+        n = m;
+    }
+    s << "  }\n";
+}
+
+std::string emit_header(const Desc& d) {
+    std::ostringstream s;
+    s << "// problem header (generated from the descriptor)\n";
+    s << "typedef " << (d.dtype == 2 ? "double" : "float") << " T;\n";
+    s << "typedef " << (d.idx == 3 ? "int" : "long long") << " IDX;\n";
+    s << "#define OEQ_SHARED_W " << d.shared << "\n#define OEQ_UVW " << d.uvw << "\n#define OEQ_IR_MUL " << d.layout
+      << "\n#define OEQ_KAHAN " << d.kahan << "\n";
+    s << "#define OEQ_DEV __device__ __forceinline__\n";
+    s << "constexpr int L1_DIM = " << d.dim[0] << ", L2_DIM = " << d.dim[1] << ", L3_DIM = " << d.dim[2]
+      << ", WN = " << d.wn << ", NINS = " << d.ins.size() << ", NB1 = " << d.L[0].size() << ", NB2 = " << d.L[1].size()
+      << ", NB3 = " << d.L[2].size() << ";\n";
+    for (int r = 0; r < 3; ++r) {
+        s << "template <int B> struct Blk" << (r + 1) << ";\n";
+        for (size_t b = 0; b < d.L[r].size(); ++b) {
+            const Block& k = d.L[r][b];
+            s << "template <> struct Blk" << (r + 1) << "<" << b << "> { static constexpr int MUL = " << k.mul
+              << ", D = " << k.d() << ", OFF = " << k.off << "; };\n";
+        }
+    }
+    s << "template <int I> struct Ins;\n";
+    for (size_t n = 0; n < d.ins.size(); ++n) {
+        const Instr& I = d.ins[n];
+        const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
+        s << "template <> struct Ins<" << n << "> {\n";
+        s << "  static constexpr int A = " << I.a << ", B = " << I.b << ", O = " << I.o << ", WOFF = " << I.woff
+          << ", U = " << A.mul << ", V = " << B.mul << ", WN_ = " << O.mul << ", D1 = " << A.d() << ", D2 = " << B.d()
+          << ", D3 = " << O.d() << ", NNZ = " << I.nz.size() << ";\n";
+        emit_contraction(s, "fwd", "x", "y", "t", I.nz, 0);
+        emit_contraction(s, "dx", "y", "g", "dx", I.nz, 1);
+        emit_contraction(s, "dy", "x", "g", "dy", I.nz, 2);
+        s << "};\n";
+    }
+    return s.str();
+}
+
+// --------------------------------------------------------------------------------------- kernel families
+enum Family { FAM_GENERIC = 0, FAM_COUNT };
+const char* family_name(int f) {
+    switch (f) {
+        case FAM_GENERIC: return "generic";
+    }
+    return "?";
+}
+int family_from_name(const std::string& n) {
+    if (n == "generic" || n == "generic_forward" || n == "generic_backward") return FAM_GENERIC;
+    return -1;
+}
+
+std::string family_source(const Desc& d, const std::string& header, int fam) {
+    std::string src = header;
+    src += K_COMMON;
+    if (fam == FAM_GENERIC) src += K_GENERIC;
+    (void)d;
+    return src;
+}
+
+// -------------------------------------------------------------------------------------- NVRTC + caching
+uint64_t fnv1a(const std::string& s) {
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+    return h;
+}
+
+std::string default_cache_dir() {
+    if (const char* e = getenv("OEQB_CACHE_DIR")) return e;
+    Dl_info info;
+    if (dladdr((void*)&default_cache_dir, &info) && info.dli_fname) {
+        std::string p = info.dli_fname;
+        size_t slash = p.find_last_of('/');
+        if (slash != std::string::npos) return p.substr(0, slash) + "/_cubin_cache";
+    }
+    return "/tmp/oeq_b200_cubin_cache";
+}
+
+const std::string& cache_dir() {
+    if (g_cache_dir.empty()) g_cache_dir = default_cache_dir();
+    return g_cache_dir;
+}
+
+bool read_file(const std::string& path, std::string& out) {
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) return false;
+    fseek(f, 0, SEEK_END);
+    long n = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    out.resize(n > 0 ? n : 0);
+    size_t got = n > 0 ? fread(&out[0], 1, n, f) : 0;
+    fclose(f);
+    return got == (size_t)(n > 0 ? n : 0) && n > 0;
+}
+
+void write_file_atomic(const std::string& path, const std::string& data) {
+    mkdir(cache_dir().c_str(), 0755);
+    std::string tmp = path + ".tmp" + std::to_string((long long)getpid());
+    FILE* f = fopen(tmp.c_str(), "wb");
+    if (!f) return;
+    size_t put = fwrite(data.data(), 1, data.size(), f);
+    fclose(f);
+    if (put == data.size()) rename(tmp.c_str(), path.c_str()); else remove(tmp.c_str());
+}
+
+// Compiles `src` for sm_100a; returns the cubin (from the disk cache when present).
+int compile_cubin(const std::string& src, const char* label, std::string& cubin) {
+    static const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo", "-default-device",
+                                 "--extra-device-vectorization"};
+    const int nopts = sizeof(opts) / sizeof(opts[0]);
+    int major = 0, minor = 0;
+    nvrtcVersion(&major, &minor);
+    std::string keytext = src;
+    for (int i = 0; i < nopts; ++i) keytext += opts[i];
+    keytext += std::to_string(major * 100 + minor);
+    char name[64];
+    snprintf(name, sizeof name, "/%016llx.cubin", (unsigned long long)fnv1a(keytext));
+    const std::string path = cache_dir() + name;
+    if (read_file(path, cubin)) {
+        if (g_log) fprintf(stderr, "[oeq_b200] %s: cubin cache hit %s\n", label, path.c_str());
+        return OEQB_OK;
+    }
+    nvrtcProgram prog;
+    nvrtcResult r = nvrtcCreateProgram(&prog, src.c_str(), label, 0, nullptr, nullptr);
+    if (r != NVRTC_SUCCESS) return fail(OEQB_ECOMPILE, "nvrtcCreateProgram: %s", nvrtcGetErrorString(r));
+    r = nvrtcCompileProgram(prog, nopts, opts);
+    if (r != NVRTC_SUCCESS) {
+        size_t ls = 0;
+        nvrtcGetProgramLogSize(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) nvrtcGetProgramLog(prog, &log[0]);
+        nvrtcDestroyProgram(&prog);
+        if (log.size() > 3500) log.resize(3500);
+        return fail(OEQB_ECOMPILE, "NVRTC failed for %s: %s\n%s", label, nvrtcGetErrorString(r), log.c_str());
+    }
+    size_t cs = 0;
+    nvrtcGetCUBINSize(prog, &cs);
+    cubin.resize(cs);
+    nvrtcGetCUBIN(prog, &cubin[0]);
+    nvrtcDestroyProgram(&prog);
+    write_file_atomic(path, cubin);
+    if (g_log) fprintf(stderr, "[oeq_b200] %s: compiled %zu bytes of cubin\n", label, cs);
+    return OEQB_OK;
+}
+
+struct Program {
+    cudaLibrary_t lib = nullptr;
+    std::map<std::string, cudaKernel_t> kernels;
+    std::map<std::string, int> smem_set;  // kernel -> bitmask of devices whose smem attribute was raised
+    std::string cubin;                    // kept alive for lazy per-context loading
+};
+
+struct Entry {
+    Desc d;
+    std::string header;
+    std::unique_ptr<Program> prog[FAM_COUNT];
+};
+
+std::map<int64_t, std::unique_ptr<Entry>> g_entries;
+
+// Caller holds g_mutex.
+int get_entry(const void* desc, size_t len, int64_t key, Entry** out) {
+    auto it = g_entries.find(key);
+    if (it != g_entries.end()) { *out = it->second.get(); return OEQB_OK; }
+    if (!desc || len == 0) return fail(OEQB_EINVAL, "descriptor is empty");
+    auto e = std::make_unique<Entry>();
+    std::string why;
+    if (!parse_desc((const char*)desc, len, e->d, why)) return fail(OEQB_EPARSE, "descriptor: %s", why.c_str());
+    e->header = emit_header(e->d);
+    *out = e.get();
+    g_entries[key] = std::move(e);
+    return OEQB_OK;
+}
+
+// Caller holds g_mutex.
+int get_program(Entry* e, int fam, Program** out) {
+    if (e->prog[fam]) { *out = e->prog[fam].get(); return OEQB_OK; }
+    auto p = std::make_unique<Program>();
+    const std::string src = family_source(e->d, e->header, fam);
+    int rc = compile_cubin(src, family_name(fam), p->cubin);
+    if (rc) return rc;
+    cudaError_t ce = cudaLibraryLoadData(&p->lib, p->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    if (ce != cudaSuccess) return fail(OEQB_ECOMPILE, "cudaLibraryLoadData(%s): %s", family_name(fam), cudaGetErrorString(ce));
+    *out = p.get();
+    e->prog[fam] = std::move(p);
+    return OEQB_OK;
+}
+
+int get_kernel(Program* p, const char* name, size_t smem, cudaKernel_t* out) {
+    auto it = p->kernels.find(name);
+    if (it == p->kernels.end()) {
+        cudaKernel_t k;
+        cudaError_t ce = cudaLibraryGetKernel(&k, p->lib, name);
+        if (ce != cudaSuccess) return fail(OEQB_ECOMPILE, "kernel %s not found: %s", name, cudaGetErrorString(ce));
+        it = p->kernels.emplace(name, k).first;
+    }
+    if (smem > 48 * 1024) {
+        int dev = 0;
+        CUDA_TRY(cudaGetDevice(&dev));
+        int& mask = p->smem_set[name];
+        if (!(mask & (1 << dev))) {
+            CUDA_TRY(cudaFuncSetAttribute((const void*)it->second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            mask |= 1 << dev;
+        }
+    }
+    *out = it->second;
+    return OEQB_OK;
+}
+
+int launch(cudaKernel_t k, unsigned grid, unsigned block, size_t smem, void** args, cudaStream_t st) {
+    cudaError_t ce = cudaLaunchKernel((const void*)k, dim3(grid), dim3(block), args, smem, st);
+    if (ce != cudaSuccess) return fail(OEQB_ECUDA, "kernel launch failed: %s", cudaGetErrorString(ce));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return OEQB_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// ------------------------------------------------------------------------------------------ generic path
+struct FwdParams {
+    const void* x; const void* y; const void* W; void* z;
+    const void* rows; const void* cols;
+    long long n_units; long long n_edges;
+    int unit_mode; int out_mode;
+};
+struct BwdParams {
+    const void* x; const void* y_dx; const void* y_dw; const void* W; const void* g;
+    void* dx; void* dy; void* dW;
+    const void* rows; const void* cols; const void* perm;
+    long long n_units; long long n_edges;
+    int unit_mode; int accum;
+};
+enum { UNIT_ITEM = 0, UNIT_EDGE = 1, UNIT_SEGMENT = 2 };
+enum { OUT_STORE = 0, OUT_ADD = 1, OUT_ATOMIC = 2 };
+
+unsigned generic_grid(long long units) {
+    long long want = (units + 3) / 4;  // 4 warps per block
+    long long cap = (long long)sm_count() * 16;
+    if (want < 1) want = 1;
+    return (unsigned)(want < cap ? want : cap);
+}
+
+int generic_forward(Entry* e, FwdParams p, cudaStream_t st) {
+    if (p.n_units <= 0) return OEQB_OK;
+    Program* prog;
+    int rc = get_program(e, FAM_GENERIC, &prog);
+    if (rc) return rc;
+    cudaKernel_t k;
+    if ((rc = get_kernel(prog, "oeq_generic_forward", 0, &k))) return rc;
+    void* args[] = {&p};
+    return launch(k, generic_grid(p.n_units), 128, 0, args, st);
+}
+
+int generic_backward(Entry* e, BwdParams p, cudaStream_t st) {
+    if (p.n_units <= 0) return OEQB_OK;
+    Program* prog;
+    int rc = get_program(e, FAM_GENERIC, &prog);
+    if (rc) return rc;
+    cudaKernel_t k;
+    if ((rc = get_kernel(prog, "oeq_generic_backward", 0, &k))) return rc;
+    void* args[] = {&p};
+    return launch(k, generic_grid(p.n_units), 128, 0, args, st);
+}
+
+int check_ptrs(std::initializer_list<const void*> ptrs, const char* what) {
+    for (const void* p : ptrs)
+        if (!p) return fail(OEQB_EINVAL, "%s: null pointer argument", what);
+    return OEQB_OK;
+}
+
+}  // namespace
+
+// =============================================================================================== C ABI
+extern "C" {
+
+const char* oeqb_last_error(void) { return g_err.c_str(); }
+const char* oeqb_version(void) { return "oeq_b200 0.1 (sm_100a)"; }
+int64_t oeqb_launch_count(void) { return g_launches.load(); }
+
+int oeqb_set_option(const char* name, const char* value) {
+    if (!name || !value) return fail(OEQB_EINVAL, "oeqb_set_option: null argument");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    std::string n = name;
+    if (n == "cache_dir") g_cache_dir = value;
+    else if (n == "force_generic") g_force_generic = atoi(value) != 0;
+    else if (n == "log") g_log = atoi(value) != 0;
+    else return fail(OEQB_EINVAL, "unknown option '%s'", name);
+    return OEQB_OK;
+}
+
+int oeqb_query(const void* desc, size_t desc_len, int64_t key, oeqb_kernel_prop* out) {
+    if (!out) return fail(OEQB_EINVAL, "oeqb_query: null output");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    int rc = get_entry(desc, desc_len, key, &e);
+    if (rc) return rc;
+    const Desc& d = e->d;
+    memset(out, 0, sizeof *out);
+    out->L1_dim = d.dim[0]; out->L2_dim = d.dim[1]; out->L3_dim = d.dim[2]; out->weight_numel = d.wn;
+    out->shared_weights = d.shared; out->irrep_dtype = d.dtype; out->weight_dtype = d.dtype; out->idx_dtype = d.idx;
+    out->is_conv = d.conv; out->deterministic = d.det; out->kahan = d.kahan; out->is_uvw = d.uvw;
+    out->fast_path = d.fast && !g_force_generic;
+    return OEQB_OK;
+}
+
+int oeqb_emit_source(const void* desc, size_t desc_len, const char* kind, char* buf, size_t cap, size_t* needed) {
+    if (!desc || !kind) return fail(OEQB_EINVAL, "oeqb_emit_source: null argument");
+    Desc d;
+    std::string why;
+    if (!parse_desc((const char*)desc, desc_len, d, why)) return fail(OEQB_EPARSE, "descriptor: %s", why.c_str());
+    int fam = family_from_name(kind);
+    if (fam < 0) return fail(OEQB_EINVAL, "unknown kernel family '%s'", kind);
+    std::string src = family_source(d, emit_header(d), fam);
+    if (needed) *needed = src.size() + 1;
+    if (buf && cap) {
+        size_t n = src.size() < cap - 1 ? src.size() : cap - 1;
+        memcpy(buf, src.data(), n);
+        buf[n] = '\0';
+    }
+    return OEQB_OK;
+}
+
+int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
+    (void)key;
+    if (!desc) return -fail(OEQB_EINVAL, "oeqb_precompile: null descriptor");
+    Desc d;
+    std::string why;
+    if (!parse_desc((const char*)desc, desc_len, d, why)) return -fail(OEQB_EPARSE, "descriptor: %s", why.c_str());
+    std::lock_guard<std::mutex> lock(g_mutex);
+    const std::string header = emit_header(d);
+    int done = 0;
+    for (int fam = 0; fam < FAM_COUNT; ++fam) {
+        std::string cubin;
+        int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
+        if (rc) return -rc;
+        ++done;
+    }
+    return done;
+}
+
+int oeqb_tp_forward(const void* desc, size_t desc_len, int64_t key, int64_t batch, const void* x, const void* y,
+                    const void* W, void* z, void* stream) {
+    if (batch < 0) return fail(OEQB_EINVAL, "oeqb_tp_forward: negative batch");
+    if (batch == 0) return OEQB_OK;
+    if (int rc = check_ptrs({x, y, W, z}, "oeqb_tp_forward")) return rc;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    FwdParams p{x, y, W, z, nullptr, nullptr, batch, batch, UNIT_ITEM, OUT_STORE};
+    return generic_forward(e, p, (cudaStream_t)stream);
+}
+
+int oeqb_tp_backward(const void* desc, size_t desc_len, int64_t key, int64_t batch, const void* x, const void* y,
+                     const void* W, const void* g, void* dx, void* dy, void* dW, void* stream) {
+    if (batch < 0) return fail(OEQB_EINVAL, "oeqb_tp_backward: negative batch");
+    if (int rc = check_ptrs({x, y, W, g, dx, dy, dW}, "oeqb_tp_backward")) return rc;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const Desc& d = e->d;
+    if (d.shared) CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st));
+    if (batch == 0) return OEQB_OK;
+    CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
+    BwdParams p{x, y, y, W, g, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, UNIT_ITEM, 0};
+    return generic_backward(e, p, st);
+}
+
+int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int64_t batch, const void* x,
+                            const void* y, const void* W, const void* g, const void* x2, const void* y2,
+                            const void* W2, void* dx, void* dy, void* dW, void* dg, void* stream) {
+    if (batch < 0) return fail(OEQB_EINVAL, "oeqb_tp_double_backward: negative batch");
+    if (int rc = check_ptrs({x, y, W, g, x2, y2, W2, dx, dy, dW, dg}, "oeqb_tp_double_backward")) return rc;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const Desc& d = e->d;
+    if (d.shared) CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st));
+    if (batch == 0) return OEQB_OK;
+    CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
+    // dg = F(x2, y, W) + F(x, y2, W) + F(x, y, W2): the product is linear in each argument
+    int rc;
+    FwdParams f{x2, y, W, dg, nullptr, nullptr, batch, batch, UNIT_ITEM, OUT_STORE};
+    if ((rc = generic_forward(e, f, st))) return rc;
+    f.x = x; f.y = y2; f.out_mode = OUT_ADD;
+    if ((rc = generic_forward(e, f, st))) return rc;
+    f.y = y; f.W = W2;
+    if ((rc = generic_forward(e, f, st))) return rc;
+    // (dx, dy, dW) = mixed second derivatives contracted with g
+    BwdParams b{x2, y2, y, W, g, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, UNIT_ITEM, 0};
+    if ((rc = generic_backward(e, b, st))) return rc;
+    b.x = x; b.y_dx = y; b.y_dw = y2; b.W = W2; b.accum = 1;
+    return generic_backward(e, b, st);
+}
+
+int64_t oeqb_conv_workspace_bytes(const void* desc, size_t desc_len, int64_t key, int direction, int64_t n_nodes,
+                                  int64_t n_edges) {
+    if (n_nodes < 0 || n_edges < 0 || direction < 0 || direction > 2)
+        return -(int64_t)fail(OEQB_EINVAL, "oeqb_conv_workspace_bytes: bad argument");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return -(int64_t)rc;
+    return 0;
+}
+
+static int conv_check(const Desc& d, int64_t n_nodes, int64_t n_edges, const void* perm, const char* what) {
+    if (n_nodes < 0 || n_edges < 0) return fail(OEQB_EINVAL, "%s: negative size", what);
+    if (!d.conv) return fail(OEQB_EINVAL, "%s: descriptor was not built for a convolution", what);
+    if (d.det && n_edges > 0 && !perm) return fail(OEQB_EINVAL, "%s: deterministic mode needs transpose_perm", what);
+    return OEQB_OK;
+}
+
+int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                      const void* X, const void* Y, const void* W, void* Z, const void* rows, const void* cols,
+                      const void* transpose_perm, void* workspace, int64_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    const Desc& d = e->d;
+    if (int rc = conv_check(d, n_nodes, n_edges, transpose_perm, "oeqb_conv_forward")) return rc;
+    if (n_nodes == 0) return OEQB_OK;
+    if (int rc = check_ptrs({X, Z}, "oeqb_conv_forward")) return rc;
+    if (n_edges > 0) if (int rc = check_ptrs({Y, W, rows, cols}, "oeqb_conv_forward")) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d.det) {
+        FwdParams p{X, Y, W, Z, rows, cols, n_nodes, n_edges, UNIT_SEGMENT, OUT_STORE};
+        return generic_forward(e, p, st);
+    }
+    CUDA_TRY(cudaMemsetAsync(Z, 0, n_nodes * d.dim[2] * d.elt(), st));
+    FwdParams p{X, Y, W, Z, rows, cols, n_edges, n_edges, UNIT_EDGE, OUT_ATOMIC};
+    return generic_forward(e, p, st);
+}
+
+int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                       const void* X, const void* Y, const void* W, const void* G, void* dX, void* dY, void* dW,
+                       const void* rows, const void* cols, const void* transpose_perm, void* workspace,
+                       int64_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    const Desc& d = e->d;
+    if (int rc = conv_check(d, n_nodes, n_edges, transpose_perm, "oeqb_conv_backward")) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d.shared) { if (!dW) return fail(OEQB_EINVAL, "oeqb_conv_backward: null dW"); CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st)); }
+    if (n_nodes == 0) return OEQB_OK;
+    if (int rc = check_ptrs({X, G, dX}, "oeqb_conv_backward")) return rc;
+    if (n_edges > 0) {
+        if (int rc = check_ptrs({Y, W, dY, dW, rows, cols}, "oeqb_conv_backward")) return rc;
+        CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
+    }
+    if (d.det) {
+        BwdParams p{X, Y, Y, W, G, dX, dY, dW, rows, cols, transpose_perm, n_nodes, n_edges, UNIT_SEGMENT, 0};
+        return generic_backward(e, p, st);
+    }
+    CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
+    BwdParams p{X, Y, Y, W, G, dX, dY, dW, rows, cols, nullptr, n_edges, n_edges, UNIT_EDGE, 0};
+    return generic_backward(e, p, st);
+}
+
+int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                              const void* X, const void* Y, const void* W, const void* G, const void* X2,
+                              const void* Y2, const void* W2, void* dX, void* dY, void* dW, void* dG,
+                              const void* rows, const void* cols, const void* transpose_perm, void* workspace,
+                              int64_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    const Desc& d = e->d;
+    if (int rc = conv_check(d, n_nodes, n_edges, transpose_perm, "oeqb_conv_double_backward")) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d.shared) { if (!dW) return fail(OEQB_EINVAL, "oeqb_conv_double_backward: null dW"); CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st)); }
+    if (n_nodes == 0) return OEQB_OK;
+    if (int rc = check_ptrs({X, G, X2, dX, dG}, "oeqb_conv_double_backward")) return rc;
+    if (n_edges > 0) {
+        if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
+        CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
+    }
+    int rc;
+    if (d.det) {
+        FwdParams f{X2, Y, W, dG, rows, cols, n_nodes, n_edges, UNIT_SEGMENT, OUT_STORE};
+        if ((rc = generic_forward(e, f, st))) return rc;
+        f.x = X; f.y = Y2; f.out_mode = OUT_ADD;
+        if ((rc = generic_forward(e, f, st))) return rc;
+        f.y = Y; f.W = W2;
+        if ((rc = generic_forward(e, f, st))) return rc;
+        BwdParams b{X2, Y2, Y, W, G, dX, dY, dW, rows, cols, transpose_perm, n_nodes, n_edges, UNIT_SEGMENT, 0};
+        if ((rc = generic_backward(e, b, st))) return rc;
+        b.x = X; b.y_dx = Y; b.y_dw = Y2; b.W = W2; b.accum = 1;
+        return generic_backward(e, b, st);
+    }
+    CUDA_TRY(cudaMemsetAsync(dG, 0, n_nodes * d.dim[2] * d.elt(), st));
+    CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
+    FwdParams f{X2, Y, W, dG, rows, cols, n_edges, n_edges, UNIT_EDGE, OUT_ATOMIC};
+    if ((rc = generic_forward(e, f, st))) return rc;
+    f.x = X; f.y = Y2;
+    if ((rc = generic_forward(e, f, st))) return rc;
+    f.y = Y; f.W = W2;
+    if ((rc = generic_forward(e, f, st))) return rc;
+    BwdParams b{X2, Y2, Y, W, G, dX, dY, dW, rows, cols, nullptr, n_edges, n_edges, UNIT_EDGE, 0};
+    if ((rc = generic_backward(e, b, st))) return rc;
+    b.x = X; b.y_dx = Y; b.y_dw = Y2; b.W = W2; b.accum = 1;
+    return generic_backward(e, b, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,83 @@
+"""CPU-side checks of the native boundary: the library loads, exports every declared symbol, parses and rejects
+descriptors, and specialises + compiles its kernels for sm_100a without a GPU."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+from helpers import ROOT, tp_problem_matrix, with_dtype
+from openequivariance_b200 import native
+from openequivariance_b200.core import problems as P
+from openequivariance_b200.core.descriptor import build_descriptor, descriptor_hash
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "oeq_b200.h")).read()
+    declared = sorted(set(re.findall(r"OEQB_API [a-z0-9_ \*]+?(oeqb_[a-z_]+)\(", header)))
+    assert declared == native.exported_symbols()
+    lib = native.load()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert b"sm_100a" in lib.oeqb_version()
+
+
+def test_descriptor_roundtrip_and_query():
+    p = P.mace_like_problem()
+    text = build_descriptor(p, conv=True, deterministic=True)
+    prop = native.query(text.encode(), descriptor_hash(text))
+    assert (prop.L1_dim, prop.L2_dim, prop.L3_dim, prop.weight_numel) == (2048, 16, 12672, 2944)
+    assert prop.shared_weights == 0 and prop.irrep_dtype == 1 and prop.idx_dtype == 4
+    assert prop.is_conv == 1 and prop.deterministic == 1 and prop.is_uvw == 0 and prop.fast_path == 1
+    q = P.nequip_like_problem(np.float64)
+    text = build_descriptor(q)
+    prop = native.query(text.encode(), descriptor_hash(text))
+    assert (prop.L1_dim, prop.L3_dim, prop.weight_numel, prop.shared_weights) == (576, 576, 30720, 1)
+    assert prop.irrep_dtype == 2 and prop.is_uvw == 1 and prop.fast_path == 0
+
+
+@pytest.mark.parametrize("mangle", ["header", "truncate", "index", "wn"])
+def test_malformed_descriptor_is_rejected(mangle):
+    text = build_descriptor(P.readme_problem())
+    if mangle == "header":
+        bad = text.replace("OEQB 1", "OEQB 9")
+    elif mangle == "truncate":
+        bad = text[: len(text) // 2]
+    elif mangle == "index":
+        bad = text.replace("I 0 0 0 0", "I 0 3 0 0")
+    else:
+        bad = text.replace("wn 1", "wn 2")
+    with pytest.raises(RuntimeError, match="descriptor"):
+        native.query(bad.encode(), 7_000_000 + hash(mangle) % 1000)
+
+
+def test_unsupported_problems_fail_at_construction():
+    from openequivariance_b200.core.problem import TPProblem
+    with pytest.raises(AssertionError, match="layout='ir_mul'"):
+        build_descriptor(TPProblem("5x5e", "1x3e", "5x5e", [(0, 0, 0, "uvw", True)], shared_weights=False,
+                                   internal_weights=False, layout="ir_mul"))
+    with pytest.raises(AssertionError, match="same connection mode"):
+        build_descriptor(TPProblem("2x1e", "2x1e", "2x1e", [(0, 0, 0, "uvw", True), (0, 0, 0, "uvu", True)],
+                                   shared_weights=False, internal_weights=False))
+    with pytest.raises(AssertionError, match="trainable weights"):
+        build_descriptor(TPProblem("2x1e", "2x1e", "2x1e", [(0, 0, 0, "uvu", False)], shared_weights=False,
+                                   internal_weights=False))
+
+
+def test_emitted_source_is_specialised():
+    text = build_descriptor(P.readme_problem())
+    src = native.emit_source(text.encode(), "generic")
+    assert "struct Ins<0>" in src and "oeq_generic_forward" in src and "L3_DIM = 5" in src
+
+
+_BIG = {"mace_like", "mace_medium", "nequip_like", "diffdock1", "tetris_poly2", "nequip_water_uvu"}
+
+
+@pytest.mark.parametrize("name,problem", [t for t in tp_problem_matrix() if t[0] not in _BIG],
+                         ids=[t[0] for t in tp_problem_matrix() if t[0] not in _BIG])
+def test_kernels_compile_for_sm100a(name, problem):
+    """NVRTC needs no GPU: every small test problem must specialise and compile (cubins land in the cache that
+    travels with the tree, so the GPU suite starts warm)."""
+    for dt in (np.float32, np.float64):
+        text = build_descriptor(with_dtype(problem, dt))
+        assert native.precompile(text.encode()) >= 1

@@ -1,0 +1,168 @@
+"""GPU parity of the batched tensor product against the fp64 CPU oracle: forward, backward, double and triple
+backward, in the shape of the reference's tests/batch_test.py (batch sizes :66,79,94,113; thresholds :30-36)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import ABS_LINF, REL_L2, rel_l2, tp_problem_matrix, uniform_inputs, with_dtype
+from oracle import tp_oracle
+
+pytestmark = pytest.mark.gpu
+
+MATRIX = tp_problem_matrix()
+IDS = [t[0] for t in MATRIX]
+FP64_TOO = {"readme", "uvu_m33v3", "uvu_l431", "uvw_m40", "uvw_l431", "uvu_shared", "uvw_shared",
+            "uvu_ir_mul", "multi_out", "nequip_like", "mace_medium"}
+
+
+def _cases():
+    for name, p in MATRIX:
+        yield pytest.param(name, p, np.float32, id=f"{name}-f32")
+        if name in FP64_TOO:
+            yield pytest.param(name, p, np.float64, id=f"{name}-f64")
+
+
+def _module(problem):
+    import openequivariance_b200 as oeq
+    return oeq.TensorProduct(problem)
+
+
+def _batch(name, default):
+    return {"mace_like": 96, "mace_medium": 96, "nequip_like": 128, "diffdock1": 64, "tetris_poly2": 64}.get(name, default)
+
+
+@pytest.mark.parametrize("name,problem,dt", list(_cases()))
+def test_tp_forward(name, problem, dt):
+    p = with_dtype(problem, dt)
+    tp = _module(p)
+    B = _batch(name, 1000)
+    x, y, w, *_ = uniform_inputs(p, B)
+    want = tp_oracle.forward(p, x, y, w)
+    got = np.zeros((B, p.irreps_out.dim), dtype=dt)
+    tp.forward_cpu(x, y, got, w)
+    assert rel_l2(got, want) <= REL_L2[dt]
+    if dt == np.float32:
+        assert np.abs(got - want).max() < ABS_LINF["fwd"] * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("name,problem,dt", list(_cases()))
+def test_tp_backward(name, problem, dt):
+    p = with_dtype(problem, dt)
+    tp = _module(p)
+    B = _batch(name, 1000)
+    x, y, w, g, *_ = uniform_inputs(p, B)
+    want = tp_oracle.backward(p, x, y, w, g)
+    dx, dy, dw = np.zeros_like(x), np.zeros_like(y), np.zeros_like(w)
+    tp.backward_cpu(x, dx, y, dy, g, w, dw)
+    for got, ref, what in zip((dx, dy, dw), want, ("dx", "dy", "dW")):
+        assert rel_l2(got, ref) <= REL_L2[dt], what
+
+
+@pytest.mark.parametrize("name,problem,dt", [c for c in _cases() if c.values[0] not in ("mace_like",)])
+def test_tp_double_backward(name, problem, dt):
+    p = with_dtype(problem, dt)
+    tp = _module(p)
+    B = _batch(name, 200)
+    x, y, w, g, x2, y2, w2 = uniform_inputs(p, B)
+    # harness works in kernel weight order on both sides: reorder what goes to the oracle
+    want = tp_oracle.double_backward(p, x, y, tp.reorder_weights_to_e3nn(w), g, x2, y2, tp.reorder_weights_to_e3nn(w2))
+    got = tp.double_backward_cpu(x, y, g, w, w2, x2, y2)
+    want = (want[0], want[1], tp.reorder_weights_from_e3nn(want[2]), want[3])
+    for a, b, what in zip(got, want, ("dx", "dy", "dW", "dg")):
+        assert rel_l2(a, b) <= REL_L2[dt] * 2, what
+
+
+@pytest.mark.parametrize("name", ["readme", "uvu_m5", "uvw_m4", "uvu_shared"])
+def test_tp_triple_backward(name):
+    p = with_dtype(dict(MATRIX)[name], np.float64)
+    tp = _module(p)
+    B = 4
+    x, y, w, g, x2, y2, w2 = uniform_inputs(p, B)
+    rng = np.random.default_rng(5)
+    cots = [rng.uniform(size=t.shape) for t in (x, y, w, g)]
+    got = tp.triple_backward_cpu(x, y, g, w, w2, x2, y2, cots)
+
+    def t(a, grad=True):
+        return torch.tensor(a, dtype=torch.float64, requires_grad=grad)
+
+    xt, yt, gt, at, bt = t(x), t(y), t(g), t(x2), t(y2)
+    wt, ct = t(tp.reorder_weights_to_e3nn(w)), t(tp.reorder_weights_to_e3nn(w2))
+    out = tp_oracle.tp_forward(p, xt, yt, wt)
+    gx, gy, gw = torch.autograd.grad(out, [xt, yt, wt], gt, create_graph=True)
+    second = torch.autograd.grad([gx, gy, gw], [xt, yt, wt, gt], [at, bt, ct], create_graph=True)
+    cots_t = [t(cots[0], False), t(cots[1], False), t(tp.reorder_weights_to_e3nn(cots[2]), False), t(cots[3], False)]
+    third = torch.autograd.grad(list(second), [xt, yt, wt, gt, at, bt, ct], cots_t, allow_unused=True)
+    for i, (a, b) in enumerate(zip(got, third)):
+        b = np.zeros_like(a) if b is None else b.detach().numpy()
+        if i in (2, 6):
+            b = tp.reorder_weights_from_e3nn(b)
+        a = np.zeros_like(b) if a is None else a
+        assert rel_l2(a, b) <= 1e-11, i
+
+
+def test_equivariance_of_oracle_and_kernel():
+    """Rotating inputs by Wigner-D matrices built from the same CG machinery rotates the output: guards the basis
+    and sign conventions that no golden vector pins."""
+    import openequivariance_b200 as oeq
+    from openequivariance_b200.core.graph import spherical_harmonics
+    p = with_dtype(dict(MATRIX)["mace_medium"], np.float64)
+    B = 16
+    gen = torch.Generator().manual_seed(1)
+    v = torch.randn(B, 3, generator=gen, dtype=torch.float64)
+    q, _ = torch.linalg.qr(torch.randn(3, 3, generator=gen, dtype=torch.float64))
+    if torch.det(q) < 0:
+        q = -q
+    y = spherical_harmonics(3, v)
+    y_rot = spherical_harmonics(3, v @ q.T)
+    # D^l from harmonics: solve Y_l(Rv) = D_l Y_l(v) on a generic set of directions
+    probes = torch.randn(64, 3, generator=gen, dtype=torch.float64)
+    Yp, Yr = spherical_harmonics(3, probes), spherical_harmonics(3, probes @ q.T)
+    D = {}
+    for l in range(4):
+        sl = slice(l * l, (l + 1) ** 2)
+        D[l] = torch.linalg.lstsq(Yp[:, sl], Yr[:, sl]).solution.T
+        assert torch.allclose(D[l] @ D[l].T, torch.eye(2 * l + 1, dtype=torch.float64), atol=1e-9)
+
+    def rotate(feat, irreps):
+        out = []
+        for sl, (mul, ir) in zip(irreps.slices(), irreps):
+            blk = feat[:, sl].reshape(B, mul, ir.dim)
+            out.append(torch.einsum("ab,nub->nua", D[ir.l], blk).reshape(B, -1))
+        return torch.cat(out, 1)
+
+    x = torch.randn(B, p.irreps_in1.dim, generator=gen, dtype=torch.float64)
+    w = torch.randn(B, p.weight_numel, generator=gen, dtype=torch.float64)
+    z = tp_oracle.tp_forward(p, x, y, w)
+    z_rot = tp_oracle.tp_forward(p, rotate(x, p.irreps_in1), y_rot, w)
+    assert torch.allclose(z_rot, rotate(z, p.irreps_out), atol=1e-9)
+    tp = oeq.TensorProduct(p)
+    zk = tp(rotate(x, p.irreps_in1).cuda(), y_rot.cuda(), w.cuda()).cpu()
+    assert torch.allclose(zk, rotate(z, p.irreps_out), atol=1e-9)
+
+
+def test_weight_reorder_nontrivial_case_end_to_end():
+    """16x1e (x) 3x1e 'uvu' has a non-identity kernel weight order; e3nn-ordered weights must give oracle results."""
+    p = dict(MATRIX)["uvu_m16v5"]
+    tp = _module(p)
+    assert not np.array_equal(tp._weight_perm, np.arange(p.weight_numel))
+    x, y, w, *_ = uniform_inputs(p, 50)
+    got = np.zeros((50, p.irreps_out.dim), dtype=np.float32)
+    tp.forward_cpu(x, y, got, w)
+    assert rel_l2(got, tp_oracle.forward(p, x, y, w)) <= 1e-5
+
+
+def test_edge_cases_empty_and_single_item():
+    p = dict(MATRIX)["uvu_m5"]
+    tp = _module(p)
+    x = torch.zeros(0, p.irreps_in1.dim, device="cuda")
+    y = torch.zeros(0, p.irreps_in2.dim, device="cuda")
+    w = torch.zeros(0, p.weight_numel, device="cuda")
+    assert tp(x, y, w).shape == (0, p.irreps_out.dim)
+    xs, ys, ws, *_ = uniform_inputs(p, 1)
+    got = tp(torch.tensor(xs).cuda(), torch.tensor(ys).cuda(), torch.tensor(ws).cuda()).cpu().numpy()
+    assert rel_l2(got, tp_oracle.forward(p, xs, ys, tp.reorder_weights_to_e3nn(ws))) <= 1e-5
+    # non-contiguous inputs are accepted (made contiguous inside the op)
+    xb, yb, wb, *_ = uniform_inputs(p, 33)
+    xt = torch.tensor(np.concatenate([xb, xb], 1)).cuda()[:, : p.irreps_in1.dim]
+    got = tp(xt, torch.tensor(yb).cuda(), torch.tensor(wb).cuda()).cpu().numpy()
+    assert rel_l2(got, tp_oracle.forward(p, xb, yb, tp.reorder_weights_to_e3nn(wb))) <= 1e-5
