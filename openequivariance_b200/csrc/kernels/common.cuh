@@ -13,7 +13,16 @@
 // No system headers are included: NVRTC's built-in declarations suffice.
 #pragma once
 
+#ifndef OEQ_DEV
 #define OEQ_DEV __device__ __forceinline__
+#endif
+
+// ---- compile-time loops -------------------------------------------------------------------------------------
+template <int I> struct IntC { static constexpr int value = I; };
+template <int I, int N, typename F>
+OEQ_DEV void static_for(F&& f) {
+    if constexpr (I < N) { f(IntC<I>{}); static_for<I + 1, N>(f); }
+}
 
 // ---- feature addressing -----------------------------------------------------------------------------------
 // Element (u, i) of a block with multiplicity MUL and dimension D starting at OFF, in either layout.

@@ -1,0 +1,421 @@
+// Channel-parallel, TMA-pipelined kernels for 'uvu' problems whose second operand has multiplicity 1 everywhere
+// and whose first operand uses one common multiplicity FU (the MACE-style channelwise product), fp32.
+//
+// Work decomposition
+//   * one consumer thread per channel u (FU threads) handles every path of its channel, so all of an edge's
+//     arithmetic for one channel stays in registers and nothing is exchanged between threads except the
+//     16-number dY reduction;
+//   * one producer warp per CTA streams edges: it issues 1-D TMA bulk copies (cp.async.bulk) of the sender's
+//     feature row X[col] and the edge's weight row W[e] into a ring of shared-memory stages guarded by
+//     mbarriers, fetches Y[e] with cp.async and turns it into the edge's folded coefficients cy[n] = C_n * y[j_n]
+//     (they do not depend on the channel), and -- in the backward pass -- drains each finished stage: dX row
+//     by TMA bulk store / bulk reduce-add, dY by a fixed-order sum of per-warp partials;
+//   * receiver-sorted edges: a CTA owns a contiguous receiver range, keeps the receiver's output row (forward) or
+//     its gradient row (backward) in registers across the receiver's edges; the summation order per receiver
+//     is the edge order, whatever the grid size, hence bitwise reproducible results.
+//
+// Math per channel u and path (l1,l2,l3) with folded coefficients (reference formulas: templates/loop_unroll_tp.cuh:46-96
+// forward, :202-291 backward):
+//   forward   z[k]  += w * sum_n cy_n x[i_n]
+//   backward  s[i]   = sum_n cy_n g[k_n];  dx[i] += w s[i];  dW = sum_i x[i] s[i];  dy[j_n] += C_n x[i_n] (w g[k_n])
+//
+// Every wait on an mbarrier is bounded: when the limit is hit the thread records a code in *status, raises a
+// CTA-wide abort flag and leaves; the host reports OEQB_EKERNEL.
+#pragma once
+#if OEQ_FAST
+
+#define FAST_TP 0       // batch tensor product: edge e reads X[e], writes row e
+#define FAST_DET 1      // convolution, receiver-sorted edges, plain stores
+#define FAST_ATOMIC 2   // convolution, any edge order, atomic / bulk-reduce scatter
+
+struct FastParams {
+    const float* X; const float* Y; const float* W; const float* G;
+    float* Z; float* dX; float* dY; float* dW; float* scratch;
+    const IDX* rows; const IDX* cols;
+    long long N; long long E;
+    int* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------------
+OEQ_DEV unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+OEQ_DEV void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+OEQ_DEV void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+OEQ_DEV void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+OEQ_DEV bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+OEQ_DEV unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait (about two seconds of wall time).  Returns false when it gave up or another thread did.
+OEQ_DEV bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                *(volatile int*)status = code;   // host-mapped word: a plain store, no atomics across the bus
+                return false;
+            }
+        }
+    }
+}
+OEQ_DEV void tma_load(void* dst_smem, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+OEQ_DEV void tma_store(void* dst, const void* src_smem, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+OEQ_DEV void tma_reduce_add(void* dst, const void* src_smem, unsigned bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
+                 "r"(bytes) : "memory");
+}
+OEQ_DEV void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> OEQ_DEV void tma_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> OEQ_DEV void tma_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+OEQ_DEV void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+OEQ_DEV void ldgsts4(void* dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+OEQ_DEV void ldgsts_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> OEQ_DEV void ldgsts_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ---- shared-memory stage ----------------------------------------------------------------------------------
+constexpr int FAST_NCW = FU / 32;                         // consumer warps
+constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
+constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
+struct __align__(16) FastStage {
+    float x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
+    float w[WN];
+    float cy[NCY];
+    float y[FAST_YPAD];
+    float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
+    long long edge, row, col;
+    int first, last, pad0, pad1;
+};
+struct __align__(16) FastShared {
+    FastStage st[FAST_S];
+    unsigned long long full[FAST_S];
+    unsigned long long empty[FAST_S];
+    long long range[4];              // e0, e1, n0, n1
+    int abort_flag;
+    int pad[3];
+};
+static_assert(sizeof(FastShared) <= 232448, "stages exceed shared memory");
+constexpr int FAST_D = (FAST_S >= 5) ? 2 : 1;     // TMA look-ahead in edges (backward needs FAST_S >= FAST_D + 2)
+constexpr int FAST_XPC = L1_DIM / FU;             // registers per channel for an X / dX row
+constexpr int FAST_GPC = L3_DIM / FU;             // registers per channel for a Z / G row
+
+// transposed butterfly: on return lane L (L < N) holds in v[0] the sum over all 32 lanes of element L
+template <int N>
+OEQ_DEV void warp_reduce_transpose(float (&v)[N], int lane) {
+#pragma unroll
+    for (int m = 16; m >= N; m >>= 1) {
+#pragma unroll
+        for (int t = 0; t < N; ++t) v[t] += __shfl_xor_sync(0xffffffffu, v[t], m);
+    }
+#pragma unroll
+    for (int h = N / 2; h >= 1; h >>= 1) {
+        const bool up = (lane & h) != 0;
+#pragma unroll
+        for (int t = 0; t < h; ++t) {
+            const float send = up ? v[t] : v[t + h];
+            const float keep = up ? v[t + h] : v[t];
+            v[t] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+        }
+    }
+}
+
+// ---- work split -------------------------------------------------------------------------------------------
+// Edge / receiver range of a CTA.  Deterministic forward: ranges are snapped to receiver boundaries (a receiver's
+// edges never straddle two CTAs) and together cover every receiver, including those without edges.
+template <int KIND, bool SNAP>
+OEQ_DEV void cta_range(const FastParams& p, long long* out) {
+    const long long G = gridDim.x, b = blockIdx.x;
+    long long e0 = (p.E * b) / G, e1 = (p.E * (b + 1)) / G, n0 = 0, n1 = 0;
+    if (KIND == FAST_DET && SNAP) {
+        n0 = (e0 == 0) ? 0 : (long long)p.rows[e0 - 1] + 1;
+        n1 = (b == G - 1) ? p.N : ((e1 == 0) ? 0 : (long long)p.rows[e1 - 1] + 1);
+        e0 = lower_bound_ll(p.E, n0, [&](long long k) { return p.rows[k]; });
+        e1 = lower_bound_ll(p.E, n1, [&](long long k) { return p.rows[k]; });
+    }
+    out[0] = e0; out[1] = e1; out[2] = n0; out[3] = n1;
+}
+
+// ---- producer ---------------------------------------------------------------------------------------------
+template <int KIND, bool BWD>
+OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
+    const long long e0 = sh.range[0], n = sh.range[1] - sh.range[0];
+    volatile int* abortf = &sh.abort_flag;
+    IDX colv = 0, rowv = 0, rown = 0;
+
+    auto phase_a = [&](long long ia) -> bool {   // claim a stage for edge ia and start its copies
+        const int s = (int)(ia % FAST_S);
+        FastStage& st = sh.st[s];
+        const long long e = e0 + ia;
+        if ((ia & 31) == 0 && KIND != FAST_TP) {
+            const long long me = e + lane;
+            colv = (me < p.E) ? p.cols[me] : (IDX)0;
+            rowv = (me < p.E) ? p.rows[me] : (IDX)0;
+            rown = (me + 1 < p.E) ? p.rows[me + 1] : (IDX)-1;
+        }
+        long long col = e, row = e, nxt = -1;
+        if (KIND != FAST_TP) {
+            col = (long long)__shfl_sync(0xffffffffu, colv, (int)(ia & 31));
+            row = (long long)__shfl_sync(0xffffffffu, rowv, (int)(ia & 31));
+            nxt = (long long)__shfl_sync(0xffffffffu, rown, (int)(ia & 31));
+        }
+        if (ia >= FAST_S) {
+            if (!BWD) {
+                if (!mbar_wait(&sh.empty[s], (unsigned)(((ia / FAST_S) - 1) & 1), abortf, p.status, 11)) return false;
+            } else {
+                tma_wait_read<FAST_S - FAST_D - 1>();   // the stage's previous dX row has left shared memory
+            }
+        }
+        if (lane == 0) {
+            st.edge = e; st.row = row; st.col = col;
+            st.first = (ia == 0) || (KIND == FAST_TP);   // consumers also compare rows; see fast_backward
+            st.last = (ia == n - 1) || (row != nxt) || (KIND == FAST_TP);
+            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN) * sizeof(float)));
+            tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
+            tma_load(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s]);
+        }
+        for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y[j], p.Y + e * L2_DIM + j);
+        ldgsts_commit();
+        return true;
+    };
+    auto phase_b = [&](long long i) {            // Y[e] has landed: fold it into the coefficients, publish the stage
+        FastStage& st = sh.st[(int)(i % FAST_S)];
+        // copies are committed one group per edge, FAST_D edges ahead; near the end of the range fewer are in flight
+        if (i + FAST_D <= n) ldgsts_wait<FAST_D - 1>(); else ldgsts_wait<0>();
+        __syncwarp();
+        for (int q = lane; q < NCY; q += 32) st.cy[q] = FAST_CYC[q] * st.y[FAST_CYJ[q]];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.full[(int)(i % FAST_S)]);
+    };
+    auto phase_c = [&](long long j) -> bool {    // backward only: drain the outputs of a finished edge
+        const int s = (int)(j % FAST_S);
+        FastStage& st = sh.st[s];
+        if (!mbar_wait(&sh.empty[s], (unsigned)((j / FAST_S) & 1), abortf, p.status, 12)) return false;
+        if (lane < L2_DIM) {
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < FAST_NCW; ++w) tot += st.dyp[w][lane];
+            p.dY[st.edge * L2_DIM + lane] = tot;
+        }
+        if (lane == 0) {
+            if (KIND == FAST_TP) tma_store(p.dX + st.edge * L1_DIM, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            else if (KIND == FAST_DET) tma_store(p.scratch + st.edge * L1_DIM, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            else tma_reduce_add(p.dX + st.col * L1_DIM, st.x, (unsigned)(L1_DIM * sizeof(float)));
+        }
+        tma_commit();
+        return true;
+    };
+
+    bool ok = true;
+    for (long long i = -(long long)FAST_D; i < n && ok; ++i) {
+        if (i >= 0) phase_b(i);
+        if (BWD && i >= 1) ok = phase_c(i - 1);
+        if (ok && i + FAST_D < n) ok = phase_a(i + FAST_D);
+    }
+    if (BWD) {
+        if (ok && n > 0) ok = phase_c(n - 1);
+        tma_wait_all<0>();
+    }
+    ldgsts_wait<0>();
+}
+
+// ---- forward ----------------------------------------------------------------------------------------------
+template <int KIND>
+OEQ_DEV void fast_forward_body(const FastParams& p) {
+    extern __shared__ __align__(16) unsigned char fast_smem_raw[];
+    FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FU); }
+        sh.abort_flag = 0;
+        cta_range<KIND, true>(p, sh.range);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid >= FU) { fast_producer<KIND, false>(p, sh, lane); return; }
+
+    const int u = tid;
+    const long long n = sh.range[1] - sh.range[0];
+    volatile int* abortf = &sh.abort_flag;
+    float acc[FAST_GPC];
+#pragma unroll
+    for (int k = 0; k < FAST_GPC; ++k) acc[k] = 0.f;
+    long long next_row = sh.range[2];
+
+    auto zero_rows = [&](long long a, long long b) {   // receivers without edges
+        for (long long r = a; r < b; ++r)
+            for (int q = u; q < L3_DIM; q += FU) p.Z[r * L3_DIM + q] = 0.f;
+    };
+
+    for (long long i = 0; i < n; ++i) {
+        const int s = (int)(i % FAST_S);
+        FastStage& st = sh.st[s];
+        if (!mbar_wait(&sh.full[s], (unsigned)((i / FAST_S) & 1), abortf, p.status, 21)) return;
+        const long long row = st.row;
+        const int last = st.last;
+        float xr[FAST_XPC];
+        static_for<0, NB1>([&](auto bc) {
+            using B1 = Blk1<decltype(bc)::value>;
+#pragma unroll
+            for (int i1 = 0; i1 < B1::D; ++i1) xr[B1::OFF / FU + i1] = st.x[B1::OFF + u * B1::D + i1];
+        });
+        const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
+        static_for<0, NINS>([&](auto ic) {
+            using F = FIns<decltype(ic)::value>;
+            F::fwd(xr + F::XO, cy4, st.w[F::WOFF + u], acc + F::GO);
+        });
+        mbar_arrive(&sh.empty[s]);
+        if (last) {
+            if (KIND == FAST_DET) { zero_rows(next_row, row); next_row = row + 1; }
+            float* zrow = p.Z + row * L3_DIM;
+            static_for<0, NB3>([&](auto oc) {
+                using B3 = Blk3<decltype(oc)::value>;
+#pragma unroll
+                for (int k = 0; k < B3::D; ++k) {
+                    float* dst = zrow + B3::OFF + u * B3::D + k;
+                    if (KIND == FAST_ATOMIC) atomicAdd(dst, acc[B3::OFF / FU + k]); else *dst = acc[B3::OFF / FU + k];
+                    acc[B3::OFF / FU + k] = 0.f;
+                }
+            });
+        }
+    }
+    if (KIND == FAST_DET) zero_rows(next_row, sh.range[3]);
+}
+
+// ---- backward ---------------------------------------------------------------------------------------------
+template <int KIND>
+OEQ_DEV void fast_backward_body(const FastParams& p) {
+    extern __shared__ __align__(16) unsigned char fast_smem_raw[];
+    FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FU); }
+        sh.abort_flag = 0;
+        cta_range<KIND, false>(p, sh.range);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid >= FU) { fast_producer<KIND, true>(p, sh, lane); return; }
+
+    const int u = tid;
+    const long long n = sh.range[1] - sh.range[0];
+    volatile int* abortf = &sh.abort_flag;
+    float g[FAST_GPC];
+    long long cur_row = -1;
+
+    for (long long i = 0; i < n; ++i) {
+        const int s = (int)(i % FAST_S);
+        FastStage& st = sh.st[s];
+        if (!mbar_wait(&sh.full[s], (unsigned)((i / FAST_S) & 1), abortf, p.status, 22)) return;
+        const long long row = st.row, e = st.edge;
+        if (row != cur_row) {   // new receiver: its gradient row goes to registers for all of its edges
+            const float* grow = p.G + row * L3_DIM;
+            static_for<0, NB3>([&](auto oc) {
+                using B3 = Blk3<decltype(oc)::value>;
+#pragma unroll
+                for (int k = 0; k < B3::D; ++k) g[B3::OFF / FU + k] = __ldg(grow + B3::OFF + u * B3::D + k);
+            });
+            cur_row = row;
+        }
+        float xr[FAST_XPC], dxr[FAST_XPC], dyr[FAST_NYP];
+        static_for<0, NB1>([&](auto bc) {
+            using B1 = Blk1<decltype(bc)::value>;
+#pragma unroll
+            for (int i1 = 0; i1 < B1::D; ++i1) { xr[B1::OFF / FU + i1] = st.x[B1::OFF + u * B1::D + i1]; dxr[B1::OFF / FU + i1] = 0.f; }
+        });
+#pragma unroll
+        for (int j = 0; j < FAST_NYP; ++j) dyr[j] = 0.f;
+        const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
+        float* dwrow = p.dW + e * WN;
+        static_for<0, NINS>([&](auto ic) {
+            using F = FIns<decltype(ic)::value>;
+            float dw;
+            F::bwd(xr + F::XO, g + F::GO, cy4, st.w[F::WOFF + u], dxr + F::XO, dyr + F::Y0, dw);
+            dwrow[F::WOFF + u] = dw;
+        });
+        static_for<0, NB1>([&](auto bc) {
+            using B1 = Blk1<decltype(bc)::value>;
+#pragma unroll
+            for (int i1 = 0; i1 < B1::D; ++i1) st.x[B1::OFF + u * B1::D + i1] = dxr[B1::OFF / FU + i1];
+        });
+        warp_reduce_transpose<FAST_NYP>(dyr, lane);
+        if (lane < FAST_NYP) st.dyp[warp][lane] = dyr[0];
+        fence_async_smem();          // the dX row is read from shared memory by the async proxy (TMA)
+        mbar_arrive(&sh.empty[s]);
+    }
+}
+
+// ---- entry points (one per program: FAST_KERNEL selects which) ----------------------------------------------
+#if FAST_KERNEL == 0
+extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_fwd_tp(const FastParams p) { fast_forward_body<FAST_TP>(p); }
+#elif FAST_KERNEL == 1
+extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_fwd_det(const FastParams p) { fast_forward_body<FAST_DET>(p); }
+#elif FAST_KERNEL == 2
+extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_fwd_atomic(const FastParams p) { fast_forward_body<FAST_ATOMIC>(p); }
+#elif FAST_KERNEL == 3
+extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_bwd_tp(const FastParams p) { fast_backward_body<FAST_TP>(p); }
+#elif FAST_KERNEL == 4
+extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_bwd_det(const FastParams p) { fast_backward_body<FAST_DET>(p); }
+#elif FAST_KERNEL == 5
+extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_bwd_atomic(const FastParams p) { fast_backward_body<FAST_ATOMIC>(p); }
+#elif FAST_KERNEL == 6
+// Deterministic scatter of the per-edge dX rows: colptr[c] = first position k (in sender-major order) whose sender >= c
+extern "C" __global__ void oeq_fast_colptr(const IDX* cols, const IDX* perm, long long E, long long N, long long* colptr) {
+    const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (k > E) return;
+    const long long prev = (k == 0) ? -1 : (long long)cols[perm[k - 1]];
+    const long long cur = (k == E) ? N : (long long)cols[perm[k]];
+    for (long long c = prev + 1; c <= cur; ++c) colptr[c] = k;
+}
+// dX[c] = sum over the sender's edges, in sender-major list order, of the per-edge rows in scratch
+extern "C" __global__ void __launch_bounds__(256) oeq_fast_dx_reduce(const float* scratch, const IDX* perm, const long long* colptr,
+                                                                     long long N, float* dX) {
+    constexpr int NQ = L1_DIM / 4;
+    for (long long c = blockIdx.x; c < N; c += gridDim.x) {
+        const long long k0 = colptr[c], k1 = colptr[c + 1];
+        for (int q = threadIdx.x; q < NQ; q += 256) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            long long k = k0;
+            for (; k + 4 <= k1; k += 4) {
+                const long long ea = perm[k], eb = perm[k + 1], ec = perm[k + 2], ed = perm[k + 3];
+                const float4 a = __ldcs(reinterpret_cast<const float4*>(scratch + ea * L1_DIM) + q);
+                const float4 b = __ldcs(reinterpret_cast<const float4*>(scratch + eb * L1_DIM) + q);
+                const float4 cc = __ldcs(reinterpret_cast<const float4*>(scratch + ec * L1_DIM) + q);
+                const float4 d = __ldcs(reinterpret_cast<const float4*>(scratch + ed * L1_DIM) + q);
+                acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+                acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+                acc.x += cc.x; acc.y += cc.y; acc.z += cc.z; acc.w += cc.w;
+                acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+            }
+            for (; k < k1; ++k) {
+                const float4 a = __ldcs(reinterpret_cast<const float4*>(scratch + (long long)perm[k] * L1_DIM) + q);
+                acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+            }
+            reinterpret_cast<float4*>(dX + c * L1_DIM)[q] = acc;
+        }
+    }
+}
+#endif
+
+#endif  // OEQ_FAST

@@ -12,12 +12,6 @@
 //   uvw  z[w,k] += sum_{u,v} W[u,v,w] * sum_ij C[ijk] x[u,i] y[v,j]
 #pragma once
 
-template <int I> struct IntC { static constexpr int value = I; };
-template <int I, int N, typename F>
-OEQ_DEV void static_for(F&& f) {
-    if constexpr (I < N) { f(IntC<I>{}); static_for<I + 1, N>(f); }
-}
-
 #define OEQ_UNIT_ITEM 0
 #define OEQ_UNIT_EDGE 1
 #define OEQ_UNIT_SEGMENT 2

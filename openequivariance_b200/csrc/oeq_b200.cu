@@ -71,6 +71,10 @@ struct Desc {
     std::vector<Instr> ins;
     bool fast = false;   // channel-parallel pipelined kernels applicable
     int fast_U = 0;      // common multiplicity on the fast path
+    int fast_S = 0;      // shared-memory stages per CTA
+    int fast_ctas = 0;   // resident CTAs per SM the stages are sized for
+    int fast_ncy = 0;    // folded-coefficient slots per edge (each instruction padded to a multiple of 4)
+    size_t fast_smem = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
     size_t idx_bytes() const { return idx == 3 ? 4 : 8; }
 };
@@ -135,7 +139,7 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     if (d.dim[0] * 1LL > (1LL << 24) || d.dim[2] > (1LL << 24) || d.wn > (1LL << 30)) return bad("problem too large");
 
     // Fast path: fp32, mul_ir, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
-    // that is a multiple of 32, l <= 4 everywhere, no Kahan.
+    // that is a multiple of 32, l <= 4 everywhere, no Kahan, rows small enough to live in registers.
     d.fast = false;
     if (d.dtype == 1 && d.layout == 0 && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
         bool ok = true;
@@ -143,9 +147,28 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         for (auto& b : d.L[0]) ok = ok && b.mul == U && b.l <= 4;
         for (auto& b : d.L[1]) ok = ok && b.mul == 1 && b.l <= 4;
         for (auto& b : d.L[2]) ok = ok && b.mul == U && b.l <= 4;
-        ok = ok && U >= 32 && U % 32 == 0 && U <= 512;
-        d.fast = ok;
-        d.fast_U = U;
+        ok = ok && U >= 32 && U % 32 == 0 && U <= 256 && d.dim[1] <= 32;
+        ok = ok && d.dim[0] / U <= 32 && d.dim[2] / U <= 112;
+        if (ok) {
+            int ncy = 0;
+            for (auto& I : d.ins) ncy += ((int)I.nz.size() + 3) & ~3;
+            const int nyp = d.dim[1] <= 1 ? 1 : d.dim[1] <= 2 ? 2 : d.dim[1] <= 4 ? 4 : d.dim[1] <= 8 ? 8 : d.dim[1] <= 16 ? 16 : 32;
+            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (U / 32) * nyp) + 40) + 15) & ~(size_t)15;
+            int ctas = 256 / U;
+            ctas = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas);
+            int S = 0;
+            for (; ctas >= 1; ctas /= 2) {
+                const size_t budget = 232448 / ctas - 1024 - 256;
+                S = (int)(budget / (stage + 16));
+                if (S > 6) S = 6;
+                if (S >= 3) break;
+            }
+            if (S >= 3 && ctas >= 1) {
+                d.fast = true;
+                d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy;
+                d.fast_smem = (size_t)S * (stage + 16) + 128;
+            }
+        }
     }
     return true;
 }
@@ -218,24 +241,115 @@ std::string emit_header(const Desc& d) {
     return s.str();
 }
 
-// --------------------------------------------------------------------------------------- kernel families
-enum Family { FAM_GENERIC = 0, FAM_COUNT };
-const char* family_name(int f) {
-    switch (f) {
-        case FAM_GENERIC: return "generic";
+// Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
+// cy[n] = C_n * y[j_n] is formed once per edge by the producer warp; the consumer code below reads it as float4.
+std::string emit_fast(const Desc& d) {
+    std::ostringstream s;
+    if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
+    s << "#define OEQ_FAST 1\n";
+    s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << d.fast_S
+      << ", FAST_CTAS = " << d.fast_ctas << ";\n";
+    std::ostringstream cyc, cyj;
+    std::vector<int> cyoff;
+    int off = 0;
+    for (auto& I : d.ins) {
+        cyoff.push_back(off);
+        const int pad = ((int)I.nz.size() + 3) & ~3;
+        for (int n = 0; n < pad; ++n) {
+            const bool real = n < (int)I.nz.size();
+            cyc << (real ? hexf(I.nz[n].c) : std::string("0.0")) << "f, ";
+            cyj << (real ? d.L[1][I.b].off + I.nz[n].j : 0) << ", ";
+        }
+        off += pad;
     }
-    return "?";
+    s << "__device__ const float FAST_CYC[NCY] = {" << cyc.str() << "};\n";
+    s << "__device__ const int FAST_CYJ[NCY] = {" << cyj.str() << "};\n";
+    s << "template <int I> struct FIns;\n";
+    const char comp[4] = {'x', 'y', 'z', 'w'};
+    for (size_t n = 0; n < d.ins.size(); ++n) {
+        const Instr& I = d.ins[n];
+        const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
+        const int D1 = A.d(), D3 = O.d(), nnz = (int)I.nz.size(), nq = (nnz + 3) / 4;
+        auto C = [&](int z) { std::ostringstream t; t << "c" << (z / 4) << "." << comp[z % 4]; return t.str(); };
+        s << "template <> struct FIns<" << n << "> {\n";
+        s << "  static constexpr int XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
+          << ", CY4 = " << cyoff[n] / 4 << ", WOFF = " << I.woff << ", D1 = " << D1 << ", D3 = " << D3 << ";\n";
+        // ---- forward
+        s << "  static OEQ_DEV void fwd(const float* x, const float4* cy, const float w, float* acc) {\n";
+        for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
+        if (D1 <= D3) {
+            for (int i = 0; i < D1; ++i) s << "    const float xs" << i << " = w * x[" << i << "];\n";
+            for (int z = 0; z < nnz; ++z)
+                s << "    acc[" << I.nz[z].k << "] = fmaf(" << C(z) << ", xs" << I.nz[z].i << ", acc[" << I.nz[z].k << "]);\n";
+        } else {
+            for (int k = 0; k < D3; ++k) s << "    float t" << k << " = 0.f;\n";
+            for (int z = 0; z < nnz; ++z)
+                s << "    t" << I.nz[z].k << " = fmaf(" << C(z) << ", x[" << I.nz[z].i << "], t" << I.nz[z].k << ");\n";
+            for (int k = 0; k < D3; ++k) s << "    acc[" << k << "] = fmaf(w, t" << k << ", acc[" << k << "]);\n";
+        }
+        s << "  }\n";
+        // ---- backward
+        s << "  static OEQ_DEV void bwd(const float* x, const float* g, const float4* cy, const float w, float* dx, float* dy, float& dw) {\n";
+        for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
+        for (int i = 0; i < D1; ++i) s << "    float s" << i << " = 0.f;\n";
+        for (int z = 0; z < nnz; ++z)
+            s << "    s" << I.nz[z].i << " = fmaf(" << C(z) << ", g[" << I.nz[z].k << "], s" << I.nz[z].i << ");\n";
+        s << "    float dwv = 0.f;\n";
+        for (int i = 0; i < D1; ++i) {
+            s << "    dwv = fmaf(x[" << i << "], s" << i << ", dwv);\n";
+            s << "    dx[" << i << "] = fmaf(w, s" << i << ", dx[" << i << "]);\n";
+        }
+        s << "    dw = dwv;\n";
+        const bool scale_g = D3 <= D1;
+        if (scale_g) for (int k = 0; k < D3; ++k) s << "    const float q" << k << " = w * g[" << k << "];\n";
+        else for (int i = 0; i < D1; ++i) s << "    const float q" << i << " = w * x[" << i << "];\n";
+        std::vector<Nz> byik = I.nz;
+        std::stable_sort(byik.begin(), byik.end(), [](const Nz& a, const Nz& b) { return a.i != b.i ? a.i < b.i : a.k < b.k; });
+        for (size_t z = 0; z < byik.size();) {
+            size_t m = z;
+            s << "    { const float pr = ";
+            if (scale_g) s << "x[" << byik[z].i << "] * q" << byik[z].k; else s << "q" << byik[z].i << " * g[" << byik[z].k << "]";
+            s << ";";
+            while (m < byik.size() && byik[m].i == byik[z].i && byik[m].k == byik[z].k) {
+                s << " dy[" << byik[m].j << "] = fmaf(" << hexf(byik[m].c) << "f, pr, dy[" << byik[m].j << "]);";
+                ++m;
+            }
+            s << " }\n";
+            z = m;
+        }
+        s << "  }\n};\n";
+    }
+    return s.str();
 }
+
+// --------------------------------------------------------------------------------------- kernel families
+enum Family {
+    FAM_GENERIC = 0,
+    FAM_FAST_FWD_TP, FAM_FAST_FWD_DET, FAM_FAST_FWD_ATOMIC, FAM_FAST_BWD_TP, FAM_FAST_BWD_DET, FAM_FAST_BWD_ATOMIC,
+    FAM_FAST_SCATTER,
+    FAM_COUNT
+};
+const char* const kFamilyNames[FAM_COUNT] = {"generic", "fast_fwd_tp", "fast_fwd_det", "fast_fwd_atomic", "fast_bwd_tp",
+                                             "fast_bwd_det", "fast_bwd_atomic", "fast_scatter"};
+const char* family_name(int f) { return (f >= 0 && f < FAM_COUNT) ? kFamilyNames[f] : "?"; }
 int family_from_name(const std::string& n) {
-    if (n == "generic" || n == "generic_forward" || n == "generic_backward") return FAM_GENERIC;
+    for (int f = 0; f < FAM_COUNT; ++f)
+        if (n == kFamilyNames[f]) return f;
+    if (n == "generic_forward" || n == "generic_backward") return FAM_GENERIC;
     return -1;
 }
 
 std::string family_source(const Desc& d, const std::string& header, int fam) {
     std::string src = header;
-    src += K_COMMON;
-    if (fam == FAM_GENERIC) src += K_GENERIC;
-    (void)d;
+    if (fam == FAM_GENERIC) {
+        src += K_COMMON;
+        src += K_GENERIC;
+    } else {
+        src += emit_fast(d);
+        src += "#define FAST_KERNEL " + std::to_string(fam - FAM_FAST_FWD_TP) + "\n";
+        src += K_COMMON;
+        src += K_FAST_UVU;
+    }
     return src;
 }
 
@@ -453,6 +567,89 @@ int generic_backward(Entry* e, BwdParams p, cudaStream_t st) {
     return launch(k, generic_grid(p.n_units), 128, 0, args, st);
 }
 
+// ------------------------------------------------------------------------------- channel-parallel path
+struct FastParams {
+    const void* X; const void* Y; const void* W; const void* G;
+    void* Z; void* dX; void* dY; void* dW; void* scratch;
+    const void* rows; const void* cols;
+    long long N; long long E;
+    int* status;
+};
+
+// One host-mapped status word per device: kernels store a non-zero code when a bounded wait runs out.
+int* g_status_host[64] = {nullptr};
+int* g_status_dev[64] = {nullptr};
+
+int status_word(int** dev_ptr) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(OEQB_EINVAL, "device index %d out of range", dev);
+    if (!g_status_host[dev]) {
+        int* h = nullptr;
+        CUDA_TRY(cudaHostAlloc((void**)&h, 64, cudaHostAllocMapped));
+        memset(h, 0, 64);
+        int* dptr = nullptr;
+        CUDA_TRY(cudaHostGetDevicePointer((void**)&dptr, h, 0));
+        g_status_host[dev] = h;
+        g_status_dev[dev] = dptr;
+    }
+    const int code = *(volatile int*)g_status_host[dev];
+    if (code != 0) {
+        *(volatile int*)g_status_host[dev] = 0;
+        return fail(OEQB_EKERNEL, "an earlier kernel gave up a bounded wait (code %d); its outputs are invalid", code);
+    }
+    *dev_ptr = g_status_dev[dev];
+    return OEQB_OK;
+}
+
+bool aligned16(std::initializer_list<const void*> ptrs) {
+    for (const void* p : ptrs)
+        if (((uintptr_t)p & 15u) != 0) return false;
+    return true;
+}
+
+bool use_fast(const Desc& d) { return d.fast && !g_force_generic; }
+
+constexpr size_t kAlign = 256;
+size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+// kernel: 0 fwd_tp, 1 fwd_det, 2 fwd_atomic, 3 bwd_tp, 4 bwd_det, 5 bwd_atomic
+int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st) {
+    static const char* names[6] = {"oeq_fast_fwd_tp", "oeq_fast_fwd_det", "oeq_fast_fwd_atomic",
+                                   "oeq_fast_bwd_tp", "oeq_fast_bwd_det", "oeq_fast_bwd_atomic"};
+    const Desc& d = e->d;
+    int rc;
+    if ((rc = status_word(&p.status))) return rc;
+    Program* prog;
+    if ((rc = get_program(e, FAM_FAST_FWD_TP + kernel, &prog))) return rc;
+    cudaKernel_t k;
+    if ((rc = get_kernel(prog, names[kernel], d.fast_smem, &k))) return rc;
+    long long grid = (long long)sm_count() * d.fast_ctas;
+    const long long work = p.E > 0 ? p.E : 1;
+    if (grid > work) grid = work;
+    void* args[] = {&p};
+    return launch(k, (unsigned)grid, (unsigned)(d.fast_U + 32), d.fast_smem, args, st);
+}
+
+// dX[c] = sum of the per-edge rows in scratch over the sender's edges, in sender-major list order
+int fast_scatter(Entry* e, const void* scratch, const void* cols, const void* perm, long long N, long long E, void* colptr,
+                 void* dX, cudaStream_t st) {
+    int rc;
+    Program* prog;
+    if ((rc = get_program(e, FAM_FAST_SCATTER, &prog))) return rc;
+    cudaKernel_t k1, k2;
+    if ((rc = get_kernel(prog, "oeq_fast_colptr", 0, &k1))) return rc;
+    if ((rc = get_kernel(prog, "oeq_fast_dx_reduce", 0, &k2))) return rc;
+    {
+        void* args[] = {(void*)&cols, (void*)&perm, &E, &N, &colptr};
+        if ((rc = launch(k1, (unsigned)((E + 1 + 255) / 256), 256, 0, args, st))) return rc;
+    }
+    long long grid = (long long)sm_count() * 8;
+    if (grid > N) grid = N;
+    void* args[] = {(void*)&scratch, (void*)&perm, &colptr, &N, &dX};
+    return launch(k2, (unsigned)grid, 256, 0, args, st);
+}
+
 int check_ptrs(std::initializer_list<const void*> ptrs, const char* what) {
     for (const void* p : ptrs)
         if (!p) return fail(OEQB_EINVAL, "%s: null pointer argument", what);
@@ -521,6 +718,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     const std::string header = emit_header(d);
     int done = 0;
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
+        if (fam != FAM_GENERIC && !d.fast) continue;
         std::string cubin;
         int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
         if (rc) return -rc;
@@ -537,6 +735,10 @@ int oeqb_tp_forward(const void* desc, size_t desc_len, int64_t key, int64_t batc
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    if (use_fast(e->d) && aligned16({x, W})) {
+        FastParams f{x, y, W, nullptr, z, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
+        return fast_launch(e, 0, f, (cudaStream_t)stream);
+    }
     FwdParams p{x, y, W, z, nullptr, nullptr, batch, batch, UNIT_ITEM, OUT_STORE};
     return generic_forward(e, p, (cudaStream_t)stream);
 }
@@ -552,6 +754,10 @@ int oeqb_tp_backward(const void* desc, size_t desc_len, int64_t key, int64_t bat
     const Desc& d = e->d;
     if (d.shared) CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st));
     if (batch == 0) return OEQB_OK;
+    if (use_fast(d) && aligned16({x, W, dx})) {
+        FastParams f{x, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
+        return fast_launch(e, 3, f, st);
+    }
     CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
     BwdParams p{x, y, y, W, g, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, UNIT_ITEM, 0};
     return generic_backward(e, p, st);
@@ -592,6 +798,10 @@ int64_t oeqb_conv_workspace_bytes(const void* desc, size_t desc_len, int64_t key
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return -(int64_t)rc;
+    const Desc& d = e->d;
+    // Deterministic backward on the channel-parallel path: one dX row per edge plus the sender offsets.
+    if (direction == 1 && d.conv && d.det && use_fast(d))
+        return (int64_t)(round_up((size_t)n_edges * d.dim[0] * d.elt()) + round_up((size_t)(n_nodes + 1) * 8));
     return 0;
 }
 
@@ -615,11 +825,20 @@ int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_
     if (int rc = check_ptrs({X, Z}, "oeqb_conv_forward")) return rc;
     if (n_edges > 0) if (int rc = check_ptrs({Y, W, rows, cols}, "oeqb_conv_forward")) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W});
     if (d.det) {
+        if (fast) {
+            FastParams f{X, Y, W, nullptr, Z, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+            return fast_launch(e, 1, f, st);
+        }
         FwdParams p{X, Y, W, Z, rows, cols, n_nodes, n_edges, UNIT_SEGMENT, OUT_STORE};
         return generic_forward(e, p, st);
     }
     CUDA_TRY(cudaMemsetAsync(Z, 0, n_nodes * d.dim[2] * d.elt(), st));
+    if (fast) {
+        FastParams f{X, Y, W, nullptr, Z, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+        return fast_launch(e, 2, f, st);
+    }
     FwdParams p{X, Y, W, Z, rows, cols, n_edges, n_edges, UNIT_EDGE, OUT_ATOMIC};
     return generic_forward(e, p, st);
 }
@@ -628,7 +847,6 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
                        const void* X, const void* Y, const void* W, const void* G, void* dX, void* dY, void* dW,
                        const void* rows, const void* cols, const void* transpose_perm, void* workspace,
                        int64_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
@@ -640,8 +858,25 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
     if (int rc = check_ptrs({X, G, dX}, "oeqb_conv_backward")) return rc;
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, dY, dW, rows, cols}, "oeqb_conv_backward")) return rc;
-        CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
     }
+    const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W, dX, workspace});
+    if (d.det && fast) {
+        const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
+        const size_t need = scratch_bytes + round_up((size_t)(n_nodes + 1) * 8);
+        if (!workspace || workspace_bytes < (int64_t)need)
+            return fail(OEQB_EINVAL, "oeqb_conv_backward: workspace of %lld bytes is smaller than the %zu required",
+                        (long long)workspace_bytes, need);
+        void* colptr = (char*)workspace + scratch_bytes;
+        FastParams f{X, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
+        if (int rc = fast_launch(e, 4, f, st)) return rc;
+        return fast_scatter(e, workspace, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
+    }
+    if (!d.det && fast) {
+        CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
+        FastParams f{X, Y, W, G, nullptr, dX, dY, dW, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+        return fast_launch(e, 5, f, st);
+    }
+    if (n_edges > 0) CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
     if (d.det) {
         BwdParams p{X, Y, Y, W, G, dX, dY, dW, rows, cols, transpose_perm, n_nodes, n_edges, UNIT_SEGMENT, 0};
         return generic_backward(e, p, st);
