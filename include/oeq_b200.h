@@ -40,6 +40,9 @@ extern "C" {
 #define OEQB_EUNSUPPORTED 5
 #define OEQB_EKERNEL 6     /* a kernel reported a bounded wait that ran out (device status word non-zero) */
 
+/* Size of the scratch array built into the library for oeqb_conv_backward_noalloc (64 MiB). */
+#define OEQB_NOALLOC_SCRATCH_BYTES (64u << 20)
+
 /* Mirrors KernelProp of extension/torch_core.hpp:144-178 (sizes and dtype tags the op layer validates
  * tensors against), plus which kernel family will serve the problem. */
 typedef struct oeqb_kernel_prop {
@@ -104,6 +107,31 @@ OEQB_API int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, 
                        void* dX, void* dY, void* dW,
                        const void* rows, const void* cols, const void* transpose_perm,
                        void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Allocation-free variant of oeqb_conv_backward for deterministic convolutions on the channel-parallel kernels.
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: hosts that may not allocate device memory at the point where they call us -- a solver or serving
+ * runtime that has already handed all device memory to its own arena, or a step that must not provoke the implicit
+ * device-wide synchronisation that cudaMalloc / cudaFree perform.  Such callers cannot give us a workspace, and we
+ * must not create one.  The per-edge gradient rows and the sender offsets therefore live in a fixed array compiled
+ * into the library (OEQB_NOALLOC_SCRATCH_BYTES, held by every GPU that loads the library until the process ends).
+ *
+ * Limits and rules:
+ *   - n_edges * L1_dim * 4 (rounded up to 256) + (n_nodes + 1) * 8 (rounded up to 256) + 256 bytes must fit in
+ *     OEQB_NOALLOC_SCRATCH_BYTES; larger graphs are refused with OEQB_EINVAL and a message giving both numbers.
+ *   - Only descriptors with deterministic = 1 that oeqb_query reports as fast_path = 1; others get OEQB_EUNSUPPORTED.
+ *   - The first call for a problem on a device does one-time set-up (looks up the array's device address, specialises
+ *     and loads the kernels).  Make that call before entering any stream capture; later calls do no set-up.
+ *   - No cudaMalloc / cudaFree / allocator call is made, on any call.  All calls share the one array, and it keeps the
+ *     previous call's contents: the library re-zeroes the one word that must start at zero and overwrites the rest.
+ *     Two calls whose kernels overlap on the GPU (different streams, or different host threads) race on the array.
+ *   - Results are the same as oeqb_conv_backward's.  A kernel wait that runs out is recorded inside the array and is
+ *     not reported by this entry point. */
+OEQB_API int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                               const void* X, const void* Y, const void* W, const void* G,
+                               void* dX, void* dY, void* dW,
+                               const void* rows, const void* cols, const void* transpose_perm, void* stream);
 
 /* Second-order pass of the convolution; argument meaning as oeqb_tp_double_backward with node-level X, X2,
  * dX, G, dG.  Replaces JITConvImpl::double_backward (convolution.hpp:138-176) behind

@@ -614,12 +614,13 @@ constexpr size_t kAlign = 256;
 size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 // kernel: 0 fwd_tp, 1 fwd_det, 2 fwd_atomic, 3 bwd_tp, 4 bwd_det, 5 bwd_atomic
-int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st) {
+int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status_override = nullptr) {
     static const char* names[6] = {"oeq_fast_fwd_tp", "oeq_fast_fwd_det", "oeq_fast_fwd_atomic",
                                    "oeq_fast_bwd_tp", "oeq_fast_bwd_det", "oeq_fast_bwd_atomic"};
     const Desc& d = e->d;
     int rc;
-    if ((rc = status_word(&p.status))) return rc;
+    if (status_override) p.status = status_override;
+    else if ((rc = status_word(&p.status))) return rc;
     Program* prog;
     if ((rc = get_program(e, FAM_FAST_FWD_TP + kernel, &prog))) return rc;
     cudaKernel_t k;
@@ -648,6 +649,28 @@ int fast_scatter(Entry* e, const void* scratch, const void* cols, const void* pe
     if (grid > N) grid = N;
     void* args[] = {(void*)&scratch, (void*)&perm, &colptr, &N, &dX};
     return launch(k2, (unsigned)grid, 256, 0, args, st);
+}
+
+// ------------------------------------------------------------------- scratch that nobody has to allocate
+// Backing store of oeqb_conv_backward_noalloc: a fixed array that is part of the library image, so every GPU that
+// loads the library holds these bytes until the process exits.  In host code the name below is only a handle for
+// the symbol; the device address is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[OEQB_NOALLOC_SCRATCH_BYTES];
+void* g_noalloc_ptr[64] = {nullptr};
+
+int noalloc_scratch(void** out) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(OEQB_EINVAL, "device index %d out of range", dev);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        cudaError_t ce = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (ce != cudaSuccess || !p)
+            return fail(OEQB_ECUDA, "cudaGetSymbolAddress(built-in scratch) failed on device %d: %s", dev, cudaGetErrorString(ce));
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return OEQB_OK;
 }
 
 int check_ptrs(std::initializer_list<const void*> ptrs, const char* what) {
@@ -930,6 +953,44 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
     if ((rc = generic_backward(e, b, st))) return rc;
     b.x = X; b.y_dx = Y; b.y_dw = Y2; b.W = W2; b.accum = 1;
     return generic_backward(e, b, st);
+}
+
+
+int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                               const void* X, const void* Y, const void* W, const void* G, void* dX, void* dY, void* dW,
+                               const void* rows, const void* cols, const void* transpose_perm, void* stream) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    const Desc& d = e->d;
+    if (int rc = conv_check(d, n_nodes, n_edges, transpose_perm, "oeqb_conv_backward_noalloc")) return rc;
+    if (!(d.det && use_fast(d)))
+        return fail(OEQB_EUNSUPPORTED, "oeqb_conv_backward_noalloc: only deterministic convolutions served by the "
+                                       "channel-parallel kernels use scratch; call oeqb_conv_backward for this problem");
+    if (n_nodes == 0 || n_edges == 0)
+        return fail(OEQB_EINVAL, "oeqb_conv_backward_noalloc: empty graph; call oeqb_conv_backward");
+    const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
+    const size_t colptr_bytes = round_up((size_t)(n_nodes + 1) * 8);
+    const size_t need = scratch_bytes + colptr_bytes + kAlign;   // last slot: the kernels' status word
+    if (need > (size_t)OEQB_NOALLOC_SCRATCH_BYTES)
+        return fail(OEQB_EINVAL, "oeqb_conv_backward_noalloc: this graph needs %zu bytes of scratch (%lld edges x %lld-float "
+                                 "rows + %lld sender offsets) but the built-in array holds %zu; use oeqb_conv_backward "
+                                 "with a caller-provided workspace",
+                    need, (long long)n_edges, (long long)d.dim[0], (long long)n_nodes + 1, (size_t)OEQB_NOALLOC_SCRATCH_BYTES);
+    if (int rc = check_ptrs({X, Y, W, G, dX, dY, dW, rows, cols}, "oeqb_conv_backward_noalloc")) return rc;
+    if (!aligned16({X, W, dX}))
+        return fail(OEQB_EINVAL, "oeqb_conv_backward_noalloc: X, W and dX must be 16-byte aligned");
+    void* base = nullptr;
+    if (int rc = noalloc_scratch(&base)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    void* colptr = (char*)base + scratch_bytes;
+    int* status = (int*)((char*)base + scratch_bytes + colptr_bytes);
+    // The array keeps whatever the previous call left.  Per-edge rows and sender offsets are overwritten in full by
+    // the kernels below; only the status word has to start at zero.
+    CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
+    FastParams f{X, Y, W, G, nullptr, dX, dY, dW, base, rows, cols, n_nodes, n_edges, nullptr};
+    if (int rc = fast_launch(e, 4, f, st, status)) return rc;
+    return fast_scatter(e, base, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
 }
 
 }  // extern "C"
