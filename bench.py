@@ -206,8 +206,7 @@ def run_ours(args):
     deterministic = args.mode == "det"
 
     if world > 1:
-        from openequivariance_b200 import partition
-        result = partition.bench_partitioned(args, n_nodes * world, dev, rank, world)
+        result = bench_partitioned(args, n_nodes * world, dev, rank, world)
     else:
         result = bench_single(args, n_nodes, deterministic, dev)
 
@@ -384,6 +383,72 @@ def bench_e2e(args, conv, problem, X, Y, W, G, rows, cols, perm, dev, E):
     return {"value": E / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
             "ms_per_step": ms, "steps": steps,
             "note": "X, Y, W, G, rows, cols, perm copied from pinned host memory each step; dX and the scalar loss read back"}
+
+
+def bench_partitioned(args, n_nodes_total, dev, rank, world):
+    """Weak-scaling step of ``bench.py`` for N > 1: ``n_nodes_total`` = nodes per GPU x world, same density."""
+    import torch
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    from openequivariance_b200.core import problems as P
+    from openequivariance_b200.core.graph import periodic_radius_graph, spherical_harmonics
+    from openequivariance_b200.partition import PartitionedConv, build_plan
+
+    problem = P.mace_like_problem()
+    g = periodic_radius_graph(n_nodes_total, mean_degree=32.0, cutoff=5.0, seed=0, device=dev)
+    plan = build_plan(g["rows"], g["cols"], n_nodes_total, world, rank)
+    E_total = int(g["rows"].numel())
+    vec = g["vec"][plan.e0:plan.e1]
+    Y = spherical_harmonics(3, vec).float().contiguous()
+    del g, vec
+    torch.cuda.empty_cache()
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    E = plan.n_local_edges
+    W = torch.randn(E, problem.weight_numel, device=dev, generator=gen)
+    G = torch.randn(plan.n_owned, problem.irreps_out.dim, device=dev, generator=gen)
+    conv = oeq.TensorProductConv(problem, deterministic=True)
+    pc = PartitionedConv(conv, plan, dev)
+    pc.x_local[:plan.n_owned] = torch.randn(plan.n_owned, problem.irreps_in1.dim, device=dev, generator=gen)
+
+    def step():
+        pc.forward(None, Y, W)
+        return pc.backward(G)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(dev.index or 0)
+    launches0 = native.launch_count()
+    sampler.start()
+    ms = timed_region(step, args.steps, 0, dev, world)
+    clocks = sampler.stop()
+    launches = native.launch_count() - launches0
+    fwd_b, bwd_b = algorithmic_bytes(problem, plan.n_owned, E, True)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:  # noqa: BLE001
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = (fwd_b + bwd_b) / (ms * 1e-3) / 1e9
+    halo_bytes = plan.n_halo * problem.irreps_in1.dim * 4
+    return {
+        "metric": METRIC, "value": E_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "receiver-partitioned fused conv fwd+bwd (deterministic), MACE-like, x-slab per GPU",
+                   "nodes": n_nodes_total, "edges": E_total, "nodes_per_gpu": n_nodes_total // world,
+                   "halo_rows_rank0": plan.n_halo, "halo_bytes_rank0_per_direction": halo_bytes,
+                   "interior_receivers_rank0": plan.interior[1] - plan.interior[0],
+                   "l2_policy": "inputs larger than L2", "collective": "grouped NCCL send/recv of halo rows (forward, "
+                   "overlapped with interior receivers) and of halo gradients (backward)"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "rank 0: conv fwd+bwd step incl. halo exchange",
+                     "peak_kind": "measured" if "hbm_gbs" in peaks else "fallback"},
+        "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "skipped": "end-to-end staging from host memory is measured at N=1 only"},
+    }
 
 
 def main():
