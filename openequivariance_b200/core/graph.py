@@ -35,6 +35,14 @@ def sort_edges(rows, cols):
     return order, perm
 
 
+def transpose_permutation(rows, cols):
+    """For an edge list in ANY fixed order: positions of its edges listed in (col, row) order (stable)."""
+    if isinstance(rows, torch.Tensor):
+        n = int(max(int(rows.max()), int(cols.max())) + 1) if rows.numel() else 1
+        return torch.argsort(cols.to(torch.int64) * n + rows.to(torch.int64), stable=True)
+    return np.lexsort((rows, cols))
+
+
 class CoordGraph:
     """Adjacency of a point cloud, row-major sorted, with the permutation to column-major order.
 

@@ -31,7 +31,7 @@ from typing import Callable, List, Optional
 import torch
 import torch.distributed as dist
 
-from .core.graph import sort_edges
+from .core.graph import transpose_permutation
 
 
 def owner_range(n_nodes: int, world: int, rank: int):
@@ -103,7 +103,9 @@ def build_plan(rows: torch.Tensor, cols: torch.Tensor, n_nodes: int, world: int,
     owned = (c >= n0) & (c < n1)
     cols_local = torch.where(owned, c - n0, (n1 - n0) + torch.searchsorted(halo, c))
     rows_local = (rows[e0:e1] - n0).contiguous()
-    _, perm_local = sort_edges(rows_local, cols_local)
+    # the local list keeps the global (row, global col) order, which is not sorted by local col inside a row:
+    # take the sender-major permutation of the list as it stands
+    perm_local = transpose_permutation(rows_local, cols_local)
     # interior receivers: the longest middle run without any boundary receiver on either side of the split point
     n_owned = n1 - n0
     boundary_rows = torch.unique(rows_local[~owned])
