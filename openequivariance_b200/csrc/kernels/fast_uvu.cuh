@@ -96,13 +96,15 @@ OEQ_DEV void ldgsts_commit() { asm volatile("cp.async.commit_group;" ::: "memory
 template <int N> OEQ_DEV void ldgsts_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ---- shared-memory stage ----------------------------------------------------------------------------------
-constexpr int FAST_NCW = FU / 32;                         // consumer warps
+constexpr int FAST_GT = FU / FAST_CH;                      // threads per group: each carries FAST_CH channels
+constexpr int FAST_NT = FAST_NG * FAST_GT;                // consumer threads
+constexpr int FAST_NCW = FAST_NT / 32;                    // consumer warps
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
     float x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
     float w[WN];
-    float cy[NCY];
+    float cy[NCY];                   // folded coefficients cy[n] = C_n * y[j_n] of this edge
     float y[FAST_YPAD];
     float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
     long long edge, row, col;
@@ -118,8 +120,7 @@ struct __align__(16) FastShared {
 };
 static_assert(sizeof(FastShared) <= 232448, "stages exceed shared memory");
 constexpr int FAST_D = (FAST_S >= 5) ? 2 : 1;     // TMA look-ahead in edges (backward needs FAST_S >= FAST_D + 2)
-constexpr int FAST_XPC = L1_DIM / FU;             // registers per channel for an X / dX row
-constexpr int FAST_GPC = L3_DIM / FU;             // registers per channel for a Z / G row
+// FAST_XPC / FAST_GPC (problem header): registers per channel for an X / dX row and for a Z / G row
 
 // transposed butterfly: on return lane L (L < N) holds in v[0] the sum over all 32 lanes of element L
 template <int N>
@@ -163,6 +164,16 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
     const long long e0 = sh.range[0], n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
     IDX colv = 0, rowv = 0, rown = 0;
+    // this lane's share of the coefficient table stays in registers for the whole kernel
+    constexpr int CY_PER_LANE = (NCY + 31) / 32;
+    float tab_c[CY_PER_LANE];
+    int tab_j[CY_PER_LANE];
+#pragma unroll
+    for (int t = 0; t < CY_PER_LANE; ++t) {
+        const int q = lane + 32 * t;
+        tab_c[t] = (q < NCY) ? FAST_CYC[q] : 0.f;
+        tab_j[t] = (q < NCY) ? FAST_CYJ[q] : 0;
+    }
 
     auto phase_a = [&](long long ia) -> bool {   // claim a stage for edge ia and start its copies
         const int s = (int)(ia % FAST_S);
@@ -204,7 +215,14 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         // copies are committed one group per edge, FAST_D edges ahead; near the end of the range fewer are in flight
         if (i + FAST_D <= n) ldgsts_wait<FAST_D - 1>(); else ldgsts_wait<0>();
         __syncwarp();
-        for (int q = lane; q < NCY; q += 32) st.cy[q] = FAST_CYC[q] * st.y[FAST_CYJ[q]];
+#pragma unroll
+        for (int t = 0; t < CY_PER_LANE; ++t) {
+            const int q = lane + 32 * t;
+            if (q < NCY) {
+                const float v = tab_c[t] * st.y[tab_j[t]];
+                st.cy[q] = v;
+            }
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.full[(int)(i % FAST_S)]);
     };
@@ -240,62 +258,72 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
     ldgsts_wait<0>();
 }
 
-// ---- forward ----------------------------------------------------------------------------------------------
-template <int KIND>
-OEQ_DEV void fast_forward_body(const FastParams& p) {
-    extern __shared__ __align__(16) unsigned char fast_smem_raw[];
-    FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
-    const int tid = threadIdx.x, lane = tid & 31;
-    if (tid == 0) {
-        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FU); }
-        sh.abort_flag = 0;
-        cta_range<KIND, true>(p, sh.range);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (tid >= FU) { fast_producer<KIND, false>(p, sh, lane); return; }
 
-    const int u = tid;
+// ---- forward ----------------------------------------------------------------------------------------------
+// Consumer thread t: group t / FAST_GT, channels u + ch * FAST_GT (u = t % FAST_GT, ch < FAST_CH).  The folded
+// coefficients are the same for every channel, so a thread that carries two channels reads them from shared memory
+// once for both: that halves the load on the shared-memory pipe, which is what limits these kernels.  A group owns a
+// subset of the output blocks (forward) or of the input blocks (backward) and runs only the paths that touch its
+// blocks, which keeps the per-thread row registers at the single-channel level.
+template <int KIND, int GRP>
+OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int tid) {
+    const int u = tid % FAST_GT;   // channel ch of this thread is u + ch * FAST_GT
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
-    float acc[FAST_GPC];
+    float acc[FAST_CH * FAST_GPC];
 #pragma unroll
-    for (int k = 0; k < FAST_GPC; ++k) acc[k] = 0.f;
+    for (int k = 0; k < FAST_CH * FAST_GPC; ++k) acc[k] = 0.f;
     long long next_row = sh.range[2];
-
     auto zero_rows = [&](long long a, long long b) {   // receivers without edges
         for (long long r = a; r < b; ++r)
-            for (int q = u; q < L3_DIM; q += FU) p.Z[r * L3_DIM + q] = 0.f;
+            for (int q = tid; q < L3_DIM; q += FAST_NT) p.Z[r * L3_DIM + q] = 0.f;
     };
-
     for (long long i = 0; i < n; ++i) {
         const int s = (int)(i % FAST_S);
         FastStage& st = sh.st[s];
         if (!mbar_wait(&sh.full[s], (unsigned)((i / FAST_S) & 1), abortf, p.status, 21)) return;
         const long long row = st.row;
         const int last = st.last;
-        float xr[FAST_XPC];
+        float xr[FAST_CH * FAST_XPC];
         static_for<0, NB1>([&](auto bc) {
-            using B1 = Blk1<decltype(bc)::value>;
+            constexpr int B = decltype(bc)::value;
+            using B1 = Blk1<B>;
+            if constexpr ((GRP == 0 ? FP_FWD_NEEDS_X0[B] : FP_FWD_NEEDS_X1[B]) != 0) {
 #pragma unroll
-            for (int i1 = 0; i1 < B1::D; ++i1) xr[B1::OFF / FU + i1] = st.x[B1::OFF + u * B1::D + i1];
+                for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                    for (int i1 = 0; i1 < B1::D; ++i1)
+                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[B1::OFF + (u + ch * FAST_GT) * B1::D + i1];
+            }
         });
         const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
         static_for<0, NINS>([&](auto ic) {
-            using F = FIns<decltype(ic)::value>;
-            F::fwd(xr + F::XO, cy4, st.w[F::WOFF + u], acc + F::GO);
+            constexpr int I = decltype(ic)::value;
+            using F = FIns<I>;
+            if constexpr (FP_INS_GF[I] == GRP) {
+                float wv[FAST_CH];
+#pragma unroll
+                for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
+                F::fwd(xr + F::XO, cy4, wv, acc + F::GO);
+            }
         });
         mbar_arrive(&sh.empty[s]);
         if (last) {
             if (KIND == FAST_DET) { zero_rows(next_row, row); next_row = row + 1; }
             float* zrow = p.Z + row * L3_DIM;
             static_for<0, NB3>([&](auto oc) {
-                using B3 = Blk3<decltype(oc)::value>;
+                constexpr int O = decltype(oc)::value;
+                using B3 = Blk3<O>;
+                if constexpr (FP_Z_OWNER[O] == GRP) {
 #pragma unroll
-                for (int k = 0; k < B3::D; ++k) {
-                    float* dst = zrow + B3::OFF + u * B3::D + k;
-                    if (KIND == FAST_ATOMIC) atomicAdd(dst, acc[B3::OFF / FU + k]); else *dst = acc[B3::OFF / FU + k];
-                    acc[B3::OFF / FU + k] = 0.f;
+                    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                        for (int k = 0; k < B3::D; ++k) {
+                            float* dst = zrow + B3::OFF + (u + ch * FAST_GT) * B3::D + k;
+                            float& a = acc[ch * FAST_GPC + B3::OFF / FU + k];
+                            if (KIND == FAST_ATOMIC) atomicAdd(dst, a); else *dst = a;
+                            a = 0.f;
+                        }
                 }
             });
         }
@@ -303,27 +331,30 @@ OEQ_DEV void fast_forward_body(const FastParams& p) {
     if (KIND == FAST_DET) zero_rows(next_row, sh.range[3]);
 }
 
-// ---- backward ---------------------------------------------------------------------------------------------
 template <int KIND>
-OEQ_DEV void fast_backward_body(const FastParams& p) {
+OEQ_DEV void fast_forward_body(const FastParams& p) {
     extern __shared__ __align__(16) unsigned char fast_smem_raw[];
     FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FU); }
+        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); }
         sh.abort_flag = 0;
-        cta_range<KIND, false>(p, sh.range);
+        cta_range<KIND, true>(p, sh.range);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid >= FU) { fast_producer<KIND, true>(p, sh, lane); return; }
+    if (tid >= FAST_NT) { fast_producer<KIND, false>(p, sh, lane); return; }
+    if (FAST_NG == 1 || tid < FAST_GT) fast_forward_group<KIND, 0>(p, sh, tid); else fast_forward_group<KIND, 1>(p, sh, tid);
+}
 
-    const int u = tid;
+// ---- backward ---------------------------------------------------------------------------------------------
+template <int KIND, int GRP>
+OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int tid) {
+    const int u = tid % FAST_GT, lane = tid & 31, warp = tid >> 5;
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
-    float g[FAST_GPC];
+    float g[FAST_CH * FAST_GPC];
     long long cur_row = -1;
-
     for (long long i = 0; i < n; ++i) {
         const int s = (int)(i % FAST_S);
         FastStage& st = sh.st[s];
@@ -332,32 +363,58 @@ OEQ_DEV void fast_backward_body(const FastParams& p) {
         if (row != cur_row) {   // new receiver: its gradient row goes to registers for all of its edges
             const float* grow = p.G + row * L3_DIM;
             static_for<0, NB3>([&](auto oc) {
-                using B3 = Blk3<decltype(oc)::value>;
+                constexpr int O = decltype(oc)::value;
+                using B3 = Blk3<O>;
+                if constexpr ((GRP == 0 ? FP_BWD_NEEDS_G0[O] : FP_BWD_NEEDS_G1[O]) != 0) {
 #pragma unroll
-                for (int k = 0; k < B3::D; ++k) g[B3::OFF / FU + k] = __ldg(grow + B3::OFF + u * B3::D + k);
+                    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                        for (int k = 0; k < B3::D; ++k)
+                            g[ch * FAST_GPC + B3::OFF / FU + k] = __ldg(grow + B3::OFF + (u + ch * FAST_GT) * B3::D + k);
+                }
             });
             cur_row = row;
         }
-        float xr[FAST_XPC], dxr[FAST_XPC], dyr[FAST_NYP];
+        float xr[FAST_CH * FAST_XPC], dxr[FAST_CH * FAST_XPC], dyr[FAST_NYP];
         static_for<0, NB1>([&](auto bc) {
-            using B1 = Blk1<decltype(bc)::value>;
+            constexpr int B = decltype(bc)::value;
+            using B1 = Blk1<B>;
+            if constexpr (FP_X_OWNER[B] == GRP) {
 #pragma unroll
-            for (int i1 = 0; i1 < B1::D; ++i1) { xr[B1::OFF / FU + i1] = st.x[B1::OFF + u * B1::D + i1]; dxr[B1::OFF / FU + i1] = 0.f; }
+                for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                    for (int i1 = 0; i1 < B1::D; ++i1) {
+                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[B1::OFF + (u + ch * FAST_GT) * B1::D + i1];
+                        dxr[ch * FAST_XPC + B1::OFF / FU + i1] = 0.f;
+                    }
+            }
         });
 #pragma unroll
         for (int j = 0; j < FAST_NYP; ++j) dyr[j] = 0.f;
         const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
         float* dwrow = p.dW + e * WN;
         static_for<0, NINS>([&](auto ic) {
-            using F = FIns<decltype(ic)::value>;
-            float dw;
-            F::bwd(xr + F::XO, g + F::GO, cy4, st.w[F::WOFF + u], dxr + F::XO, dyr + F::Y0, dw);
-            dwrow[F::WOFF + u] = dw;
+            constexpr int I = decltype(ic)::value;
+            using F = FIns<I>;
+            if constexpr (FP_INS_GB[I] == GRP) {
+                float wv[FAST_CH], dw[FAST_CH];
+#pragma unroll
+                for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
+                F::bwd(xr + F::XO, g + F::GO, cy4, wv, dxr + F::XO, dyr + F::Y0, dw);
+#pragma unroll
+                for (int ch = 0; ch < FAST_CH; ++ch) dwrow[F::WOFF + u + ch * FAST_GT] = dw[ch];
+            }
         });
         static_for<0, NB1>([&](auto bc) {
-            using B1 = Blk1<decltype(bc)::value>;
+            constexpr int B = decltype(bc)::value;
+            using B1 = Blk1<B>;
+            if constexpr (FP_X_OWNER[B] == GRP) {
 #pragma unroll
-            for (int i1 = 0; i1 < B1::D; ++i1) st.x[B1::OFF + u * B1::D + i1] = dxr[B1::OFF / FU + i1];
+                for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                    for (int i1 = 0; i1 < B1::D; ++i1)
+                        st.x[B1::OFF + (u + ch * FAST_GT) * B1::D + i1] = dxr[ch * FAST_XPC + B1::OFF / FU + i1];
+            }
         });
         warp_reduce_transpose<FAST_NYP>(dyr, lane);
         if (lane < FAST_NYP) st.dyp[warp][lane] = dyr[0];
@@ -366,19 +423,35 @@ OEQ_DEV void fast_backward_body(const FastParams& p) {
     }
 }
 
+template <int KIND>
+OEQ_DEV void fast_backward_body(const FastParams& p) {
+    extern __shared__ __align__(16) unsigned char fast_smem_raw[];
+    FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); }
+        sh.abort_flag = 0;
+        cta_range<KIND, false>(p, sh.range);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid >= FAST_NT) { fast_producer<KIND, true>(p, sh, lane); return; }
+    if (FAST_NG == 1 || tid < FAST_GT) fast_backward_group<KIND, 0>(p, sh, tid); else fast_backward_group<KIND, 1>(p, sh, tid);
+}
+
 // ---- entry points (one per program: FAST_KERNEL selects which) ----------------------------------------------
 #if FAST_KERNEL == 0
-extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_fwd_tp(const FastParams p) { fast_forward_body<FAST_TP>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_fwd_tp(const FastParams p) { fast_forward_body<FAST_TP>(p); }
 #elif FAST_KERNEL == 1
-extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_fwd_det(const FastParams p) { fast_forward_body<FAST_DET>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_fwd_det(const FastParams p) { fast_forward_body<FAST_DET>(p); }
 #elif FAST_KERNEL == 2
-extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_fwd_atomic(const FastParams p) { fast_forward_body<FAST_ATOMIC>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_fwd_atomic(const FastParams p) { fast_forward_body<FAST_ATOMIC>(p); }
 #elif FAST_KERNEL == 3
-extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_bwd_tp(const FastParams p) { fast_backward_body<FAST_TP>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_bwd_tp(const FastParams p) { fast_backward_body<FAST_TP>(p); }
 #elif FAST_KERNEL == 4
-extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_bwd_det(const FastParams p) { fast_backward_body<FAST_DET>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_bwd_det(const FastParams p) { fast_backward_body<FAST_DET>(p); }
 #elif FAST_KERNEL == 5
-extern "C" __global__ void __launch_bounds__(FU + 32, FAST_CTAS) oeq_fast_bwd_atomic(const FastParams p) { fast_backward_body<FAST_ATOMIC>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_bwd_atomic(const FastParams p) { fast_backward_body<FAST_ATOMIC>(p); }
 #elif FAST_KERNEL == 6
 // Deterministic scatter of the per-edge dX rows: colptr[c] = first position k (in sender-major order) whose sender >= c
 extern "C" __global__ void oeq_fast_colptr(const IDX* cols, const IDX* perm, long long E, long long N, long long* colptr) {

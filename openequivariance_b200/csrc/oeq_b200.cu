@@ -39,6 +39,7 @@ thread_local std::string g_err;
 std::atomic<long long> g_launches{0};
 bool g_log = false;
 bool g_force_generic = false;
+bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
 std::string g_cache_dir;
 std::mutex g_mutex;
 
@@ -74,6 +75,8 @@ struct Desc {
     int fast_S = 0;      // shared-memory stages per CTA
     int fast_ctas = 0;   // resident CTAs per SM the stages are sized for
     int fast_ncy = 0;    // folded-coefficient slots per edge (each instruction padded to a multiple of 4)
+    int fast_ng = 1;     // thread groups sharing an edge
+    int fast_ch = 1;     // channels carried by one consumer thread
     size_t fast_smem = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
     size_t idx_bytes() const { return idx == 3 ? 4 : 8; }
@@ -153,9 +156,15 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
             int ncy = 0;
             for (auto& I : d.ins) ncy += ((int)I.nz.size() + 3) & ~3;
             const int nyp = d.dim[1] <= 1 ? 1 : d.dim[1] <= 2 ? 2 : d.dim[1] <= 4 ? 4 : d.dim[1] <= 8 ? 8 : d.dim[1] <= 16 ? 16 : 32;
-            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (U / 32) * nyp) + 40) + 15) & ~(size_t)15;
+            // Two channels per thread halve the shared-memory traffic of the coefficient loads; the row registers
+            // that doubles are won back by dealing the blocks to two thread groups.
+            const int ch = (!g_single_group && U % 64 == 0 && d.ins.size() >= 2) ? 2 : 1;
+            const int ng = ch == 2 ? 2 : 1;
+            const int nthreads = ng * U / ch;
+            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (nthreads / 32) * nyp) + 40) + 15) & ~(size_t)15;
             int ctas = 256 / U;
             ctas = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas);
+            while (ctas > 1 && ctas * (nthreads + 32) * (ch == 2 ? 168 : 128) > 65536) --ctas;   // registers per thread
             int S = 0;
             for (; ctas >= 1; ctas /= 2) {
                 const size_t budget = 232448 / ctas - 1024 - 256;
@@ -165,7 +174,7 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
             }
             if (S >= 3 && ctas >= 1) {
                 d.fast = true;
-                d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy;
+                d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
                 d.fast_smem = (size_t)S * (stage + 16) + 128;
             }
         }
@@ -243,12 +252,13 @@ std::string emit_header(const Desc& d) {
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
 // cy[n] = C_n * y[j_n] is formed once per edge by the producer warp; the consumer code below reads it as float4.
-std::string emit_fast(const Desc& d) {
+std::string emit_fast(const Desc& d, int ch, int ng) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
     s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << d.fast_S
-      << ", FAST_CTAS = " << d.fast_ctas << ";\n";
+      << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
+      << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
     std::ostringstream cyc, cyj;
     std::vector<int> cyoff;
     int off = 0;
@@ -274,42 +284,50 @@ std::string emit_fast(const Desc& d) {
         s << "template <> struct FIns<" << n << "> {\n";
         s << "  static constexpr int XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
           << ", CY4 = " << cyoff[n] / 4 << ", WOFF = " << I.woff << ", D1 = " << D1 << ", D3 = " << D3 << ";\n";
-        // ---- forward
-        s << "  static OEQ_DEV void fwd(const float* x, const float4* cy, const float w, float* acc) {\n";
+        // ---- forward: FAST_CH channels per thread share the coefficient loads
+        s << "  static OEQ_DEV void fwd(const float* x, const float4* cy, const float* w, float* acc) {\n";
         for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
+        s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
+        s << "      const float* xc = x + ch * FAST_XPC; float* ac = acc + ch * FAST_GPC; const float wc = w[ch];\n";
         if (D1 <= D3) {
-            for (int i = 0; i < D1; ++i) s << "    const float xs" << i << " = w * x[" << i << "];\n";
+            for (int i = 0; i < D1; ++i) s << "      const float xs" << i << " = wc * xc[" << i << "];\n";
             for (int z = 0; z < nnz; ++z)
-                s << "    acc[" << I.nz[z].k << "] = fmaf(" << C(z) << ", xs" << I.nz[z].i << ", acc[" << I.nz[z].k << "]);\n";
+                s << "      ac[" << I.nz[z].k << "] = fmaf(" << C(z) << ", xs" << I.nz[z].i << ", ac[" << I.nz[z].k << "]);\n";
         } else {
-            for (int k = 0; k < D3; ++k) s << "    float t" << k << " = 0.f;\n";
+            for (int k = 0; k < D3; ++k) s << "      float t" << k << " = 0.f;\n";
             for (int z = 0; z < nnz; ++z)
-                s << "    t" << I.nz[z].k << " = fmaf(" << C(z) << ", x[" << I.nz[z].i << "], t" << I.nz[z].k << ");\n";
-            for (int k = 0; k < D3; ++k) s << "    acc[" << k << "] = fmaf(w, t" << k << ", acc[" << k << "]);\n";
+                s << "      t" << I.nz[z].k << " = fmaf(" << C(z) << ", xc[" << I.nz[z].i << "], t" << I.nz[z].k << ");\n";
+            for (int k = 0; k < D3; ++k) s << "      ac[" << k << "] = fmaf(wc, t" << k << ", ac[" << k << "]);\n";
         }
-        s << "  }\n";
+        s << "    }\n  }\n";
         // ---- backward
-        s << "  static OEQ_DEV void bwd(const float* x, const float* g, const float4* cy, const float w, float* dx, float* dy, float& dw) {\n";
-        for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
-        for (int i = 0; i < D1; ++i) s << "    float s" << i << " = 0.f;\n";
-        for (int z = 0; z < nnz; ++z)
-            s << "    s" << I.nz[z].i << " = fmaf(" << C(z) << ", g[" << I.nz[z].k << "], s" << I.nz[z].i << ");\n";
-        s << "    float dwv = 0.f;\n";
-        for (int i = 0; i < D1; ++i) {
-            s << "    dwv = fmaf(x[" << i << "], s" << i << ", dwv);\n";
-            s << "    dx[" << i << "] = fmaf(w, s" << i << ", dx[" << i << "]);\n";
-        }
-        s << "    dw = dwv;\n";
         const bool scale_g = D3 <= D1;
-        if (scale_g) for (int k = 0; k < D3; ++k) s << "    const float q" << k << " = w * g[" << k << "];\n";
-        else for (int i = 0; i < D1; ++i) s << "    const float q" << i << " = w * x[" << i << "];\n";
+        const int nqv = scale_g ? D3 : D1;
+        s << "  static OEQ_DEV void bwd(const float* x, const float* g, const float4* cy, const float* w, float* dx, float* dy, float* dw) {\n";
+        for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
+        s << "    float qv[FAST_CH][" << nqv << "];\n";
+        s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
+        s << "      const float* xc = x + ch * FAST_XPC; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * FAST_XPC; const float wc = w[ch];\n";
+        for (int i = 0; i < D1; ++i) s << "      float s" << i << " = 0.f;\n";
+        for (int z = 0; z < nnz; ++z)
+            s << "      s" << I.nz[z].i << " = fmaf(" << C(z) << ", gc[" << I.nz[z].k << "], s" << I.nz[z].i << ");\n";
+        s << "      float dwv = 0.f;\n";
+        for (int i = 0; i < D1; ++i) {
+            s << "      dwv = fmaf(xc[" << i << "], s" << i << ", dwv);\n";
+            s << "      dxc[" << i << "] = fmaf(wc, s" << i << ", dxc[" << i << "]);\n";
+        }
+        s << "      dw[ch] = dwv;\n";
+        for (int t = 0; t < nqv; ++t) s << "      qv[ch][" << t << "] = wc * " << (scale_g ? "gc" : "xc") << "[" << t << "];\n";
+        s << "    }\n";
+        // dY: products are summed over the thread's channels before the fixed coefficients are applied
         std::vector<Nz> byik = I.nz;
         std::stable_sort(byik.begin(), byik.end(), [](const Nz& a, const Nz& b) { return a.i != b.i ? a.i < b.i : a.k < b.k; });
         for (size_t z = 0; z < byik.size();) {
             size_t m = z;
-            s << "    { const float pr = ";
-            if (scale_g) s << "x[" << byik[z].i << "] * q" << byik[z].k; else s << "q" << byik[z].i << " * g[" << byik[z].k << "]";
-            s << ";";
+            s << "    { float pr = 0.f;\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = fmaf(";
+            if (scale_g) s << "x[ch * FAST_XPC + " << byik[z].i << "], qv[ch][" << byik[z].k << "]";
+            else s << "qv[ch][" << byik[z].i << "], g[ch * FAST_GPC + " << byik[z].k << "]";
+            s << ", pr);\n     ";
             while (m < byik.size() && byik[m].i == byik[z].i && byik[m].k == byik[z].k) {
                 s << " dy[" << byik[m].j << "] = fmaf(" << hexf(byik[m].c) << "f, pr, dy[" << byik[m].j << "]);";
                 ++m;
@@ -318,6 +336,41 @@ std::string emit_fast(const Desc& d) {
             z = m;
         }
         s << "  }\n};\n";
+    }
+    // Thread groups: with FAST_NG = 2 two sets of FU threads share an edge.  Backward: input blocks are dealt to the
+    // groups (longest-processing-time first on CG nonzeros) so every dX block has one writer; forward: output blocks.
+    {
+        const int nb1 = (int)d.L[0].size(), nb3 = (int)d.L[2].size();
+        std::vector<long> cost1(nb1, 0), cost3(nb3, 0);
+        for (auto& I : d.ins) { cost1[I.a] += (long)I.nz.size() + 4; cost3[I.o] += (long)I.nz.size() + 4; }
+        auto deal = [ng](const std::vector<long>& cost) {
+            std::vector<int> order(cost.size()), grp(cost.size(), 0);
+            for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
+            std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost[a] > cost[b]; });
+            long load[2] = {0, 0};
+            for (int b : order) { const int g = (ng < 2 || load[0] <= load[1]) ? 0 : 1; grp[b] = g; load[g] += cost[b]; }
+            return grp;
+        };
+        const std::vector<int> g1 = deal(cost1), g3 = deal(cost3);
+        auto list = [&](const char* name, const std::vector<int>& v) {
+            s << "constexpr int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
+            for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
+            if (v.empty()) s << "0";
+            s << "};\n";
+        };
+        s << "constexpr int FAST_NG = " << ng << ";\n";
+        list("FP_X_OWNER", g1);   // backward: group that owns (reads X of, writes dX of) each input block
+        list("FP_Z_OWNER", g3);   // forward: group that owns (accumulates, writes) each output block
+        std::vector<int> needx0(nb1, 0), needx1(nb1, 0), needg0(nb3, 0), needg1(nb3, 0), gf, gb;
+        for (auto& I : d.ins) {
+            (g3[I.o] == 0 ? needx0 : needx1)[I.a] = 1;   // the instruction's forward group reads input block a
+            (g1[I.a] == 0 ? needg0 : needg1)[I.o] = 1;   // the instruction's backward group reads gradient block o
+            gf.push_back(g3[I.o]);
+            gb.push_back(g1[I.a]);
+        }
+        list("FP_FWD_NEEDS_X0", needx0); list("FP_FWD_NEEDS_X1", needx1);
+        list("FP_BWD_NEEDS_G0", needg0); list("FP_BWD_NEEDS_G1", needg1);
+        list("FP_INS_GF", gf); list("FP_INS_GB", gb);
     }
     return s.str();
 }
@@ -345,7 +398,11 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         src += K_COMMON;
         src += K_GENERIC;
     } else {
-        src += emit_fast(d);
+        // Forward kernels carry two channels per thread in two block-owning groups (their code is small enough to stay
+        // in the instruction cache); the backward kernels, three times larger, keep one channel per thread and one
+        // code stream, which measured faster than the split variants (those stalled on instruction fetch).
+        const bool fwd = fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC;
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1);
         src += "#define FAST_KERNEL " + std::to_string(fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;
         src += K_FAST_UVU;
@@ -629,7 +686,8 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     const long long work = p.E > 0 ? p.E : 1;
     if (grid > work) grid = work;
     void* args[] = {&p};
-    return launch(k, (unsigned)grid, (unsigned)(d.fast_U + 32), d.fast_smem, args, st);
+    const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
+    return launch(k, (unsigned)grid, consumers + 32, d.fast_smem, args, st);
 }
 
 // dX[c] = sum of the per-edge rows in scratch over the sender's edges, in sender-major list order
@@ -695,6 +753,7 @@ int oeqb_set_option(const char* name, const char* value) {
     if (n == "cache_dir") g_cache_dir = value;
     else if (n == "force_generic") g_force_generic = atoi(value) != 0;
     else if (n == "log") g_log = atoi(value) != 0;
+    else if (n == "single_group") g_single_group = atoi(value) != 0;
     else return fail(OEQB_EINVAL, "unknown option '%s'", name);
     return OEQB_OK;
 }
