@@ -44,6 +44,9 @@ def parse_args():
     ap.add_argument("--cpu-sample-edges", type=int, default=16000)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="conv", choices=["conv", "tp_uvu", "tp_uvw", "tp_uvw64", "tp_readme"],
+                    help="conv = headline fused convolution; tp_* = batched tensor-product configurations (secondary lines)")
+    ap.add_argument("--batch", type=int, default=0)
     return ap.parse_args()
 
 
@@ -451,8 +454,86 @@ def bench_partitioned(args, n_nodes_total, dev, rank, world):
     }
 
 
+def bench_tp(args):
+    """Secondary lines: batched tensor product, forward / backward / double backward, in items/s per pass."""
+    import numpy as np
+    import torch
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    from openequivariance_b200.core import problems as P
+    from openequivariance_b200.core.graph import spherical_harmonics
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.workload == "tp_uvu":
+        problem, B, lmax, dt = P.mace_like_problem(), args.batch or 200000, 3, torch.float32
+    elif args.workload == "tp_uvw":
+        problem, B, lmax, dt = P.nequip_like_problem(), args.batch or 50000, 2, torch.float32
+    elif args.workload == "tp_uvw64":
+        problem, B, lmax, dt = P.nequip_like_problem(np.float64), args.batch or 50000, 2, torch.float64
+    else:
+        problem, B, lmax, dt = P.readme_problem(), args.batch or 1000, None, torch.float32
+    gen = torch.Generator(device=dev).manual_seed(0)
+    L1, L2, L3, wn = problem.irreps_in1.dim, problem.irreps_in2.dim, problem.irreps_out.dim, problem.weight_numel
+    if lmax is None:
+        x, y = torch.rand(B, L1, device=dev, generator=gen), torch.rand(B, L2, device=dev, generator=gen)
+        w = torch.rand(B, wn, device=dev, generator=gen)
+    else:
+        x = torch.randn(B, L1, device=dev, generator=gen, dtype=dt)
+        v = torch.randn(B, 3, device=dev, generator=gen, dtype=torch.float64)
+        y = spherical_harmonics(lmax, v).to(dt).contiguous()
+        if problem.shared_weights:
+            w = torch.randn(wn, device=dev, generator=gen, dtype=dt) / (32.0 * 5) ** 0.5
+        else:
+            w = torch.randn(B, wn, device=dev, generator=gen, dtype=dt)
+    g = torch.randn(B, L3, device=dev, generator=gen, dtype=dt)
+    x2, y2, w2 = torch.randn_like(x), torch.randn_like(y), torch.randn_like(w)
+    tp = oeq.TensorProduct(problem)
+    ops = torch.ops.libtorch_tp_jit
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # written between iterations: larger than L2
+    item = 8 if dt == torch.float64 else 4
+    wb = 0 if problem.shared_weights else wn
+    bytes_per = {"forward": (L1 + L2 + L3 + wb) * item, "backward": (2 * L1 + 2 * L2 + L3 + 2 * wb) * item,
+                 "double_backward": (3 * L1 + 3 * L2 + 3 * wb + 2 * L3) * item}
+    calls = {"forward": lambda: ops.jit_tp_forward(tp.kernel, tp.hash, x, y, w, L3),
+             "backward": lambda: ops.jit_tp_backward(tp.kernel, tp.hash, x, y, w, g),
+             "double_backward": lambda: ops.jit_tp_double_backward(tp.kernel, tp.hash, x, y, w, g, x2, y2, w2)}
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:  # noqa: BLE001
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    out = {}
+    launches0 = native.launch_count()
+    for name, fn in calls.items():
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        times = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize(dev)
+            times.append(a.elapsed_time(b))
+        ms = statistics.median(times)
+        gbs = B * bytes_per[name] / ms / 1e6
+        out[name] = {"ms": ms, "items_per_s": B / (ms * 1e-3), "algorithmic_gbs": gbs, "hbm_frac": gbs / peak}
+    line = {"metric": "tp_items_per_s", "value": out["forward"]["items_per_s"], "unit": "items/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": out["forward"]["ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64" if dt == torch.float64 else "f32",
+            "data": "synthetic", "config": {"workload": args.workload, "batch": B, "l2_policy": "256 MB buffer written between iterations"},
+            "passes": out, "gpu_launches": native.launch_count() - launches0,
+            "fast_path": int(native.query(tp.kernel_string.encode(), tp.hash).fast_path)}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.workload != "conv" and args.impl != "reference":
+        return bench_tp(args)
     if args.impl == "reference":
         run_reference_arm(args)
     else:

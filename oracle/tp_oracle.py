@@ -23,10 +23,15 @@ is not installed here and cannot be, so this file restates its published algorit
 Gradients of every order come from torch autograd on these einsums, which is how the reference's
 harness obtains e3nn's (``_torch/NPDoubleBackwardMixin.py:17-137``).
 
-Pinning status: the Wigner-3j tensors and path weights are pinned entry-by-entry against the
-reference's own generator (tests/golden/).  The reference holds no golden vectors for the contraction
-itself (its tests call live e3nn), so for that part: PARITY UNPINNED; O(3)-equivariance and
-gradcheck tests stand in.
+Pinning status: PINNED.  (1) The Wigner-3j tensors, path weights, instruction tables and e3nn->kernel weight
+permutations are pinned entry-by-entry against the reference's own generator (tests/golden/wigner_3j.npz,
+problems.json, coord_graph.json; made by tests/golden/make_golden.py).  (2) The contraction itself -- forward and
+backward of five tensor-product problems (uvu / uvw, unshared / shared weights, two with a non-trivial weight
+re-tiling) and of an atomic and a deterministic convolution -- is pinned against outputs of the unmodified reference
+run on a B200 through its own JIT CUDA kernels (tests/golden/reference_gpu.npz, made by
+tests/golden/make_reference_gpu_golden.py; checked in tests/test_reference_gpu_golden.py to 2e-6 relative L2, the
+fp32 rounding of those kernels).  The reference holds no stored golden vectors of its own (its tests call live e3nn,
+which is not installable here); O(3)-equivariance and third-order autograd checks complement the pins.
 """
 
 from __future__ import annotations
