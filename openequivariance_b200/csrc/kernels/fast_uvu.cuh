@@ -34,6 +34,9 @@ struct FastParams {
     const IDX* rows; const IDX* cols;
     long long N; long long E;
     int* status;
+    const float* Wdx;   // second-order backward: weights that scale dX (W scales the dY products)
+    int accum;          // add to the outputs instead of overwriting them
+    int pad;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
@@ -104,6 +107,7 @@ constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
     float x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
     float w[WN];
+    float w2[FAST_DBL ? WN : 4];     // second-order backward only: the row of Wdx
     float cy[NCY];                   // folded coefficients cy[n] = C_n * y[j_n] of this edge
     float y[FAST_YPAD];
     float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
@@ -202,9 +206,10 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
             st.edge = e; st.row = row; st.col = col;
             st.first = (ia == 0) || (KIND == FAST_TP);   // consumers also compare rows; see fast_backward
             st.last = (ia == n - 1) || (row != nxt) || (KIND == FAST_TP);
-            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN) * sizeof(float)));
+            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN * (FAST_DBL ? 2 : 1)) * sizeof(float)));
             tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
             tma_load(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s]);
+            if (FAST_DBL) tma_load(st.w2, p.Wdx + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s]);
         }
         for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y[j], p.Y + e * L2_DIM + j);
         ldgsts_commit();
@@ -234,12 +239,15 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
             float tot = 0.f;
 #pragma unroll
             for (int w = 0; w < FAST_NCW; ++w) tot += st.dyp[w][lane];
-            p.dY[st.edge * L2_DIM + lane] = tot;
+            float* dst = p.dY + st.edge * L2_DIM + lane;
+            *dst = p.accum ? *dst + tot : tot;
         }
         if (lane == 0) {
-            if (KIND == FAST_TP) tma_store(p.dX + st.edge * L1_DIM, st.x, (unsigned)(L1_DIM * sizeof(float)));
-            else if (KIND == FAST_DET) tma_store(p.scratch + st.edge * L1_DIM, st.x, (unsigned)(L1_DIM * sizeof(float)));
-            else tma_reduce_add(p.dX + st.col * L1_DIM, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            // each per-edge row has a single writer, so adding to it (second pass of a double backward) stays deterministic
+            float* row = (KIND == FAST_TP) ? p.dX + st.edge * L1_DIM : (KIND == FAST_DET) ? p.scratch + st.edge * L1_DIM
+                                                                                        : p.dX + st.col * L1_DIM;
+            if (KIND == FAST_ATOMIC || p.accum) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            else tma_store(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
         }
         tma_commit();
         return true;
@@ -309,7 +317,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
         });
         mbar_arrive(&sh.empty[s]);
         if (last) {
-            if (KIND == FAST_DET) { zero_rows(next_row, row); next_row = row + 1; }
+            if (KIND == FAST_DET && !p.accum) { zero_rows(next_row, row); next_row = row + 1; }
             float* zrow = p.Z + row * L3_DIM;
             static_for<0, NB3>([&](auto oc) {
                 constexpr int O = decltype(oc)::value;
@@ -321,14 +329,14 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                         for (int k = 0; k < B3::D; ++k) {
                             float* dst = zrow + B3::OFF + (u + ch * FAST_GT) * B3::D + k;
                             float& a = acc[ch * FAST_GPC + B3::OFF / FU + k];
-                            if (KIND == FAST_ATOMIC) atomicAdd(dst, a); else *dst = a;
+                            if (KIND == FAST_ATOMIC) atomicAdd(dst, a); else *dst = p.accum ? *dst + a : a;
                             a = 0.f;
                         }
                 }
             });
         }
     }
-    if (KIND == FAST_DET) zero_rows(next_row, sh.range[3]);
+    if (KIND == FAST_DET && !p.accum) zero_rows(next_row, sh.range[3]);
 }
 
 template <int KIND>
@@ -397,12 +405,18 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
             constexpr int I = decltype(ic)::value;
             using F = FIns<I>;
             if constexpr (FP_INS_GB[I] == GRP) {
-                float wv[FAST_CH], dw[FAST_CH];
+                float wv[FAST_CH], wx[FAST_CH], dw[FAST_CH];
 #pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
-                F::bwd(xr + F::XO, g + F::GO, cy4, wv, dxr + F::XO, dyr + F::Y0, dw);
+                for (int ch = 0; ch < FAST_CH; ++ch) {
+                    wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
+                    wx[ch] = FAST_DBL ? st.w2[F::WOFF + u + ch * FAST_GT] : wv[ch];
+                }
+                F::bwd(xr + F::XO, g + F::GO, cy4, wv, wx, dxr + F::XO, dyr + F::Y0, dw);
 #pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch) dwrow[F::WOFF + u + ch * FAST_GT] = dw[ch];
+                for (int ch = 0; ch < FAST_CH; ++ch) {
+                    float* dst = dwrow + F::WOFF + u + ch * FAST_GT;
+                    *dst = p.accum ? *dst + dw[ch] : dw[ch];
+                }
             }
         });
         static_for<0, NB1>([&](auto bc) {

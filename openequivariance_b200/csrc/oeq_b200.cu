@@ -78,6 +78,8 @@ struct Desc {
     int fast_ng = 1;     // thread groups sharing an edge
     int fast_ch = 1;     // channels carried by one consumer thread
     size_t fast_smem = 0;
+    int fast_S2 = 0;         // stages of the second-order backward kernels (their stage carries a second weight row)
+    size_t fast_smem2 = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
     size_t idx_bytes() const { return idx == 3 ? 4 : 8; }
 };
@@ -161,7 +163,7 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
             const int ch = (!g_single_group && U % 64 == 0 && d.ins.size() >= 2) ? 2 : 1;
             const int ng = ch == 2 ? 2 : 1;
             const int nthreads = ng * U / ch;
-            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (nthreads / 32) * nyp) + 40) + 15) & ~(size_t)15;
+            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (nthreads / 32) * nyp) + 56) + 15) & ~(size_t)15;
             int ctas = 256 / U;
             ctas = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas);
             while (ctas > 1 && ctas * (nthreads + 32) * (ch == 2 ? 168 : 128) > 65536) --ctas;   // registers per thread
@@ -176,6 +178,11 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 d.fast = true;
                 d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
                 d.fast_smem = (size_t)S * (stage + 16) + 128;
+                const size_t stage2 = stage + 4 * (size_t)d.wn;
+                int S2 = (int)((232448 / ctas - 1024 - 256) / (stage2 + 16));
+                if (S2 > 6) S2 = 6;
+                d.fast_S2 = S2;    // < 3: second-order passes fall back to the general kernels
+                d.fast_smem2 = (size_t)S2 * (stage2 + 16) + 128;
             }
         }
     }
@@ -252,11 +259,12 @@ std::string emit_header(const Desc& d) {
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
 // cy[n] = C_n * y[j_n] is formed once per edge by the producer warp; the consumer code below reads it as float4.
-std::string emit_fast(const Desc& d, int ch, int ng) {
+std::string emit_fast(const Desc& d, int ch, int ng, bool dbl) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
-    s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << d.fast_S
+    s << "#define FAST_DBL " << (dbl ? 1 : 0) << "\n";
+    s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << (dbl ? d.fast_S2 : d.fast_S)
       << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
     std::ostringstream cyc, cyj;
@@ -303,18 +311,18 @@ std::string emit_fast(const Desc& d, int ch, int ng) {
         // ---- backward
         const bool scale_g = D3 <= D1;
         const int nqv = scale_g ? D3 : D1;
-        s << "  static OEQ_DEV void bwd(const float* x, const float* g, const float4* cy, const float* w, float* dx, float* dy, float* dw) {\n";
+        s << "  static OEQ_DEV void bwd(const float* x, const float* g, const float4* cy, const float* w, const float* wdx, float* dx, float* dy, float* dw) {\n";
         for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
         s << "    float qv[FAST_CH][" << nqv << "];\n";
         s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-        s << "      const float* xc = x + ch * FAST_XPC; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * FAST_XPC; const float wc = w[ch];\n";
+        s << "      const float* xc = x + ch * FAST_XPC; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * FAST_XPC; const float wc = w[ch]; const float wx = wdx[ch];\n";
         for (int i = 0; i < D1; ++i) s << "      float s" << i << " = 0.f;\n";
         for (int z = 0; z < nnz; ++z)
             s << "      s" << I.nz[z].i << " = fmaf(" << C(z) << ", gc[" << I.nz[z].k << "], s" << I.nz[z].i << ");\n";
         s << "      float dwv = 0.f;\n";
         for (int i = 0; i < D1; ++i) {
             s << "      dwv = fmaf(xc[" << i << "], s" << i << ", dwv);\n";
-            s << "      dxc[" << i << "] = fmaf(wc, s" << i << ", dxc[" << i << "]);\n";
+            s << "      dxc[" << i << "] = fmaf(wx, s" << i << ", dxc[" << i << "]);\n";
         }
         s << "      dw[ch] = dwv;\n";
         for (int t = 0; t < nqv; ++t) s << "      qv[ch][" << t << "] = wc * " << (scale_g ? "gc" : "xc") << "[" << t << "];\n";
@@ -380,10 +388,12 @@ enum Family {
     FAM_GENERIC = 0,
     FAM_FAST_FWD_TP, FAM_FAST_FWD_DET, FAM_FAST_FWD_ATOMIC, FAM_FAST_BWD_TP, FAM_FAST_BWD_DET, FAM_FAST_BWD_ATOMIC,
     FAM_FAST_SCATTER,
+    FAM_FAST_BWD2_TP, FAM_FAST_BWD2_DET, FAM_FAST_BWD2_ATOMIC,   // second-order variants of the backward kernels
     FAM_COUNT
 };
 const char* const kFamilyNames[FAM_COUNT] = {"generic", "fast_fwd_tp", "fast_fwd_det", "fast_fwd_atomic", "fast_bwd_tp",
-                                             "fast_bwd_det", "fast_bwd_atomic", "fast_scatter"};
+                                             "fast_bwd_det", "fast_bwd_atomic", "fast_scatter", "fast_bwd2_tp",
+                                             "fast_bwd2_det", "fast_bwd2_atomic"};
 const char* family_name(int f) { return (f >= 0 && f < FAM_COUNT) ? kFamilyNames[f] : "?"; }
 int family_from_name(const std::string& n) {
     for (int f = 0; f < FAM_COUNT; ++f)
@@ -402,8 +412,10 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         // in the instruction cache); the backward kernels, three times larger, keep one channel per thread and one
         // code stream, which measured faster than the split variants (those stalled on instruction fetch).
         const bool fwd = fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC;
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1);
-        src += "#define FAST_KERNEL " + std::to_string(fam - FAM_FAST_FWD_TP) + "\n";
+        const bool dbl = fam >= FAM_FAST_BWD2_TP;
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl);
+        // the second-order variants reuse the backward entry points (kernel ids 3..5)
+        src += "#define FAST_KERNEL " + std::to_string(dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;
         src += K_FAST_UVU;
     }
@@ -631,6 +643,9 @@ struct FastParams {
     const void* rows; const void* cols;
     long long N; long long E;
     int* status;
+    const void* Wdx;   // second-order backward: weights that scale dX (W itself scales the dY products)
+    int accum;         // add to the outputs instead of overwriting them
+    int pad;
 };
 
 // One host-mapped status word per device: kernels store a non-zero code when a bounded wait runs out.
@@ -671,7 +686,7 @@ constexpr size_t kAlign = 256;
 size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 // kernel: 0 fwd_tp, 1 fwd_det, 2 fwd_atomic, 3 bwd_tp, 4 bwd_det, 5 bwd_atomic
-int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status_override = nullptr) {
+int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status_override = nullptr, bool dbl = false) {
     static const char* names[6] = {"oeq_fast_fwd_tp", "oeq_fast_fwd_det", "oeq_fast_fwd_atomic",
                                    "oeq_fast_bwd_tp", "oeq_fast_bwd_det", "oeq_fast_bwd_atomic"};
     const Desc& d = e->d;
@@ -679,15 +694,16 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (status_override) p.status = status_override;
     else if ((rc = status_word(&p.status))) return rc;
     Program* prog;
-    if ((rc = get_program(e, FAM_FAST_FWD_TP + kernel, &prog))) return rc;
+    const size_t smem = dbl ? d.fast_smem2 : d.fast_smem;
+    if ((rc = get_program(e, dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel, &prog))) return rc;
     cudaKernel_t k;
-    if ((rc = get_kernel(prog, names[kernel], d.fast_smem, &k))) return rc;
+    if ((rc = get_kernel(prog, names[kernel], smem, &k))) return rc;
     long long grid = (long long)sm_count() * d.fast_ctas;
     const long long work = p.E > 0 ? p.E : 1;
     if (grid > work) grid = work;
     void* args[] = {&p};
     const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
-    return launch(k, (unsigned)grid, consumers + 32, d.fast_smem, args, st);
+    return launch(k, (unsigned)grid, consumers + 32, smem, args, st);
 }
 
 // dX[c] = sum of the per-edge rows in scratch over the sender's edges, in sender-major list order
@@ -801,6 +817,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     int done = 0;
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
         if (fam != FAM_GENERIC && !d.fast) continue;
+        if (fam >= FAM_FAST_BWD2_TP && d.fast_S2 < 3) continue;
         std::string cubin;
         int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
         if (rc) return -rc;
@@ -857,9 +874,24 @@ int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int6
     const Desc& d = e->d;
     if (d.shared) CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st));
     if (batch == 0) return OEQB_OK;
+    int rc;
+    if (use_fast(d) && d.fast_S2 >= 3 && aligned16({x, x2, W, W2, dx})) {
+        // same decomposition on the channel-parallel kernels: three forward passes (store, add, add) and two
+        // second-order backward passes (the second adds); see the general path below for the algebra
+        FastParams f{x2, y, W, nullptr, dg, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
+        if ((rc = fast_launch(e, 0, f, st))) return rc;
+        f.X = x; f.Y = y2; f.accum = 1;
+        if ((rc = fast_launch(e, 0, f, st))) return rc;
+        f.Y = y; f.W = W2;
+        if ((rc = fast_launch(e, 0, f, st))) return rc;
+        FastParams b{x2, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
+        b.Wdx = W2;
+        if ((rc = fast_launch(e, 3, b, st, nullptr, true))) return rc;
+        b.X = x; b.Y = y2; b.W = W2; b.Wdx = W; b.accum = 1;
+        return fast_launch(e, 3, b, st, nullptr, true);
+    }
     CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
     // dg = F(x2, y, W) + F(x, y2, W) + F(x, y, W2): the product is linear in each argument
-    int rc;
     FwdParams f{x2, y, W, dg, nullptr, nullptr, batch, batch, UNIT_ITEM, OUT_STORE};
     if ((rc = generic_forward(e, f, st))) return rc;
     f.x = x; f.y = y2; f.out_mode = OUT_ADD;
@@ -882,7 +914,7 @@ int64_t oeqb_conv_workspace_bytes(const void* desc, size_t desc_len, int64_t key
     if (int rc = get_entry(desc, desc_len, key, &e)) return -(int64_t)rc;
     const Desc& d = e->d;
     // Deterministic backward on the channel-parallel path: one dX row per edge plus the sender offsets.
-    if (direction == 1 && d.conv && d.det && use_fast(d))
+    if ((direction == 1 || (direction == 2 && d.fast_S2 >= 3)) && d.conv && d.det && use_fast(d))
         return (int64_t)(round_up((size_t)n_edges * d.dim[0] * d.elt()) + round_up((size_t)(n_nodes + 1) * 8));
     return 0;
 }
@@ -973,7 +1005,6 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
                               const void* Y2, const void* W2, void* dX, void* dY, void* dW, void* dG,
                               const void* rows, const void* cols, const void* transpose_perm, void* workspace,
                               int64_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
@@ -985,9 +1016,38 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
     if (int rc = check_ptrs({X, G, X2, dX, dG}, "oeqb_conv_double_backward")) return rc;
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
-        CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
     }
     int rc;
+    if (use_fast(d) && d.fast_S2 >= 3 && n_edges > 0 && aligned16({X, X2, W, W2, dX, workspace})) {
+        // channel-parallel kernels: dG from three forward passes, (dX, dY, dW) from two second-order backward passes
+        const int kf = d.det ? 1 : 2, kb = d.det ? 4 : 5;
+        void* colptr = nullptr;
+        if (d.det) {
+            const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
+            const size_t need = scratch_bytes + round_up((size_t)(n_nodes + 1) * 8);
+            if (!workspace || workspace_bytes < (int64_t)need)
+                return fail(OEQB_EINVAL, "oeqb_conv_double_backward: workspace of %lld bytes is smaller than the %zu required",
+                            (long long)workspace_bytes, need);
+            colptr = (char*)workspace + scratch_bytes;
+        } else {
+            CUDA_TRY(cudaMemsetAsync(dG, 0, n_nodes * d.dim[2] * d.elt(), st));
+            CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
+        }
+        FastParams f{X2, Y, W, nullptr, dG, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+        if ((rc = fast_launch(e, kf, f, st))) return rc;
+        f.X = X; f.Y = Y2; f.accum = 1;
+        if ((rc = fast_launch(e, kf, f, st))) return rc;
+        f.Y = Y; f.W = W2;
+        if ((rc = fast_launch(e, kf, f, st))) return rc;
+        FastParams b{X2, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
+        b.Wdx = W2;
+        if ((rc = fast_launch(e, kb, b, st, nullptr, true))) return rc;
+        b.X = X; b.Y = Y2; b.W = W2; b.Wdx = W; b.accum = 1;
+        if ((rc = fast_launch(e, kb, b, st, nullptr, true))) return rc;
+        if (d.det) return fast_scatter(e, workspace, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
+        return OEQB_OK;
+    }
+    if (n_edges > 0) CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
     if (d.det) {
         FwdParams f{X2, Y, W, dG, rows, cols, n_nodes, n_edges, UNIT_SEGMENT, OUT_STORE};
         if ((rc = generic_forward(e, f, st))) return rc;

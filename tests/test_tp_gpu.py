@@ -58,7 +58,7 @@ def test_tp_backward(name, problem, dt):
         assert rel_l2(got, ref) <= REL_L2[dt], what
 
 
-@pytest.mark.parametrize("name,problem,dt", [c for c in _cases() if c.values[0] not in ("mace_like",)])
+@pytest.mark.parametrize("name,problem,dt", list(_cases()))
 def test_tp_double_backward(name, problem, dt):
     p = with_dtype(problem, dt)
     tp = _module(p)
