@@ -114,10 +114,13 @@ struct __align__(16) FastStage {
     long long edge, row, col;
     int first, last, pad0, pad1;
 };
+constexpr int FAST_ZBUF = (FAST_KERNEL == 2) ? L3_DIM : 4;   // atomic forward stages a receiver row for a bulk reduce
 struct __align__(16) FastShared {
     FastStage st[FAST_S];
+    float zbuf[FAST_ZBUF];
     unsigned long long full[FAST_S];
     unsigned long long empty[FAST_S];
+    unsigned long long zfull, zfree;
     long long range[4];              // e0, e1, n0, n1
     int abort_flag;
     int pad[3];
@@ -282,6 +285,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
 #pragma unroll
     for (int k = 0; k < FAST_CH * FAST_GPC; ++k) acc[k] = 0.f;
     long long next_row = sh.range[2];
+    long long nseg = 0;                                // receiver rows this CTA has handed to the bulk reduce
     auto zero_rows = [&](long long a, long long b) {   // receivers without edges
         for (long long r = a; r < b; ++r)
             for (int q = tid; q < L3_DIM; q += FAST_NT) p.Z[r * L3_DIM + q] = 0.f;
@@ -301,7 +305,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                 for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                     for (int i1 = 0; i1 < B1::D; ++i1)
-                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[B1::OFF + (u + ch * FAST_GT) * B1::D + i1];
+                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
             }
         });
         const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
@@ -316,7 +320,36 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
             }
         });
         mbar_arrive(&sh.empty[s]);
-        if (last) {
+        if (last && KIND == FAST_ATOMIC) {
+            // The row is added to Z[row] by one bulk reduce (cp.reduce.async.bulk) out of shared memory: far fewer
+            // L2 atomic transactions than one red per element.  zfree/zfull hand the staging row back and forth
+            // between the consumer threads and the thread that issues the copy.
+            if (nseg > 0 && !mbar_wait(&sh.zfree, (unsigned)((nseg - 1) & 1), abortf, p.status, 23)) return;
+            static_for<0, NB3>([&](auto oc) {
+                constexpr int O = decltype(oc)::value;
+                using B3 = Blk3<O>;
+                if constexpr (FP_Z_OWNER[O] == GRP) {
+#pragma unroll
+                    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                        for (int k = 0; k < B3::D; ++k) {
+                            float& a = acc[ch * FAST_GPC + B3::OFF / FU + k];
+                            sh.zbuf[feat_idx<B3::OFF, B3::MUL, B3::D>(u + ch * FAST_GT, k)] = a;
+                            a = 0.f;
+                        }
+                }
+            });
+            fence_async_smem();
+            mbar_arrive(&sh.zfull);
+            if (tid == 0) {
+                if (!mbar_wait(&sh.zfull, (unsigned)(nseg & 1), abortf, p.status, 24)) return;
+                tma_reduce_add(p.Z + row * L3_DIM, sh.zbuf, (unsigned)(L3_DIM * sizeof(float)));
+                tma_commit();
+                tma_wait_read<0>();
+                mbar_arrive(&sh.zfree);
+            }
+            ++nseg;
+        } else if (last) {
             if (KIND == FAST_DET && !p.accum) { zero_rows(next_row, row); next_row = row + 1; }
             float* zrow = p.Z + row * L3_DIM;
             static_for<0, NB3>([&](auto oc) {
@@ -327,7 +360,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                         for (int k = 0; k < B3::D; ++k) {
-                            float* dst = zrow + B3::OFF + (u + ch * FAST_GT) * B3::D + k;
+                            float* dst = zrow + feat_idx<B3::OFF, B3::MUL, B3::D>(u + ch * FAST_GT, k);
                             float& a = acc[ch * FAST_GPC + B3::OFF / FU + k];
                             if (KIND == FAST_ATOMIC) atomicAdd(dst, a); else *dst = p.accum ? *dst + a : a;
                             a = 0.f;
@@ -337,6 +370,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
         }
     }
     if (KIND == FAST_DET && !p.accum) zero_rows(next_row, sh.range[3]);
+    if (KIND == FAST_ATOMIC && tid == 0) tma_wait_all<0>();
 }
 
 template <int KIND>
@@ -346,6 +380,8 @@ OEQ_DEV void fast_forward_body(const FastParams& p) {
     const int tid = threadIdx.x, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); }
+        mbar_init(&sh.zfull, FAST_NT);
+        mbar_init(&sh.zfree, 1);
         sh.abort_flag = 0;
         cta_range<KIND, true>(p, sh.range);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -378,7 +414,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                         for (int k = 0; k < B3::D; ++k)
-                            g[ch * FAST_GPC + B3::OFF / FU + k] = __ldg(grow + B3::OFF + (u + ch * FAST_GT) * B3::D + k);
+                            g[ch * FAST_GPC + B3::OFF / FU + k] = __ldg(grow + feat_idx<B3::OFF, B3::MUL, B3::D>(u + ch * FAST_GT, k));
                 }
             });
             cur_row = row;
@@ -392,7 +428,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                 for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                     for (int i1 = 0; i1 < B1::D; ++i1) {
-                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[B1::OFF + (u + ch * FAST_GT) * B1::D + i1];
+                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
                         dxr[ch * FAST_XPC + B1::OFF / FU + i1] = 0.f;
                     }
             }
@@ -427,7 +463,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                 for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                     for (int i1 = 0; i1 < B1::D; ++i1)
-                        st.x[B1::OFF + (u + ch * FAST_GT) * B1::D + i1] = dxr[ch * FAST_XPC + B1::OFF / FU + i1];
+                        st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)] = dxr[ch * FAST_XPC + B1::OFF / FU + i1];
             }
         });
         warp_reduce_transpose<FAST_NYP>(dyr, lane);

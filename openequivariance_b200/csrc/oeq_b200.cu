@@ -80,6 +80,8 @@ struct Desc {
     size_t fast_smem = 0;
     int fast_S2 = 0;         // stages of the second-order backward kernels (their stage carries a second weight row)
     size_t fast_smem2 = 0;
+    int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
+    size_t fast_smem3 = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
     size_t idx_bytes() const { return idx == 3 ? 4 : 8; }
 };
@@ -143,10 +145,10 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     if (d.layout == 1 && d.uvw) return bad("ir_mul layout with uvw");
     if (d.dim[0] * 1LL > (1LL << 24) || d.dim[2] > (1LL << 24) || d.wn > (1LL << 30)) return bad("problem too large");
 
-    // Fast path: fp32, mul_ir, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
+    // Fast path: fp32, either layout, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
     // that is a multiple of 32, l <= 4 everywhere, no Kahan, rows small enough to live in registers.
     d.fast = false;
-    if (d.dtype == 1 && d.layout == 0 && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
+    if (d.dtype == 1 && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
         bool ok = true;
         int U = d.L[0][0].mul;
         for (auto& b : d.L[0]) ok = ok && b.mul == U && b.l <= 4;
@@ -183,6 +185,10 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 if (S2 > 6) S2 = 6;
                 d.fast_S2 = S2;    // < 3: second-order passes fall back to the general kernels
                 d.fast_smem2 = (size_t)S2 * (stage2 + 16) + 128;
+                int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 16));
+                if (S3 > 6) S3 = 6;
+                d.fast_S3 = S3;    // < 2: atomic forward falls back to the general kernel
+                d.fast_smem3 = (size_t)(S3 > 0 ? S3 : 0) * (stage + 16) + 4 * (size_t)d.dim[2] + 160;
             }
         }
     }
@@ -259,12 +265,12 @@ std::string emit_header(const Desc& d) {
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
 // cy[n] = C_n * y[j_n] is formed once per edge by the producer warp; the consumer code below reads it as float4.
-std::string emit_fast(const Desc& d, int ch, int ng, bool dbl) {
+std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
     s << "#define FAST_DBL " << (dbl ? 1 : 0) << "\n";
-    s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << (dbl ? d.fast_S2 : d.fast_S)
+    s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << stages
       << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
     std::ostringstream cyc, cyj;
@@ -413,10 +419,11 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         // code stream, which measured faster than the split variants (those stalled on instruction fetch).
         const bool fwd = fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC;
         const bool dbl = fam >= FAM_FAST_BWD2_TP;
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl);
+        const int stages = dbl ? d.fast_S2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
-        src += K_COMMON;
+        src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
         src += K_FAST_UVU;
     }
     return src;
@@ -694,7 +701,7 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (status_override) p.status = status_override;
     else if ((rc = status_word(&p.status))) return rc;
     Program* prog;
-    const size_t smem = dbl ? d.fast_smem2 : d.fast_smem;
+    const size_t smem = dbl ? d.fast_smem2 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
     if ((rc = get_program(e, dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel, &prog))) return rc;
     cudaKernel_t k;
     if ((rc = get_kernel(prog, names[kernel], smem, &k))) return rc;
@@ -818,6 +825,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
         if (fam != FAM_GENERIC && !d.fast) continue;
         if (fam >= FAM_FAST_BWD2_TP && d.fast_S2 < 3) continue;
+        if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;
         std::string cubin;
         int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
         if (rc) return -rc;
@@ -949,7 +957,7 @@ int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_
         return generic_forward(e, p, st);
     }
     CUDA_TRY(cudaMemsetAsync(Z, 0, n_nodes * d.dim[2] * d.elt(), st));
-    if (fast) {
+    if (fast && d.fast_S3 >= 2 && aligned16({Z})) {
         FastParams f{X, Y, W, nullptr, Z, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
         return fast_launch(e, 2, f, st);
     }
@@ -1018,7 +1026,7 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
         if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
     }
     int rc;
-    if (use_fast(d) && d.fast_S2 >= 3 && n_edges > 0 && aligned16({X, X2, W, W2, dX, workspace})) {
+    if (use_fast(d) && d.fast_S2 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, dX, dG, workspace})) {
         // channel-parallel kernels: dG from three forward passes, (dX, dY, dW) from two second-order backward passes
         const int kf = d.det ? 1 : 2, kb = d.det ? 4 : 5;
         void* colptr = nullptr;

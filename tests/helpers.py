@@ -71,6 +71,10 @@ def tp_problem_matrix():
     out.append(("uvu_shared", single("20x1e", "1x1e", "20x1e", "uvu", shared=True)))
     out.append(("uvw_shared", single("12x1e", "2x1e", "9x1e", "uvw", shared=True)))
     out.append(("uvu_ir_mul", single("24x2e", "2x1o", "24x3o", "uvu", layout="ir_mul")))
+    out.append(("uvu_ir_mul_fast", single("64x2e", "1x1o", "64x3o", "uvu", layout="ir_mul")))
+    ctpp_ir_mul = P.nequip_problems()[4].clone()
+    ctpp_ir_mul.layout = "ir_mul"
+    out.append(("ctpp_ir_mul", ctpp_ir_mul))
     out.append(("multi_out", TPProblem("6x1o+4x2e", "1x1o+1x0e", "6x1o+6x2e+4x2e",
                                        [(0, 0, 1, "uvu", True), (0, 1, 0, "uvu", True, 0.7), (1, 1, 2, "uvu", True),
                                         (0, 0, 1, "uvu", True, 0.5)], shared_weights=False, internal_weights=False)))

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 MATRIX = dict(tp_problem_matrix())
 CONV_PROBLEMS = ["readme", "uvu_m33v3", "uvu_l431", "uvw_m4", "uvw_m40", "multi_out", "mace_medium", "nequip_water_uvu",
-                 "mace_like"]
+                 "ctpp_ir_mul", "uvu_ir_mul_fast", "mace_like"]
 MODES = ["atomic", "deterministic", "kahan"]
 
 

@@ -70,7 +70,8 @@ def test_emitted_source_is_specialised():
     assert "struct Ins<0>" in src and "oeq_generic_forward" in src and "L3_DIM = 5" in src
 
 
-_BIG = {"mace_like", "mace_medium", "nequip_like", "diffdock1", "tetris_poly2", "nequip_water_uvu"}
+_BIG = {"mace_like", "mace_medium", "nequip_like", "diffdock1", "tetris_poly2", "nequip_water_uvu", "ctpp_ir_mul",
+        "uvu_ir_mul_fast"}
 
 
 @pytest.mark.parametrize("name,problem", [t for t in tp_problem_matrix() if t[0] not in _BIG],
