@@ -53,7 +53,7 @@ typedef struct oeqb_kernel_prop {
     int32_t idx_dtype;     /* 3 = int32, 4 = int64 */
     int32_t is_conv, deterministic, kahan;
     int32_t is_uvw;
-    int32_t fast_path;     /* 1 when the channel-parallel TMA-pipelined kernels apply */
+    int32_t fast_path;     /* 1: channel-parallel TMA-pipelined kernels; 2: tcgen05 'uvw' forward; 0: general kernels */
     int32_t reserved;
 } oeqb_kernel_prop;
 

@@ -39,6 +39,7 @@ thread_local std::string g_err;
 std::atomic<long long> g_launches{0};
 bool g_log = false;
 bool g_force_generic = false;
+bool g_no_tc = false;          // tuning aid: keep 'uvw' forward on the general kernel
 bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
 std::string g_cache_dir;
 std::mutex g_mutex;
@@ -80,6 +81,7 @@ struct Desc {
     size_t fast_smem = 0;
     int fast_S2 = 0;         // stages of the second-order backward kernels (their stage carries a second weight row)
     size_t fast_smem2 = 0;
+    bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
@@ -191,6 +193,19 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 d.fast_smem3 = (size_t)(S3 > 0 ? S3 : 0) * (stage + 16) + 4 * (size_t)d.dim[2] + 160;
             }
         }
+    }
+    // Tensor-core path for 'uvw': shared fp32 weights, every in1 / out multiplicity 32, in2 multiplicity 1, l <= 3.
+    d.tc = false;
+    if (d.dtype == 1 && d.layout == 0 && d.uvw && d.shared && !d.L[0].empty()) {
+        bool ok = d.dim[1] <= 16;
+        for (auto& b : d.L[0]) ok = ok && b.mul == 32 && b.l <= 3;
+        for (auto& b : d.L[1]) ok = ok && b.mul == 1 && b.l <= 3;
+        for (auto& b : d.L[2]) ok = ok && b.mul == 32 && b.l <= 3;
+        // every output block must be written by at least one path (the kernel stores only blocks it accumulates)
+        std::vector<int> hit(d.L[2].size(), 0);
+        for (auto& I : d.ins) hit[I.o] = 1;
+        for (int h : hit) ok = ok && h;
+        d.tc = ok;
     }
     return true;
 }
@@ -389,17 +404,66 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
     return s.str();
 }
 
+// Per-path tables for the tensor-core 'uvw' forward (kernels/uvw_tc.cuh): paths ordered by output block, and for each
+// path and output component k the Clebsch-Gordan sum that produces one element of the A operand.
+std::string emit_tc(const Desc& d) {
+    std::ostringstream s;
+    if (!d.tc) { s << "#define OEQ_TC 0\n"; return s.str(); }
+    s << "#define OEQ_TC 1\n";
+    std::vector<int> order(d.ins.size());
+    for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return d.ins[a].o < d.ins[b].o; });
+    std::vector<int> first(d.ins.size(), 0), last(d.ins.size(), 0);
+    for (size_t q = 0; q < order.size(); ++q) {
+        if (q == 0 || d.ins[order[q - 1]].o != d.ins[order[q]].o) first[order[q]] = 1;
+        if (q + 1 == order.size() || d.ins[order[q + 1]].o != d.ins[order[q]].o) last[order[q]] = 1;
+    }
+    // run-time tables, one entry per path in schedule order (paths sorted by output block)
+    auto ilist = [&](const char* name, const std::vector<long long>& v) {
+        s << "__device__ const int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
+        for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
+        if (v.empty()) s << "0";
+        s << "};\n";
+    };
+    std::vector<long long> vd1, vd3, vx, vz, vw, vf, vl, kbeg, ti, tj;
+    std::vector<double> tcf;
+    int maxd1 = 1;
+    for (size_t q = 0; q < order.size(); ++q) {
+        const Instr& I = d.ins[order[q]];
+        const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
+        vd1.push_back(A.d()); vd3.push_back(O.d()); vx.push_back(A.off); vz.push_back(O.off); vw.push_back(I.woff);
+        vf.push_back(first[order[q]]); vl.push_back(last[order[q]]);
+        if (A.d() > maxd1) maxd1 = A.d();
+        for (int k = 0; k < 8; ++k) {
+            kbeg.push_back((long long)ti.size());
+            if (k < O.d())
+                for (auto& z : I.nz)
+                    if (z.k == k) { ti.push_back(z.i); tj.push_back(B.off + z.j); tcf.push_back(z.c); }
+        }
+    }
+    kbeg.push_back((long long)ti.size());
+    s << "constexpr int TC_MAXD1 = " << maxd1 << ";\n";
+    ilist("TC_D1", vd1); ilist("TC_D3", vd3); ilist("TC_XOFF", vx); ilist("TC_ZOFF", vz); ilist("TC_WOFF", vw);
+    ilist("TC_FIRST", vf); ilist("TC_LAST", vl); ilist("TC_KBEG", kbeg); ilist("TC_TI", ti); ilist("TC_TJ", tj);
+    s << "__device__ const float TC_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
+    for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
+    if (tcf.empty()) s << "0";
+    s << "};\n";
+    return s.str();
+}
+
 // --------------------------------------------------------------------------------------- kernel families
 enum Family {
     FAM_GENERIC = 0,
     FAM_FAST_FWD_TP, FAM_FAST_FWD_DET, FAM_FAST_FWD_ATOMIC, FAM_FAST_BWD_TP, FAM_FAST_BWD_DET, FAM_FAST_BWD_ATOMIC,
     FAM_FAST_SCATTER,
     FAM_FAST_BWD2_TP, FAM_FAST_BWD2_DET, FAM_FAST_BWD2_ATOMIC,   // second-order variants of the backward kernels
+    FAM_UVW_TC,                                                  // tcgen05 'uvw' forward
     FAM_COUNT
 };
 const char* const kFamilyNames[FAM_COUNT] = {"generic", "fast_fwd_tp", "fast_fwd_det", "fast_fwd_atomic", "fast_bwd_tp",
                                              "fast_bwd_det", "fast_bwd_atomic", "fast_scatter", "fast_bwd2_tp",
-                                             "fast_bwd2_det", "fast_bwd2_atomic"};
+                                             "fast_bwd2_det", "fast_bwd2_atomic", "uvw_tc"};
 const char* family_name(int f) { return (f >= 0 && f < FAM_COUNT) ? kFamilyNames[f] : "?"; }
 int family_from_name(const std::string& n) {
     for (int f = 0; f < FAM_COUNT; ++f)
@@ -413,6 +477,10 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
     if (fam == FAM_GENERIC) {
         src += K_COMMON;
         src += K_GENERIC;
+    } else if (fam == FAM_UVW_TC) {
+        src += emit_tc(d);
+        src += K_COMMON;
+        src += K_UVW_TC;
     } else {
         // Forward kernels carry two channels per thread in two block-owning groups (their code is small enough to stay
         // in the instruction cache); the backward kernels, three times larger, keep one channel per thread and one
@@ -754,6 +822,33 @@ int noalloc_scratch(void** out) {
     return OEQB_OK;
 }
 
+// ------------------------------------------------------------------------------------ tensor-core 'uvw'
+struct TcParams {
+    const void* x; const void* y; const void* W; void* z;
+    long long batch;
+    int* status;
+};
+// sizeof(TcShared) in kernels/uvw_tc.cuh, rounded up: operand buffers + staged input block + harmonics
+size_t tc_smem_bytes(const Desc& d) {
+    int maxd1 = 1;
+    for (auto& I : d.ins) maxd1 = std::max(maxd1, d.L[0][I.a].d());
+    return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 128 * (32 * maxd1 + 4) + 128 * (((int)d.dim[1] + 3) & ~3)) + 512;
+}
+
+int tc_forward(Entry* e, TcParams p, cudaStream_t st) {
+    int rc;
+    if ((rc = status_word(&p.status))) return rc;
+    Program* prog;
+    if ((rc = get_program(e, FAM_UVW_TC, &prog))) return rc;
+    cudaKernel_t k;
+    const size_t smem = tc_smem_bytes(e->d);
+    if ((rc = get_kernel(prog, "oeq_uvw_tc_forward", smem, &k))) return rc;
+    long long tiles = (p.batch + 127) / 128, grid = sm_count();
+    if (grid > tiles) grid = tiles;
+    void* args[] = {&p};
+    return launch(k, (unsigned)grid, 256, smem, args, st);
+}
+
 int check_ptrs(std::initializer_list<const void*> ptrs, const char* what) {
     for (const void* p : ptrs)
         if (!p) return fail(OEQB_EINVAL, "%s: null pointer argument", what);
@@ -777,6 +872,7 @@ int oeqb_set_option(const char* name, const char* value) {
     else if (n == "force_generic") g_force_generic = atoi(value) != 0;
     else if (n == "log") g_log = atoi(value) != 0;
     else if (n == "single_group") g_single_group = atoi(value) != 0;
+    else if (n == "no_tc") g_no_tc = atoi(value) != 0;
     else return fail(OEQB_EINVAL, "unknown option '%s'", name);
     return OEQB_OK;
 }
@@ -792,7 +888,7 @@ int oeqb_query(const void* desc, size_t desc_len, int64_t key, oeqb_kernel_prop*
     out->L1_dim = d.dim[0]; out->L2_dim = d.dim[1]; out->L3_dim = d.dim[2]; out->weight_numel = d.wn;
     out->shared_weights = d.shared; out->irrep_dtype = d.dtype; out->weight_dtype = d.dtype; out->idx_dtype = d.idx;
     out->is_conv = d.conv; out->deterministic = d.det; out->kahan = d.kahan; out->is_uvw = d.uvw;
-    out->fast_path = d.fast && !g_force_generic;
+    out->fast_path = (d.fast && !g_force_generic) ? 1 : ((d.tc && !g_force_generic && !g_no_tc) ? 2 : 0);
     return OEQB_OK;
 }
 
@@ -823,7 +919,8 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     const std::string header = emit_header(d);
     int done = 0;
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
-        if (fam != FAM_GENERIC && !d.fast) continue;
+        if (fam == FAM_UVW_TC) { if (!d.tc) continue; }
+        else if (fam != FAM_GENERIC && !d.fast) continue;
         if (fam >= FAM_FAST_BWD2_TP && d.fast_S2 < 3) continue;
         if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;
         std::string cubin;
@@ -845,6 +942,10 @@ int oeqb_tp_forward(const void* desc, size_t desc_len, int64_t key, int64_t batc
     if (use_fast(e->d) && aligned16({x, W})) {
         FastParams f{x, y, W, nullptr, z, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
         return fast_launch(e, 0, f, (cudaStream_t)stream);
+    }
+    if (e->d.tc && !g_force_generic && !g_no_tc) {
+        TcParams t{x, y, W, z, batch, nullptr};
+        return tc_forward(e, t, (cudaStream_t)stream);
     }
     FwdParams p{x, y, W, z, nullptr, nullptr, batch, batch, UNIT_ITEM, OUT_STORE};
     return generic_forward(e, p, (cudaStream_t)stream);

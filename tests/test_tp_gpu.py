@@ -166,3 +166,26 @@ def test_edge_cases_empty_and_single_item():
     xt = torch.tensor(np.concatenate([xb, xb], 1)).cuda()[:, : p.irreps_in1.dim]
     got = tp(xt, torch.tensor(yb).cuda(), torch.tensor(wb).cuda()).cpu().numpy()
     assert rel_l2(got, tp_oracle.forward(p, xb, yb, tp.reorder_weights_to_e3nn(wb))) <= 1e-5
+
+
+def test_uvw_tensor_core_forward_is_used_and_matches_general_kernel():
+    """The NequIP-like problem is served by the tcgen05 kernel (fast_path == 2); its 3xTF32 result must agree with
+    the fp64 oracle to the fp32 tolerance and with the general CUDA-core kernel to rounding, also on a ragged batch."""
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    p = dict(MATRIX)["nequip_like"]
+    tp = _module(p)
+    assert native.query(tp.kernel_string.encode(), tp.hash).fast_path == 2
+    for B in (1, 127, 128, 129, 1000):
+        x, y, w, *_ = uniform_inputs(p, B, seed=B)
+        args = [torch.tensor(a, device="cuda") for a in (x, y, w)]
+        before = native.launch_count()
+        got = tp(*args).cpu().numpy()
+        assert native.launch_count() == before + 1
+        native.set_option("no_tc", "1")
+        try:
+            ref = tp(*args).cpu().numpy()
+        finally:
+            native.set_option("no_tc", "0")
+        assert rel_l2(got, ref) <= 2e-6
+        assert rel_l2(got, tp_oracle.forward(p, x, y, tp.reorder_weights_to_e3nn(w))) <= 1e-5
