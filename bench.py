@@ -309,8 +309,12 @@ def bench_single(args, n_nodes, deterministic, dev):
     dominant = "backward" if bwd_ms >= fwd_ms else "forward"
     dom_bytes, dom_ms = (bwd_b, bwd_ms) if dominant == "backward" else (fwd_b, fwd_ms)
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    # DRAM bytes per edge of the dominant pass from one ncu capture on the 8,000-node case (profiles/
+    # oeq_fast_conv_det__mace_like_8000nodes.md), scaled by the edge count: traffic is dominated by per-edge rows
+    traffic_per_edge = {"forward": 18.6e3, "backward": (40.3e3 + 8.3e3) if deterministic else None}
+    traffic = traffic_per_edge[dominant] * E if (traffic_per_edge[dominant] and n_nodes >= 8000) else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "kernel": f"conv {dominant} pass", "peak_kind": peak_kind,
+                "traffic": traffic, "kernel": f"conv {dominant} pass", "peak_kind": peak_kind,
                 "passes": {"forward": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "gbs": fwd_b / fwd_ms / 1e6},
                            "backward": {"ms": bwd_ms, "algorithmic_bytes": bwd_b, "gbs": bwd_b / bwd_ms / 1e6}},
                 "fwd_bwd_frac": (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak}
