@@ -126,7 +126,9 @@ struct __align__(16) FastShared {
     int pad[3];
 };
 static_assert(sizeof(FastShared) <= 232448, "stages exceed shared memory");
-constexpr int FAST_D = (FAST_S >= 5) ? 2 : 1;     // TMA look-ahead in edges (backward needs FAST_S >= FAST_D + 2)
+// TMA look-ahead in edges.  One stage stays in hand: in the backward pass for the dX row that is still leaving shared
+// memory (FAST_S >= FAST_D + 2); the forward pass measured fastest two edges ahead (7.07 ms against 7.23 / 7.36 ms at 3 / 4).
+constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 5) ? 2 : 1) : ((FAST_S >= 4) ? FAST_S - 2 : 1);
 // FAST_XPC / FAST_GPC (problem header): registers per channel for an X / dX row and for a Z / G row
 
 // transposed butterfly: on return lane L (L < N) holds in v[0] the sum over all 32 lanes of element L
