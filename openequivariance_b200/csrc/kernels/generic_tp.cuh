@@ -230,3 +230,115 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_backward(const Bwd
         });
     }
 }
+
+#if OEQ_SHARED_W
+// Backward for shared weights, path-major: a warp takes a chunk of consecutive items (or edges) and, for one
+// (instruction, v, tile of 32 w) at a time, runs over the chunk keeping that tile of dW in registers; only the chunk's
+// sums are added to global dW (one atomic per weight and chunk instead of one per weight and item, which is what the
+// reference does: templates/loop_unroll_tp.cuh:258-259).  dX and dY are added to per item, so the caller zeroes them.
+// Modes: OEQ_UNIT_ITEM (tensor product) and OEQ_UNIT_EDGE (atomic convolution).
+constexpr int OEQ_WTILE = 32;
+
+extern "C" __global__ void __launch_bounds__(128) oeq_generic_backward_shared(const BwdParams p, const int chunk) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = (gridDim.x * (long long)blockDim.x) >> 5;
+    const bool edge_mode = p.unit_mode == OEQ_UNIT_EDGE;
+    const long long nchunks = (p.n_edges + chunk - 1) / chunk;
+    for (long long unit = warp0; unit < nchunks; unit += nwarps) {
+        const long long e_lo = unit * chunk, e_hi = (e_lo + chunk < p.n_edges) ? e_lo + chunk : p.n_edges;
+        static_for<0, NINS>([&](auto ic) {
+            using In = Ins<decltype(ic)::value>;
+            using B1 = Blk1<In::A>;
+            using B2 = Blk2<In::B>;
+            using B3 = Blk3<In::O>;
+            constexpr int MULPAD = (B1::MUL + 31) & ~31;
+            for (int c = lane; c < MULPAD; c += 32) {   // c: channel u of the in1 block
+                const bool active = c < B1::MUL;
+                for (int v = 0; v < In::V; ++v) {
+#if !OEQ_UVW
+                    const int wi = widx_uvu<In::U, In::V>(In::WOFF, active ? c : 0, v);
+                    const T w = active ? p.W[wi] : T(0);
+                    T dwacc = T(0);
+#else
+                    for (int w0 = 0; w0 < In::WN_; w0 += OEQ_WTILE) {
+                    T wreg[OEQ_WTILE], dwacc[OEQ_WTILE];
+#pragma unroll
+                    for (int ww = 0; ww < OEQ_WTILE; ++ww) {
+                        const bool in = active && (w0 + ww < In::WN_);
+                        wreg[ww] = in ? p.W[widx_uvw<In::U, In::V, In::WN_>(In::WOFF, c, v, w0 + ww)] : T(0);
+                        dwacc[ww] = T(0);
+                    }
+#endif
+                    for (long long e = e_lo; e < e_hi; ++e) {
+                        const long long x_row = edge_mode ? (long long)p.cols[e] : e;
+                        const long long g_row = edge_mode ? (long long)p.rows[e] : e;
+                        const T* xrow = p.x + x_row * L1_DIM;
+                        const T* grow = p.g + g_row * L3_DIM;
+                        T xv[In::D1], y1[In::D2], y2[In::D2], gp[In::D3], t[In::D3], dxp[In::D1], dyp[In::D2];
+#pragma unroll
+                        for (int i = 0; i < In::D1; ++i) {
+                            xv[i] = active ? xrow[feat_idx<B1::OFF, B1::MUL, B1::D>(c, i)] : T(0);
+                            dxp[i] = T(0);
+                        }
+#pragma unroll
+                        for (int j = 0; j < In::D2; ++j) {
+                            y1[j] = p.y_dx[e * L2_DIM + feat_idx<B2::OFF, B2::MUL, B2::D>(v, j)];
+                            y2[j] = p.y_dw[e * L2_DIM + feat_idx<B2::OFF, B2::MUL, B2::D>(v, j)];
+                            dyp[j] = T(0);
+                        }
+#pragma unroll
+                        for (int k = 0; k < In::D3; ++k) t[k] = T(0);
+                        In::fwd(xv, y2, t);
+#if !OEQ_UVW
+#pragma unroll
+                        for (int k = 0; k < In::D3; ++k) {
+                            const T gk = active ? grow[feat_idx<B3::OFF, B3::MUL, B3::D>(c, k)] : T(0);
+                            gp[k] = w * gk;
+                            dwacc += t[k] * gk;
+                        }
+#else
+#pragma unroll
+                        for (int k = 0; k < In::D3; ++k) gp[k] = T(0);
+#pragma unroll
+                        for (int ww = 0; ww < OEQ_WTILE; ++ww) {
+                            if (w0 + ww < In::WN_) {
+#pragma unroll
+                                for (int k = 0; k < In::D3; ++k) {
+                                    const T gk = grow[feat_idx<B3::OFF, B3::MUL, B3::D>(w0 + ww, k)];
+                                    gp[k] += wreg[ww] * gk;
+                                    dwacc[ww] += t[k] * gk;
+                                }
+                            }
+                        }
+#endif
+                        In::dx(y1, gp, dxp);
+                        In::dy(xv, gp, dyp);
+                        if (active) {
+                            T* dxrow = p.dx + x_row * L1_DIM;
+#pragma unroll
+                            for (int i = 0; i < In::D1; ++i)
+                                emit_out(&dxrow[feat_idx<B1::OFF, B1::MUL, B1::D>(c, i)], dxp[i], edge_mode ? OEQ_OUT_ATOMIC : OEQ_OUT_ADD);
+                        }
+#pragma unroll
+                        for (int j = 0; j < In::D2; ++j) {
+                            const T s = warp_sum(dyp[j]);
+                            if (lane == 0) p.dy[e * L2_DIM + feat_idx<B2::OFF, B2::MUL, B2::D>(v, j)] += s;
+                        }
+                    }
+#if !OEQ_UVW
+                    if (active) atomicAdd(&p.dW[wi], dwacc);
+#else
+                    if (active) {
+#pragma unroll
+                        for (int ww = 0; ww < OEQ_WTILE; ++ww)
+                            if (w0 + ww < In::WN_) atomicAdd(&p.dW[widx_uvw<In::U, In::V, In::WN_>(In::WOFF, c, v, w0 + ww)], dwacc[ww]);
+                    }
+                    }   // w0 tiles
+#endif
+                }
+            }
+        });
+    }
+}
+#endif  // OEQ_SHARED_W

@@ -705,6 +705,18 @@ int generic_backward(Entry* e, BwdParams p, cudaStream_t st) {
     Program* prog;
     int rc = get_program(e, FAM_GENERIC, &prog);
     if (rc) return rc;
+    if (e->d.shared && p.unit_mode != UNIT_SEGMENT && p.n_edges >= 256) {
+        // shared weights: path-major kernel that sums dW over a chunk of items in registers (32x fewer atomics).
+        // It adds to dX, so for the tensor product dX has to start at zero (the convolution zeroes it anyway).
+        const Desc& d = e->d;
+        if (p.unit_mode == UNIT_ITEM && !p.accum)
+            CUDA_TRY(cudaMemsetAsync(p.dx, 0, (size_t)p.n_edges * d.dim[0] * d.elt(), st));
+        cudaKernel_t ks;
+        if ((rc = get_kernel(prog, "oeq_generic_backward_shared", 0, &ks))) return rc;
+        int chunk = 32;
+        void* args[] = {&p, &chunk};
+        return launch(ks, generic_grid((p.n_edges + chunk - 1) / chunk), 128, 0, args, st);
+    }
     cudaKernel_t k;
     if ((rc = get_kernel(prog, "oeq_generic_backward", 0, &k))) return rc;
     void* args[] = {&p};
@@ -921,7 +933,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
         if (fam == FAM_UVW_TC) { if (!d.tc) continue; }
         else if (fam != FAM_GENERIC && !d.fast) continue;
-        if (fam >= FAM_FAST_BWD2_TP && d.fast_S2 < 3) continue;
+        if (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC && d.fast_S2 < 3) continue;
         if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;
         std::string cubin;
         int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
