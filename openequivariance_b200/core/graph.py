@@ -83,7 +83,6 @@ def periodic_radius_graph(n_nodes: int, mean_degree: float = 32.0, cutoff: float
         # tiny boxes: all pairs
         i = torch.arange(n_nodes, device=device).repeat_interleave(n_nodes)
         j = torch.arange(n_nodes, device=device).repeat(n_nodes)
-        order0 = torch.arange(n_nodes, device=device)
     else:
         cs = box / ncell
         cc = torch.clamp((pos / cs).floor().to(torch.int64), 0, ncell - 1)

@@ -85,7 +85,6 @@ struct Desc {
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
-    size_t idx_bytes() const { return idx == 3 ? 4 : 8; }
 };
 
 bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {

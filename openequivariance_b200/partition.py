@@ -25,7 +25,7 @@ Remote rows always land in this GPU's own memory before a kernel reads them; no 
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, List, Optional
 
 import torch
@@ -59,7 +59,6 @@ class PartitionPlan:
     interior_edges: tuple = (0, 0)         # matching edge sub-range [ea, eb) (local)
     rows_mid: Optional[torch.Tensor] = None    # rows_local[ea:eb] - a
     rows_right: Optional[torch.Tensor] = None  # rows_local[eb:] - b
-    extras: dict = field(default_factory=dict)
 
     @property
     def n_owned(self) -> int:
