@@ -7,8 +7,8 @@
 //     16-number dY reduction;
 //   * one producer warp per CTA streams edges: it issues 1-D TMA bulk copies (cp.async.bulk) of the sender's
 //     feature row X[col] and the edge's weight row W[e] into a ring of shared-memory stages guarded by
-//     mbarriers, fetches Y[e] with cp.async and turns it into the edge's folded coefficients cy[n] = C_n * y[j_n]
-//     (they do not depend on the channel), and -- in the backward pass -- drains each finished stage: dX row
+//     mbarriers, fetches Y[e] with cp.async and turns it into the edge's folded coefficients
+//     cy[i,k] = sum_j C[i,j,k] y[j] (they do not depend on the channel), and -- in the backward pass -- drains each finished stage: dX row
 //     by TMA bulk store / bulk reduce-add, dY by a fixed-order sum of per-warp partials;
 //   * receiver-sorted edges: a CTA owns a contiguous receiver range, keeps the receiver's output row (forward) or
 //     its gradient row (backward) in registers across the receiver's edges; the summation order per receiver
@@ -16,8 +16,8 @@
 //
 // Math per channel u and path (l1,l2,l3) with folded coefficients (reference formulas: templates/loop_unroll_tp.cuh:46-96
 // forward, :202-291 backward):
-//   forward   z[k]  += w * sum_n cy_n x[i_n]
-//   backward  s[i]   = sum_n cy_n g[k_n];  dx[i] += w s[i];  dW = sum_i x[i] s[i];  dy[j_n] += C_n x[i_n] (w g[k_n])
+//   forward   z[k]  += w * sum_i cy[i,k] x[i]
+//   backward  s[i]   = sum_k cy[i,k] g[k];  dx[i] += w s[i];  dW = sum_i x[i] s[i];  dy[j] += C[i,j,k] x[i] (w g[k])
 //
 // Every wait on an mbarrier is bounded: when the limit is hit the thread records a code in *status, raises a
 // CTA-wide abort flag and leaves; the host reports OEQB_EKERNEL.
@@ -108,7 +108,7 @@ struct __align__(16) FastStage {
     float x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
     float w[WN];
     float w2[FAST_DBL ? WN : 4];     // second-order backward only: the row of Wdx
-    float cy[NCY];                   // folded coefficients cy[n] = C_n * y[j_n] of this edge
+    float cy[NCY];                   // folded coefficients of this edge: cy[q] = sum_j C[i_q][j][k_q] * y[j], one per (i, k) pair
     float y[FAST_YPAD];
     float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
     long long edge, row, col;
@@ -175,13 +175,16 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
     IDX colv = 0, rowv = 0, rown = 0;
     // this lane's share of the coefficient table stays in registers for the whole kernel
     constexpr int CY_PER_LANE = (NCY + 31) / 32;
-    float tab_c[CY_PER_LANE];
-    int tab_j[CY_PER_LANE];
+    float tab_c[CY_PER_LANE][FAST_CYT];
+    int tab_j[CY_PER_LANE][FAST_CYT];
 #pragma unroll
     for (int t = 0; t < CY_PER_LANE; ++t) {
         const int q = lane + 32 * t;
-        tab_c[t] = (q < NCY) ? FAST_CYC[q] : 0.f;
-        tab_j[t] = (q < NCY) ? FAST_CYJ[q] : 0;
+#pragma unroll
+        for (int m = 0; m < FAST_CYT; ++m) {
+            tab_c[t][m] = (q < NCY) ? FAST_CYC[q * FAST_CYT + m] : 0.f;
+            tab_j[t][m] = (q < NCY) ? FAST_CYJ[q * FAST_CYT + m] : 0;
+        }
     }
 
     auto phase_a = [&](long long ia) -> bool {   // claim a stage for edge ia and start its copies
@@ -229,7 +232,9 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         for (int t = 0; t < CY_PER_LANE; ++t) {
             const int q = lane + 32 * t;
             if (q < NCY) {
-                const float v = tab_c[t] * st.y[tab_j[t]];
+                float v = tab_c[t][0] * st.y[tab_j[t][0]];
+#pragma unroll
+                for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tab_c[t][m], st.y[tab_j[t][m]], v);
                 st.cy[q] = v;
             }
         }
@@ -245,13 +250,13 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
 #pragma unroll
             for (int w = 0; w < FAST_NCW; ++w) tot += st.dyp[w][lane];
             float* dst = p.dY + st.edge * L2_DIM + lane;
-            *dst = p.accum ? *dst + tot : tot;
+            *dst = (FAST_DBL && p.accum) ? *dst + tot : tot;   // only second-order passes add to their outputs
         }
         if (lane == 0) {
             // each per-edge row has a single writer, so adding to it (second pass of a double backward) stays deterministic
             float* row = (KIND == FAST_TP) ? p.dX + st.edge * L1_DIM : (KIND == FAST_DET) ? p.scratch + st.edge * L1_DIM
                                                                                         : p.dX + st.col * L1_DIM;
-            if (KIND == FAST_ATOMIC || p.accum) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            if (KIND == FAST_ATOMIC || (FAST_DBL && p.accum)) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
             else tma_store(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
         }
         tma_commit();
@@ -292,33 +297,37 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
         for (long long r = a; r < b; ++r)
             for (int q = tid; q < L3_DIM; q += FAST_NT) p.Z[r * L3_DIM + q] = 0.f;
     };
+    int s = -1;          // stage of edge i and the parity of its use: the ring is walked with counters, not divisions
+    unsigned par = 1;
     for (long long i = 0; i < n; ++i) {
-        const int s = (int)(i % FAST_S);
+        if (++s == FAST_S) s = 0;
+        par ^= (s == 0);
         FastStage& st = sh.st[s];
-        if (!mbar_wait(&sh.full[s], (unsigned)((i / FAST_S) & 1), abortf, p.status, 21)) return;
+        if (!mbar_wait(&sh.full[s], par, abortf, p.status, 21)) return;
         const long long row = st.row;
         const int last = st.last;
-        float xr[FAST_CH * FAST_XPC];
+        // Paths are taken input block by input block, so that only one block of the sender row is in registers at a time.
+        const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
         static_for<0, NB1>([&](auto bc) {
             constexpr int B = decltype(bc)::value;
             using B1 = Blk1<B>;
             if constexpr ((GRP == 0 ? FP_FWD_NEEDS_X0[B] : FP_FWD_NEEDS_X1[B]) != 0) {
+                float xb[FAST_CH * B1::D];
 #pragma unroll
                 for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                     for (int i1 = 0; i1 < B1::D; ++i1)
-                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
-            }
-        });
-        const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
-        static_for<0, NINS>([&](auto ic) {
-            constexpr int I = decltype(ic)::value;
-            using F = FIns<I>;
-            if constexpr (FP_INS_GF[I] == GRP) {
-                float wv[FAST_CH];
+                        xb[ch * B1::D + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
+                static_for<0, NINS>([&](auto ic) {
+                    constexpr int I = decltype(ic)::value;
+                    using F = FIns<I>;
+                    if constexpr (F::A == B && FP_INS_GF[I] == GRP) {
+                        float wv[FAST_CH];
 #pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
-                F::fwd(xr + F::XO, cy4, wv, acc + F::GO);
+                        for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
+                        F::fwd(xb, cy4, wv, acc + F::GO);
+                    }
+                });
             }
         });
         mbar_arrive(&sh.empty[s]);
@@ -401,10 +410,13 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
     volatile int* abortf = &sh.abort_flag;
     float g[FAST_CH * FAST_GPC];
     long long cur_row = -1;
+    int s = -1;
+    unsigned par = 1;
     for (long long i = 0; i < n; ++i) {
-        const int s = (int)(i % FAST_S);
+        if (++s == FAST_S) s = 0;
+        par ^= (s == 0);
         FastStage& st = sh.st[s];
-        if (!mbar_wait(&sh.full[s], (unsigned)((i / FAST_S) & 1), abortf, p.status, 22)) return;
+        if (!mbar_wait(&sh.full[s], par, abortf, p.status, 22)) return;
         const long long row = st.row, e = st.edge;
         if (row != cur_row) {   // new receiver: its gradient row goes to registers for all of its edges
             const float* grow = p.G + row * L3_DIM;
@@ -421,51 +433,48 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
             });
             cur_row = row;
         }
-        float xr[FAST_CH * FAST_XPC], dxr[FAST_CH * FAST_XPC], dyr[FAST_NYP];
-        static_for<0, NB1>([&](auto bc) {
-            constexpr int B = decltype(bc)::value;
-            using B1 = Blk1<B>;
-            if constexpr (FP_X_OWNER[B] == GRP) {
-#pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch)
-#pragma unroll
-                    for (int i1 = 0; i1 < B1::D; ++i1) {
-                        xr[ch * FAST_XPC + B1::OFF / FU + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
-                        dxr[ch * FAST_XPC + B1::OFF / FU + i1] = 0.f;
-                    }
-            }
-        });
+        float dyr[FAST_NYP];
 #pragma unroll
         for (int j = 0; j < FAST_NYP; ++j) dyr[j] = 0.f;
         const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
         float* dwrow = p.dW + e * WN;
-        static_for<0, NINS>([&](auto ic) {
-            constexpr int I = decltype(ic)::value;
-            using F = FIns<I>;
-            if constexpr (FP_INS_GB[I] == GRP) {
-                float wv[FAST_CH], wx[FAST_CH], dw[FAST_CH];
-#pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch) {
-                    wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
-                    wx[ch] = FAST_DBL ? st.w2[F::WOFF + u + ch * FAST_GT] : wv[ch];
-                }
-                F::bwd(xr + F::XO, g + F::GO, cy4, wv, wx, dxr + F::XO, dyr + F::Y0, dw);
-#pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch) {
-                    float* dst = dwrow + F::WOFF + u + ch * FAST_GT;
-                    *dst = p.accum ? *dst + dw[ch] : dw[ch];
-                }
-            }
-        });
+        // Paths are taken input block by input block: one block of x and of dx is in registers at a time, and the
+        // block's dx overwrites its x in the stage as soon as its paths are done.
         static_for<0, NB1>([&](auto bc) {
             constexpr int B = decltype(bc)::value;
             using B1 = Blk1<B>;
             if constexpr (FP_X_OWNER[B] == GRP) {
+                float xb[FAST_CH * B1::D], dxb[FAST_CH * B1::D];
+#pragma unroll
+                for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                    for (int i1 = 0; i1 < B1::D; ++i1) {
+                        xb[ch * B1::D + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
+                        dxb[ch * B1::D + i1] = 0.f;
+                    }
+                static_for<0, NINS>([&](auto ic) {
+                    constexpr int I = decltype(ic)::value;
+                    using F = FIns<I>;
+                    if constexpr (F::A == B && FP_INS_GB[I] == GRP) {
+                        float wv[FAST_CH], wx[FAST_CH], dw[FAST_CH];
+#pragma unroll
+                        for (int ch = 0; ch < FAST_CH; ++ch) {
+                            wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
+                            wx[ch] = FAST_DBL ? st.w2[F::WOFF + u + ch * FAST_GT] : wv[ch];
+                        }
+                        F::bwd(xb, g + F::GO, cy4, wv, wx, dxb, dyr + F::Y0, dw);
+#pragma unroll
+                        for (int ch = 0; ch < FAST_CH; ++ch) {
+                            float* dst = dwrow + F::WOFF + u + ch * FAST_GT;
+                            *dst = (FAST_DBL && p.accum) ? *dst + dw[ch] : dw[ch];
+                        }
+                    }
+                });
 #pragma unroll
                 for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                     for (int i1 = 0; i1 < B1::D; ++i1)
-                        st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)] = dxr[ch * FAST_XPC + B1::OFF / FU + i1];
+                        st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)] = dxb[ch * B1::D + i1];
             }
         });
         warp_reduce_transpose<FAST_NYP>(dyr, lane);

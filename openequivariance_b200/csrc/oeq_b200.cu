@@ -65,6 +65,19 @@ int fail(int code, const char* fmt, ...) {
 struct Block { int mul, l, p, off; int d() const { return 2 * l + 1; } };
 struct Nz { int i, j, k; double c; };
 struct Instr { int a, b, o; long long woff; std::vector<Nz> nz; };
+// Distinct (i, k) index pairs of an instruction's Clebsch-Gordan nonzeros, sorted, each with the nonzeros (one per j)
+// that share it.  The channel-parallel kernels fold the edge's y into one coefficient per pair.
+struct IkPair { int i, k; std::vector<Nz> terms; };
+std::vector<IkPair> ik_pairs(const Instr& I) {
+    std::vector<Nz> v = I.nz;
+    std::stable_sort(v.begin(), v.end(), [](const Nz& a, const Nz& b) { return a.i != b.i ? a.i < b.i : a.k < b.k; });
+    std::vector<IkPair> out;
+    for (const Nz& q : v) {
+        if (out.empty() || out.back().i != q.i || out.back().k != q.k) out.push_back(IkPair{q.i, q.k, {}});
+        out.back().terms.push_back(q);
+    }
+    return out;
+}
 struct Desc {
     int dtype = 1, layout = 0, shared = 0, uvw = 0, conv = 0, det = 0, kahan = 0, idx = 4;
     std::vector<Block> L[3];
@@ -159,7 +172,7 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         ok = ok && d.dim[0] / U <= 32 && d.dim[2] / U <= 112;
         if (ok) {
             int ncy = 0;
-            for (auto& I : d.ins) ncy += ((int)I.nz.size() + 3) & ~3;
+            for (auto& I : d.ins) ncy += ((int)ik_pairs(I).size() + 3) & ~3;
             const int nyp = d.dim[1] <= 1 ? 1 : d.dim[1] <= 2 ? 2 : d.dim[1] <= 4 ? 4 : d.dim[1] <= 8 ? 8 : d.dim[1] <= 16 ? 16 : 32;
             // Two channels per thread halve the shared-memory traffic of the coefficient loads; the row registers
             // that doubles are won back by dealing the blocks to two thread groups.
@@ -278,7 +291,7 @@ std::string emit_header(const Desc& d) {
 }
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
-// cy[n] = C_n * y[j_n] is formed once per edge by the producer warp; the consumer code below reads it as float4.
+// cy[i,k] = sum_j C[i,j,k] y[j] is formed once per edge by the producer warp; the consumer code below reads it as float4.
 std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
@@ -287,44 +300,53 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
     s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << stages
       << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
+    // Folded-coefficient table: slot q of an edge holds sum_t FAST_CYC[q][t] * y[FAST_CYJ[q][t]], one slot per (i, k) pair
     std::ostringstream cyc, cyj;
     std::vector<int> cyoff;
-    int off = 0;
+    std::vector<std::vector<IkPair>> pairs;
+    int off = 0, cyt = 1;
     for (auto& I : d.ins) {
+        pairs.push_back(ik_pairs(I));
+        for (auto& pr : pairs.back()) cyt = std::max(cyt, (int)pr.terms.size());
+    }
+    for (size_t n = 0; n < d.ins.size(); ++n) {
         cyoff.push_back(off);
-        const int pad = ((int)I.nz.size() + 3) & ~3;
-        for (int n = 0; n < pad; ++n) {
-            const bool real = n < (int)I.nz.size();
-            cyc << (real ? hexf(I.nz[n].c) : std::string("0.0")) << "f, ";
-            cyj << (real ? d.L[1][I.b].off + I.nz[n].j : 0) << ", ";
-        }
+        const int np = (int)pairs[n].size(), pad = (np + 3) & ~3;
+        for (int q = 0; q < pad; ++q)
+            for (int t = 0; t < cyt; ++t) {
+                const bool real = q < np && t < (int)pairs[n][q].terms.size();
+                cyc << (real ? hexf(pairs[n][q].terms[t].c) : std::string("0.0")) << "f, ";
+                cyj << (real ? d.L[1][d.ins[n].b].off + pairs[n][q].terms[t].j : 0) << ", ";
+            }
         off += pad;
     }
-    s << "__device__ const float FAST_CYC[NCY] = {" << cyc.str() << "};\n";
-    s << "__device__ const int FAST_CYJ[NCY] = {" << cyj.str() << "};\n";
+    s << "constexpr int FAST_CYT = " << cyt << ";\n";
+    s << "__device__ const float FAST_CYC[NCY * FAST_CYT] = {" << cyc.str() << "};\n";
+    s << "__device__ const int FAST_CYJ[NCY * FAST_CYT] = {" << cyj.str() << "};\n";
     s << "template <int I> struct FIns;\n";
     const char comp[4] = {'x', 'y', 'z', 'w'};
     for (size_t n = 0; n < d.ins.size(); ++n) {
         const Instr& I = d.ins[n];
         const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
-        const int D1 = A.d(), D3 = O.d(), nnz = (int)I.nz.size(), nq = (nnz + 3) / 4;
+        const std::vector<IkPair>& P = pairs[n];
+        const int D1 = A.d(), D3 = O.d(), np = (int)P.size(), nq = (np + 3) / 4;
         auto C = [&](int z) { std::ostringstream t; t << "c" << (z / 4) << "." << comp[z % 4]; return t.str(); };
         s << "template <> struct FIns<" << n << "> {\n";
-        s << "  static constexpr int XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
+        s << "  static constexpr int A = " << I.a << ", XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
           << ", CY4 = " << cyoff[n] / 4 << ", WOFF = " << I.woff << ", D1 = " << D1 << ", D3 = " << D3 << ";\n";
         // ---- forward: FAST_CH channels per thread share the coefficient loads
         s << "  static OEQ_DEV void fwd(const float* x, const float4* cy, const float* w, float* acc) {\n";
         for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
         s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-        s << "      const float* xc = x + ch * FAST_XPC; float* ac = acc + ch * FAST_GPC; const float wc = w[ch];\n";
+        s << "      const float* xc = x + ch * D1; float* ac = acc + ch * FAST_GPC; const float wc = w[ch];\n";
         if (D1 <= D3) {
             for (int i = 0; i < D1; ++i) s << "      const float xs" << i << " = wc * xc[" << i << "];\n";
-            for (int z = 0; z < nnz; ++z)
-                s << "      ac[" << I.nz[z].k << "] = fmaf(" << C(z) << ", xs" << I.nz[z].i << ", ac[" << I.nz[z].k << "]);\n";
+            for (int z = 0; z < np; ++z)
+                s << "      ac[" << P[z].k << "] = fmaf(" << C(z) << ", xs" << P[z].i << ", ac[" << P[z].k << "]);\n";
         } else {
             for (int k = 0; k < D3; ++k) s << "      float t" << k << " = 0.f;\n";
-            for (int z = 0; z < nnz; ++z)
-                s << "      t" << I.nz[z].k << " = fmaf(" << C(z) << ", xc[" << I.nz[z].i << "], t" << I.nz[z].k << ");\n";
+            for (int z = 0; z < np; ++z)
+                s << "      t" << P[z].k << " = fmaf(" << C(z) << ", xc[" << P[z].i << "], t" << P[z].k << ");\n";
             for (int k = 0; k < D3; ++k) s << "      ac[" << k << "] = fmaf(wc, t" << k << ", ac[" << k << "]);\n";
         }
         s << "    }\n  }\n";
@@ -335,10 +357,10 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
         for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
         s << "    float qv[FAST_CH][" << nqv << "];\n";
         s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-        s << "      const float* xc = x + ch * FAST_XPC; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * FAST_XPC; const float wc = w[ch]; const float wx = wdx[ch];\n";
+        s << "      const float* xc = x + ch * D1; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * D1; const float wc = w[ch]; const float wx = wdx[ch];\n";
         for (int i = 0; i < D1; ++i) s << "      float s" << i << " = 0.f;\n";
-        for (int z = 0; z < nnz; ++z)
-            s << "      s" << I.nz[z].i << " = fmaf(" << C(z) << ", gc[" << I.nz[z].k << "], s" << I.nz[z].i << ");\n";
+        for (int z = 0; z < np; ++z)
+            s << "      s" << P[z].i << " = fmaf(" << C(z) << ", gc[" << P[z].k << "], s" << P[z].i << ");\n";
         s << "      float dwv = 0.f;\n";
         for (int i = 0; i < D1; ++i) {
             s << "      dwv = fmaf(xc[" << i << "], s" << i << ", dwv);\n";
@@ -353,7 +375,7 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
         for (size_t z = 0; z < byik.size();) {
             size_t m = z;
             s << "    { float pr = 0.f;\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = fmaf(";
-            if (scale_g) s << "x[ch * FAST_XPC + " << byik[z].i << "], qv[ch][" << byik[z].k << "]";
+            if (scale_g) s << "x[ch * D1 + " << byik[z].i << "], qv[ch][" << byik[z].k << "]";
             else s << "qv[ch][" << byik[z].i << "], g[ch * FAST_GPC + " << byik[z].k << "]";
             s << ", pr);\n     ";
             while (m < byik.size() && byik[m].i == byik[z].i && byik[m].k == byik[z].k) {

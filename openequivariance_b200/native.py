@@ -72,6 +72,10 @@ def load(build_if_missing: bool = True):
         BUILT_EXTENSION, BUILT_EXTENSION_ERROR = True, None
         if os.environ.get("OEQB_LOG") == "1":
             lib.oeqb_set_option(b"log", b"1")
+        # OEQB_OPTIONS="name=value,name=value": library options (see oeqb_set_option) applied at load time
+        for item in filter(None, os.environ.get("OEQB_OPTIONS", "").split(",")):
+            name, _, value = item.partition("=")
+            lib.oeqb_set_option(name.strip().encode(), value.strip().encode())
     except Exception as exc:  # noqa: BLE001 - surfaced through BUILT_EXTENSION_ERROR and re-raised on use
         BUILT_EXTENSION, BUILT_EXTENSION_ERROR = False, exc
         raise RuntimeError(f"oeq_b200 native library unavailable ({LIB_PATH}): {exc}") from exc
