@@ -77,12 +77,26 @@ OEQ_DEV bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* a
         }
     }
 }
+// L2 eviction policies for the bulk copies: rows that are touched once (weights, per-edge outputs) should leave the L2
+// first, so that the sender rows, which neighbouring receivers read again, stay.
+OEQ_DEV unsigned long long l2_evict_first() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 OEQ_DEV void tma_load(void* dst_smem, const void* src, unsigned bytes, unsigned long long* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+OEQ_DEV void tma_load_hint(void* dst_smem, const void* src, unsigned bytes, unsigned long long* bar, unsigned long long pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol) : "memory");
+}
 OEQ_DEV void tma_store(void* dst, const void* src_smem, unsigned bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+OEQ_DEV void tma_store_hint(void* dst, const void* src_smem, unsigned bytes, unsigned long long pol) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(dst), "r"(smem_u32(src_smem)), "r"(bytes), "l"(pol) : "memory");
 }
 OEQ_DEV void tma_reduce_add(void* dst, const void* src_smem, unsigned bytes) {
     asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
@@ -172,6 +186,7 @@ template <int KIND, bool BWD>
 OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
     const long long e0 = sh.range[0], n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
+    const unsigned long long pol_stream = l2_evict_first();
     IDX colv = 0, rowv = 0, rown = 0;
     // this lane's share of the coefficient table stays in registers for the whole kernel
     constexpr int CY_PER_LANE = (NCY + 31) / 32;
@@ -215,9 +230,11 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
             st.first = (ia == 0) || (KIND == FAST_TP);   // consumers also compare rows; see fast_backward
             st.last = (ia == n - 1) || (row != nxt) || (KIND == FAST_TP);
             mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN * (FAST_DBL ? 2 : 1)) * sizeof(float)));
-            tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
-            tma_load(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s]);
-            if (FAST_DBL) tma_load(st.w2, p.Wdx + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s]);
+            // weight rows are read once: they should leave the L2 before the sender rows, which neighbouring receivers reuse
+            if (KIND == FAST_TP) tma_load_hint(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s], pol_stream);
+            else tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
+            tma_load_hint(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s], pol_stream);
+            if (FAST_DBL) tma_load_hint(st.w2, p.Wdx + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s], pol_stream);
         }
         for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y[j], p.Y + e * L2_DIM + j);
         ldgsts_commit();
@@ -257,7 +274,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
             float* row = (KIND == FAST_TP) ? p.dX + st.edge * L1_DIM : (KIND == FAST_DET) ? p.scratch + st.edge * L1_DIM
                                                                                         : p.dX + st.col * L1_DIM;
             if (KIND == FAST_ATOMIC || (FAST_DBL && p.accum)) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
-            else tma_store(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            else tma_store_hint(row, st.x, (unsigned)(L1_DIM * sizeof(float)), pol_stream);
         }
         tma_commit();
         return true;
@@ -277,15 +294,45 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
 }
 
 
+// ---- a thread's slice of a row -----------------------------------------------------------------------------
+// Thread u carries channels u + ch * FAST_GT; a block's values are kept as v[ch * D + i].  (Giving a thread two
+// neighbouring channels and moving them with 8-byte accesses was measured: no faster.)
+OEQ_DEV int chan(int u, int ch) { return u + ch * FAST_GT; }
+template <class BLK>
+OEQ_DEV void block_load(const float* row, int u, float* v) {
+#pragma unroll
+    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+        for (int i = 0; i < BLK::D; ++i) v[ch * BLK::D + i] = row[feat_idx<BLK::OFF, BLK::MUL, BLK::D>(chan(u, ch), i)];
+}
+// the reverse; ADD: add to what the row holds; STREAM: global row that is not read again soon (evict-first stores).
+// a(ch, i) yields the value of channel ch, component i.
+template <class BLK, bool ADD, bool STREAM, class F>
+OEQ_DEV void block_store(float* row, int u, F&& a) {
+#pragma unroll
+    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+        for (int i = 0; i < BLK::D; ++i) {
+            float* dst = row + feat_idx<BLK::OFF, BLK::MUL, BLK::D>(chan(u, ch), i);
+            const float t = ADD ? *dst + a(ch, i) : a(ch, i);
+            if (STREAM) __stcs(dst, t); else *dst = t;
+        }
+}
+template <int WOFF>
+OEQ_DEV void weight_load(const float* w, int u, float* wv) {
+#pragma unroll
+    for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = w[WOFF + chan(u, ch)];
+}
+
 // ---- forward ----------------------------------------------------------------------------------------------
-// Consumer thread t: group t / FAST_GT, channels u + ch * FAST_GT (u = t % FAST_GT, ch < FAST_CH).  The folded
+// Consumer thread t: group t / FAST_GT, channels chan(u, ch) (u = t % FAST_GT, ch < FAST_CH).  The folded
 // coefficients are the same for every channel, so a thread that carries two channels reads them from shared memory
 // once for both: that halves the load on the shared-memory pipe, which is what limits these kernels.  A group owns a
 // subset of the output blocks (forward) or of the input blocks (backward) and runs only the paths that touch its
 // blocks, which keeps the per-thread row registers at the single-channel level.
 template <int KIND, int GRP>
 OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int tid) {
-    const int u = tid % FAST_GT;   // channel ch of this thread is u + ch * FAST_GT
+    const int u = tid % FAST_GT;   // channel ch of this thread is chan(u, ch)
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
     float acc[FAST_CH * FAST_GPC];
@@ -313,18 +360,13 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
             using B1 = Blk1<B>;
             if constexpr ((GRP == 0 ? FP_FWD_NEEDS_X0[B] : FP_FWD_NEEDS_X1[B]) != 0) {
                 float xb[FAST_CH * B1::D];
-#pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch)
-#pragma unroll
-                    for (int i1 = 0; i1 < B1::D; ++i1)
-                        xb[ch * B1::D + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
+                block_load<B1>(st.x, u, xb);
                 static_for<0, NINS>([&](auto ic) {
                     constexpr int I = decltype(ic)::value;
                     using F = FIns<I>;
                     if constexpr (F::A == B && FP_INS_GF[I] == GRP) {
                         float wv[FAST_CH];
-#pragma unroll
-                        for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
+                        weight_load<F::WOFF>(st.w, u, wv);
                         F::fwd(xb, cy4, wv, acc + F::GO);
                     }
                 });
@@ -340,14 +382,11 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                 constexpr int O = decltype(oc)::value;
                 using B3 = Blk3<O>;
                 if constexpr (FP_Z_OWNER[O] == GRP) {
+                    block_store<B3, false, false>(sh.zbuf, u, [&](int ch, int k) { return acc[ch * FAST_GPC + B3::OFF / FU + k]; });
 #pragma unroll
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
-                        for (int k = 0; k < B3::D; ++k) {
-                            float& a = acc[ch * FAST_GPC + B3::OFF / FU + k];
-                            sh.zbuf[feat_idx<B3::OFF, B3::MUL, B3::D>(u + ch * FAST_GT, k)] = a;
-                            a = 0.f;
-                        }
+                        for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = 0.f;
                 }
             });
             fence_async_smem();
@@ -367,15 +406,22 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                 constexpr int O = decltype(oc)::value;
                 using B3 = Blk3<O>;
                 if constexpr (FP_Z_OWNER[O] == GRP) {
+                    auto val = [&](int ch, int k) { return acc[ch * FAST_GPC + B3::OFF / FU + k]; };
+                    if (KIND == FAST_ATOMIC) {
+#pragma unroll
+                        for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                            for (int k = 0; k < B3::D; ++k)
+                                atomicAdd(zrow + feat_idx<B3::OFF, B3::MUL, B3::D>(chan(u, ch), k), val(ch, k));
+                    } else if (p.accum) {
+                        block_store<B3, true, false>(zrow, u, val);
+                    } else {
+                        block_store<B3, false, true>(zrow, u, val);
+                    }
 #pragma unroll
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
-                        for (int k = 0; k < B3::D; ++k) {
-                            float* dst = zrow + feat_idx<B3::OFF, B3::MUL, B3::D>(u + ch * FAST_GT, k);
-                            float& a = acc[ch * FAST_GPC + B3::OFF / FU + k];
-                            if (KIND == FAST_ATOMIC) atomicAdd(dst, a); else *dst = p.accum ? *dst + a : a;
-                            a = 0.f;
-                        }
+                        for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = 0.f;
                 }
             });
         }
@@ -428,7 +474,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                         for (int k = 0; k < B3::D; ++k)
-                            g[ch * FAST_GPC + B3::OFF / FU + k] = __ldg(grow + feat_idx<B3::OFF, B3::MUL, B3::D>(u + ch * FAST_GT, k));
+                            g[ch * FAST_GPC + B3::OFF / FU + k] = __ldcs(grow + feat_idx<B3::OFF, B3::MUL, B3::D>(chan(u, ch), k));
                 }
             });
             cur_row = row;
@@ -445,13 +491,9 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
             using B1 = Blk1<B>;
             if constexpr (FP_X_OWNER[B] == GRP) {
                 float xb[FAST_CH * B1::D], dxb[FAST_CH * B1::D];
+                block_load<B1>(st.x, u, xb);
 #pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch)
-#pragma unroll
-                    for (int i1 = 0; i1 < B1::D; ++i1) {
-                        xb[ch * B1::D + i1] = st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)];
-                        dxb[ch * B1::D + i1] = 0.f;
-                    }
+                for (int q = 0; q < FAST_CH * B1::D; ++q) dxb[q] = 0.f;
                 static_for<0, NINS>([&](auto ic) {
                     constexpr int I = decltype(ic)::value;
                     using F = FIns<I>;
@@ -459,22 +501,19 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                         float wv[FAST_CH], wx[FAST_CH], dw[FAST_CH];
 #pragma unroll
                         for (int ch = 0; ch < FAST_CH; ++ch) {
-                            wv[ch] = st.w[F::WOFF + u + ch * FAST_GT];
-                            wx[ch] = FAST_DBL ? st.w2[F::WOFF + u + ch * FAST_GT] : wv[ch];
+                            wv[ch] = st.w[F::WOFF + chan(u, ch)];
+                            wx[ch] = FAST_DBL ? st.w2[F::WOFF + chan(u, ch)] : wv[ch];
                         }
                         F::bwd(xb, g + F::GO, cy4, wv, wx, dxb, dyr + F::Y0, dw);
 #pragma unroll
                         for (int ch = 0; ch < FAST_CH; ++ch) {
-                            float* dst = dwrow + F::WOFF + u + ch * FAST_GT;
-                            *dst = (FAST_DBL && p.accum) ? *dst + dw[ch] : dw[ch];
+                            float* dst = dwrow + F::WOFF + chan(u, ch);
+                            if (FAST_DBL && p.accum) *dst += dw[ch];
+                            else __stcs(dst, dw[ch]);   // written once, not read again by this kernel
                         }
                     }
                 });
-#pragma unroll
-                for (int ch = 0; ch < FAST_CH; ++ch)
-#pragma unroll
-                    for (int i1 = 0; i1 < B1::D; ++i1)
-                        st.x[feat_idx<B1::OFF, B1::MUL, B1::D>(u + ch * FAST_GT, i1)] = dxb[ch * B1::D + i1];
+                block_store<B1, false, false>(st.x, u, [&](int ch, int i1) { return dxb[ch * B1::D + i1]; });
             }
         });
         warp_reduce_transpose<FAST_NYP>(dyr, lane);
