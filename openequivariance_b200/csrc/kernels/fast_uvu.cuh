@@ -202,8 +202,15 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         }
     }
 
+    // Ring positions of the three phases (stage and use parity of the edge each will handle next): walked with counters,
+    // the producer shares its scheduler with consumer warps and should not spend issue slots on 64-bit divisions.
+    struct RingPos { int s = 0; unsigned par = 0; OEQ_DEV void next() { if (++s == FAST_S) { s = 0; par ^= 1u; } } };
+    RingPos pos_a, pos_b, pos_c;
+
     auto phase_a = [&](long long ia) -> bool {   // claim a stage for edge ia and start its copies
-        const int s = (int)(ia % FAST_S);
+        const int s = pos_a.s;
+        const unsigned par_prev = pos_a.par ^ 1u;   // parity of the stage's previous use
+        pos_a.next();
         FastStage& st = sh.st[s];
         const long long e = e0 + ia;
         if ((ia & 31) == 0 && KIND != FAST_TP) {
@@ -220,7 +227,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         }
         if (ia >= FAST_S) {
             if (!BWD) {
-                if (!mbar_wait(&sh.empty[s], (unsigned)(((ia / FAST_S) - 1) & 1), abortf, p.status, 11)) return false;
+                if (!mbar_wait(&sh.empty[s], par_prev, abortf, p.status, 11)) return false;
             } else {
                 tma_wait_read<FAST_S - FAST_D - 1>();   // the stage's previous dX row has left shared memory
             }
@@ -241,7 +248,9 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         return true;
     };
     auto phase_b = [&](long long i) {            // Y[e] has landed: fold it into the coefficients, publish the stage
-        FastStage& st = sh.st[(int)(i % FAST_S)];
+        const int sb = pos_b.s;
+        pos_b.next();
+        FastStage& st = sh.st[sb];
         // copies are committed one group per edge, FAST_D edges ahead; near the end of the range fewer are in flight
         if (i + FAST_D <= n) ldgsts_wait<FAST_D - 1>(); else ldgsts_wait<0>();
         __syncwarp();
@@ -256,12 +265,14 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.full[(int)(i % FAST_S)]);
+        if (lane == 0) mbar_arrive(&sh.full[sb]);
     };
     auto phase_c = [&](long long j) -> bool {    // backward only: drain the outputs of a finished edge
-        const int s = (int)(j % FAST_S);
+        const int s = pos_c.s;
+        const unsigned par = pos_c.par;
+        pos_c.next();
         FastStage& st = sh.st[s];
-        if (!mbar_wait(&sh.empty[s], (unsigned)((j / FAST_S) & 1), abortf, p.status, 12)) return false;
+        if (!mbar_wait(&sh.empty[s], par, abortf, p.status, 12)) return false;
         if (lane < L2_DIM) {
             float tot = 0.f;
 #pragma unroll
