@@ -116,6 +116,10 @@ template <int N> OEQ_DEV void ldgsts_wait() { asm volatile("cp.async.wait_group 
 constexpr int FAST_GT = FU / FAST_CH;                      // threads per group: each carries FAST_CH channels
 constexpr int FAST_NT = FAST_NG * FAST_GT;                // consumer threads
 constexpr int FAST_NCW = FAST_NT / 32;                    // consumer warps
+// Producer warps per CTA.  The forward kernels use two, which take the CTA's edges in turn: with 4 + 2 warps per CTA and
+// two CTAs per SM every scheduler hosts two consumer warps and one (half-loaded) producer; with a single producer warp two
+// of the four schedulers carried 40 % more instructions than the others and set the pace.
+// FAST_NP (problem header): 2 for forward kernels whose look-ahead is even, else 1.
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
@@ -183,7 +187,8 @@ OEQ_DEV void cta_range(const FastParams& p, long long* out) {
 
 // ---- producer ---------------------------------------------------------------------------------------------
 template <int KIND, bool BWD>
-OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
+OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const int pid) {
+    static_assert(FAST_D % FAST_NP == 0 && FAST_NP < FAST_S, "a producer looks ahead in units of its own edges");
     const long long e0 = sh.range[0], n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
     const unsigned long long pol_stream = l2_evict_first();
@@ -204,8 +209,12 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
 
     // Ring positions of the three phases (stage and use parity of the edge each will handle next): walked with counters,
     // the producer shares its scheduler with consumer warps and should not spend issue slots on 64-bit divisions.
-    struct RingPos { int s = 0; unsigned par = 0; OEQ_DEV void next() { if (++s == FAST_S) { s = 0; par ^= 1u; } } };
-    RingPos pos_a, pos_b, pos_c;
+    struct RingPos {
+        int s; unsigned par;
+        OEQ_DEV void next() { s += FAST_NP; if (s >= FAST_S) { s -= FAST_S; par ^= 1u; } }
+    };
+    RingPos pos_a{pid, 0u}, pos_b{pid, 0u}, pos_c{pid, 0u};   // this producer's edges are pid, pid + FAST_NP, ...
+    long long cur_blk = -1;
 
     auto phase_a = [&](long long ia) -> bool {   // claim a stage for edge ia and start its copies
         const int s = pos_a.s;
@@ -213,8 +222,9 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         pos_a.next();
         FastStage& st = sh.st[s];
         const long long e = e0 + ia;
-        if ((ia & 31) == 0 && KIND != FAST_TP) {
-            const long long me = e + lane;
+        if ((ia >> 5) != cur_blk && KIND != FAST_TP) {   // indices of 32 consecutive edges, one per lane
+            cur_blk = ia >> 5;
+            const long long me = e0 + (cur_blk << 5) + lane;
             colv = (me < p.E) ? p.cols[me] : (IDX)0;
             rowv = (me < p.E) ? p.rows[me] : (IDX)0;
             rown = (me + 1 < p.E) ? p.rows[me + 1] : (IDX)-1;
@@ -252,7 +262,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
         pos_b.next();
         FastStage& st = sh.st[sb];
         // copies are committed one group per edge, FAST_D edges ahead; near the end of the range fewer are in flight
-        if (i + FAST_D <= n) ldgsts_wait<FAST_D - 1>(); else ldgsts_wait<0>();
+        if (i + FAST_D - FAST_NP < n) ldgsts_wait<FAST_D / FAST_NP - 1>(); else ldgsts_wait<0>();
         __syncwarp();
 #pragma unroll
         for (int t = 0; t < CY_PER_LANE; ++t) {
@@ -292,13 +302,14 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane) {
     };
 
     bool ok = true;
-    for (long long i = -(long long)FAST_D; i < n && ok; ++i) {
+    long long i = pid - (long long)FAST_D;
+    for (; i < n && ok; i += FAST_NP) {
         if (i >= 0) phase_b(i);
-        if (BWD && i >= 1) ok = phase_c(i - 1);
+        if (BWD && i >= FAST_NP) ok = phase_c(i - FAST_NP);
         if (ok && i + FAST_D < n) ok = phase_a(i + FAST_D);
     }
     if (BWD) {
-        if (ok && n > 0) ok = phase_c(n - 1);
+        if (ok && i - FAST_NP >= 0) ok = phase_c(i - FAST_NP);   // this producer's last edge
         tma_wait_all<0>();
     }
     ldgsts_wait<0>();
@@ -455,7 +466,7 @@ OEQ_DEV void fast_forward_body(const FastParams& p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid >= FAST_NT) { fast_producer<KIND, false>(p, sh, lane); return; }
+    if (tid >= FAST_NT) { fast_producer<KIND, false>(p, sh, lane, (tid - FAST_NT) >> 5); return; }
     if (FAST_NG == 1 || tid < FAST_GT) fast_forward_group<KIND, 0>(p, sh, tid); else fast_forward_group<KIND, 1>(p, sh, tid);
 }
 
@@ -546,23 +557,23 @@ OEQ_DEV void fast_backward_body(const FastParams& p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid >= FAST_NT) { fast_producer<KIND, true>(p, sh, lane); return; }
+    if (tid >= FAST_NT) { fast_producer<KIND, true>(p, sh, lane, (tid - FAST_NT) >> 5); return; }
     if (FAST_NG == 1 || tid < FAST_GT) fast_backward_group<KIND, 0>(p, sh, tid); else fast_backward_group<KIND, 1>(p, sh, tid);
 }
 
 // ---- entry points (one per program: FAST_KERNEL selects which) ----------------------------------------------
 #if FAST_KERNEL == 0
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_fwd_tp(const FastParams p) { fast_forward_body<FAST_TP>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_fwd_tp(const FastParams p) { fast_forward_body<FAST_TP>(p); }
 #elif FAST_KERNEL == 1
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_fwd_det(const FastParams p) { fast_forward_body<FAST_DET>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_fwd_det(const FastParams p) { fast_forward_body<FAST_DET>(p); }
 #elif FAST_KERNEL == 2
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_fwd_atomic(const FastParams p) { fast_forward_body<FAST_ATOMIC>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_fwd_atomic(const FastParams p) { fast_forward_body<FAST_ATOMIC>(p); }
 #elif FAST_KERNEL == 3
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_bwd_tp(const FastParams p) { fast_backward_body<FAST_TP>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_bwd_tp(const FastParams p) { fast_backward_body<FAST_TP>(p); }
 #elif FAST_KERNEL == 4
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_bwd_det(const FastParams p) { fast_backward_body<FAST_DET>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_bwd_det(const FastParams p) { fast_backward_body<FAST_DET>(p); }
 #elif FAST_KERNEL == 5
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32, FAST_CTAS) oeq_fast_bwd_atomic(const FastParams p) { fast_backward_body<FAST_ATOMIC>(p); }
+extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_bwd_atomic(const FastParams p) { fast_backward_body<FAST_ATOMIC>(p); }
 #elif FAST_KERNEL == 6
 // Deterministic scatter of the per-edge dX rows: colptr[c] = first position k (in sender-major order) whose sender >= c
 extern "C" __global__ void oeq_fast_colptr(const IDX* cols, const IDX* perm, long long E, long long N, long long* colptr) {

@@ -41,6 +41,7 @@ bool g_log = false;
 bool g_force_generic = false;
 bool g_no_tc = false;          // tuning aid: keep 'uvw' forward on the general kernel
 bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
+bool g_single_producer = false;   // tuning aid: one producer warp per CTA in the forward kernels too
 std::string g_cache_dir;
 std::mutex g_mutex;
 
@@ -292,11 +293,15 @@ std::string emit_header(const Desc& d) {
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
 // cy[i,k] = sum_j C[i,j,k] y[j] is formed once per edge by the producer warp; the consumer code below reads it as float4.
-std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages) {
+// Producer warps of a forward kernel with `stages` stages: two when its look-ahead (2 edges from 5 stages on) is even.
+int fast_producers(bool fwd, int stages) { return (fwd && stages >= 5 && !g_single_producer) ? 2 : 1; }
+
+std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, bool fwd) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
     s << "#define FAST_DBL " << (dbl ? 1 : 0) << "\n";
+    s << "constexpr int FAST_NP = " << fast_producers(fwd, stages) << ";\n";
     s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << stages
       << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
@@ -509,7 +514,7 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         const bool fwd = fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC;
         const bool dbl = fam >= FAM_FAST_BWD2_TP;
         const int stages = dbl ? d.fast_S2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages);
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, fwd);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
@@ -811,7 +816,8 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (grid > work) grid = work;
     void* args[] = {&p};
     const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
-    return launch(k, (unsigned)grid, consumers + 32, smem, args, st);
+    const int producers = fast_producers(kernel < 3, kernel == 2 ? d.fast_S3 : d.fast_S);
+    return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
 
 // dX[c] = sum of the per-edge rows in scratch over the sender's edges, in sender-major list order
@@ -905,6 +911,7 @@ int oeqb_set_option(const char* name, const char* value) {
     else if (n == "force_generic") g_force_generic = atoi(value) != 0;
     else if (n == "log") g_log = atoi(value) != 0;
     else if (n == "single_group") g_single_group = atoi(value) != 0;
+    else if (n == "single_producer") g_single_producer = atoi(value) != 0;
     else if (n == "no_tc") g_no_tc = atoi(value) != 0;
     else return fail(OEQB_EINVAL, "unknown option '%s'", name);
     return OEQB_OK;
