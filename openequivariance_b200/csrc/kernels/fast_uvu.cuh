@@ -116,10 +116,10 @@ template <int N> OEQ_DEV void ldgsts_wait() { asm volatile("cp.async.wait_group 
 constexpr int FAST_GT = FU / FAST_CH;                      // threads per group: each carries FAST_CH channels
 constexpr int FAST_NT = FAST_NG * FAST_GT;                // consumer threads
 constexpr int FAST_NCW = FAST_NT / 32;                    // consumer warps
-// Producer warps per CTA.  The forward kernels use two, which take the CTA's edges in turn: with 4 + 2 warps per CTA and
+// Producer warps per CTA.  With two, they take the CTA's edges in turn: with 4 + 2 warps per CTA and
 // two CTAs per SM every scheduler hosts two consumer warps and one (half-loaded) producer; with a single producer warp two
 // of the four schedulers carried 40 % more instructions than the others and set the pace.
-// FAST_NP (problem header): 2 for forward kernels whose look-ahead is even, else 1.
+// FAST_NP (problem header): 2 from five stages on (the look-ahead is then a multiple of two), else 1.
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
@@ -138,15 +138,19 @@ struct __align__(16) FastShared {
     float zbuf[FAST_ZBUF];
     unsigned long long full[FAST_S];
     unsigned long long empty[FAST_S];
+    unsigned long long drained[FAST_S];   // backward with two producers: the stage's dX row has left shared memory
     unsigned long long zfull, zfree;
     long long range[4];              // e0, e1, n0, n1
     int abort_flag;
     int pad[3];
 };
 static_assert(sizeof(FastShared) <= 232448, "stages exceed shared memory");
+static_assert(FAST_KERNEL == 6 || sizeof(FastShared) <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
 // TMA look-ahead in edges.  One stage stays in hand: in the backward pass for the dX row that is still leaving shared
 // memory (FAST_S >= FAST_D + 2); the forward pass measured fastest two edges ahead (7.07 ms against 7.23 / 7.36 ms at 3 / 4).
-constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 5) ? 2 : 1) : ((FAST_S >= 4) ? FAST_S - 2 : 1);
+constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 5) ? 2 : 1)
+                       : (FAST_NP == 2)   ? ((FAST_S - 2) & ~1)
+                                          : ((FAST_S >= 4) ? FAST_S - 2 : 1);
 // FAST_XPC / FAST_GPC (problem header): registers per channel for an X / dX row and for a Z / G row
 
 // transposed butterfly: on return lane L (L < N) holds in v[0] the sum over all 32 lanes of element L
@@ -238,8 +242,11 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         if (ia >= FAST_S) {
             if (!BWD) {
                 if (!mbar_wait(&sh.empty[s], par_prev, abortf, p.status, 11)) return false;
-            } else {
+            } else if (FAST_NP == 1) {
                 tma_wait_read<FAST_S - FAST_D - 1>();   // the stage's previous dX row has left shared memory
+            } else {
+                // FAST_S is odd or even, so the stage's previous edge may have been drained by the other producer warp
+                if (!mbar_wait(&sh.drained[s], par_prev, abortf, p.status, 13)) return false;
             }
         }
         if (lane == 0) {
@@ -298,6 +305,10 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
             else tma_store_hint(row, st.x, (unsigned)(L1_DIM * sizeof(float)), pol_stream);
         }
         tma_commit();
+        if (FAST_NP == 2) {   // tell whichever producer reuses the stage that the row has been read out
+            tma_wait_read<0>();
+            if (lane == 0) mbar_arrive(&sh.drained[s]);
+        }
         return true;
     };
 
@@ -551,7 +562,7 @@ OEQ_DEV void fast_backward_body(const FastParams& p) {
     FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); }
+        for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); mbar_init(&sh.drained[s], 1); }
         sh.abort_flag = 0;
         cta_range<KIND, false>(p, sh.range);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -187,23 +187,23 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
             int S = 0;
             for (; ctas >= 1; ctas /= 2) {
                 const size_t budget = 232448 / ctas - 1024 - 256;
-                S = (int)(budget / (stage + 16));
+                S = (int)(budget / (stage + 24));
                 if (S > 6) S = 6;
                 if (S >= 3) break;
             }
             if (S >= 3 && ctas >= 1) {
                 d.fast = true;
                 d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
-                d.fast_smem = (size_t)S * (stage + 16) + 128;
+                d.fast_smem = (size_t)S * (stage + 24) + 128;
                 const size_t stage2 = stage + 4 * (size_t)d.wn;
-                int S2 = (int)((232448 / ctas - 1024 - 256) / (stage2 + 16));
+                int S2 = (int)((232448 / ctas - 1024 - 256) / (stage2 + 24));
                 if (S2 > 6) S2 = 6;
                 d.fast_S2 = S2;    // < 3: second-order passes fall back to the general kernels
-                d.fast_smem2 = (size_t)S2 * (stage2 + 16) + 128;
-                int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 16));
+                d.fast_smem2 = (size_t)S2 * (stage2 + 24) + 128;
+                int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 24));
                 if (S3 > 6) S3 = 6;
                 d.fast_S3 = S3;    // < 2: atomic forward falls back to the general kernel
-                d.fast_smem3 = (size_t)(S3 > 0 ? S3 : 0) * (stage + 16) + 4 * (size_t)d.dim[2] + 160;
+                d.fast_smem3 = (size_t)(S3 > 0 ? S3 : 0) * (stage + 24) + 4 * (size_t)d.dim[2] + 160;
             }
         }
     }
@@ -293,15 +293,16 @@ std::string emit_header(const Desc& d) {
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
 // cy[i,k] = sum_j C[i,j,k] y[j] is formed once per edge by the producer warp; the consumer code below reads it as float4.
-// Producer warps of a forward kernel with `stages` stages: two when its look-ahead (2 edges from 5 stages on) is even.
-int fast_producers(bool fwd, int stages) { return (fwd && stages >= 5 && !g_single_producer) ? 2 : 1; }
+// Producer warps of a kernel with `stages` stages: two from five stages on (its look-ahead is then a multiple of two).
+int fast_producers(int stages) { return (stages >= 5 && !g_single_producer) ? 2 : 1; }
 
-std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, bool fwd) {
+std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_t smem_bytes) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
     s << "#define FAST_DBL " << (dbl ? 1 : 0) << "\n";
-    s << "constexpr int FAST_NP = " << fast_producers(fwd, stages) << ";\n";
+    s << "constexpr int FAST_NP = " << fast_producers(stages) << ";\n";
+    s << "constexpr size_t FAST_SMEM_BYTES = " << smem_bytes << ";\n";
     s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << stages
       << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
@@ -514,7 +515,8 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         const bool fwd = fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC;
         const bool dbl = fam >= FAM_FAST_BWD2_TP;
         const int stages = dbl ? d.fast_S2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, fwd);
+        const size_t smem = dbl ? d.fast_smem2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, smem);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
@@ -816,7 +818,7 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (grid > work) grid = work;
     void* args[] = {&p};
     const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
-    const int producers = fast_producers(kernel < 3, kernel == 2 ? d.fast_S3 : d.fast_S);
+    const int producers = fast_producers(dbl ? d.fast_S2 : (kernel == 2 ? d.fast_S3 : d.fast_S));
     return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
 
