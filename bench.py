@@ -317,7 +317,7 @@ def bench_single(args, n_nodes, deterministic, dev):
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     # DRAM bytes per edge of the dominant pass from one ncu capture on the 8,000-node case (profiles/
     # oeq_fast_conv_det__mace_like_8000nodes.md), scaled by the edge count: traffic is dominated by per-edge rows
-    traffic_per_edge = {"forward": 14.25e3, "backward": (37.3e3 + 8.3e3) if deterministic else None}
+    traffic_per_edge = {"forward": 14.4e3, "backward": (37.4e3 + 8.3e3) if deterministic else None}
     traffic = traffic_per_edge[dominant] * E if (traffic_per_edge[dominant] and n_nodes >= 8000) else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": f"conv {dominant} pass", "peak_kind": peak_kind,
