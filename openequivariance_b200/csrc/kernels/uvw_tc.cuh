@@ -107,6 +107,31 @@ static_assert(sizeof(TcShared) > 116 * 1024 && sizeof(TcShared) <= 232448, "one 
 // offset (in floats) of element (row, kcol) in a chunk
 OEQ_DEV int tc_elem(int row, int kcol) { return (row >> 3) * (TC_SBO / 4) + (kcol >> 2) * (TC_LBO / 4) + (row & 7) * 4 + (kcol & 3); }
 
+// Epilogue of one output block for one thread: its item's 16 output channels x D3 components are 16 * D3 consecutive
+// floats of the z row.  All components are pulled out of tensor memory first (column 32 k + c holds channel c of
+// component k), then written as 16-byte stores, so every 32-byte sector of z is written whole.
+template <int D3>
+OEQ_DEV void tc_epilogue(unsigned tbase, float* zdst, bool live) {
+    float v[16 * D3];   // v[c * D3 + k]
+#pragma unroll
+    for (int k = 0; k < D3; ++k) {
+        unsigned r[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(tbase + 32u * (unsigned)k) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c * D3 + k] = __uint_as_float(r[c]);
+    }
+    if (live) {
+        float4* dst = reinterpret_cast<float4*>(zdst);   // 64 * D3 bytes from a 16-byte boundary
+#pragma unroll
+        for (int q = 0; q < 4 * D3; ++q) __stcs(dst + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+    }
+}
+
 // The loops over paths, output components and Clebsch-Gordan terms are run-time loops over the TC_* tables of the
 // problem header (not unrolled): the whole kernel is a few KB of code and stays in the instruction cache.
 extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const TcParams p) {
@@ -239,21 +264,13 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
                     tc_fence_after();
                     const int qd = warp & 3, half = warp >> 2;          // TMEM lane quarter, column half
                     const long long b = item0 + qd * 32 + lane;
-                    for (int k = 0; k < d3; ++k) {
-                        const unsigned taddr = tmem + ((unsigned)(qd * 32) << 16) + (nblock & 1u) * 256u + 32u * (unsigned)k + 16u * half;
-                        unsigned r[16];
-                        asm volatile(
-                            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                            : "r"(taddr) : "memory");
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (b < p.batch) {
-                            float* zrow = p.z + b * L3_DIM + zoff;
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) zrow[(16 * half + c) * d3 + k] = __uint_as_float(r[c]);
-                        }
-                    }
+                    const unsigned tbase = tmem + ((unsigned)(qd * 32) << 16) + (nblock & 1u) * 256u + 16u * half;
+                    float* zdst = p.z + (b < p.batch ? b : 0) * L3_DIM + zoff + 16 * half * d3;
+                    const bool live = b < p.batch;
+                    if (d3 == 1) tc_epilogue<1>(tbase, zdst, live);
+                    else if (d3 == 3) tc_epilogue<3>(tbase, zdst, live);
+                    else if (d3 == 5) tc_epilogue<5>(tbase, zdst, live);
+                    else tc_epilogue<7>(tbase, zdst, live);
                     tc_fence_before();
                 }
                 ++nblock;
