@@ -172,9 +172,11 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
         for (int q = 0; q < NINS && !dead; ++q) {
             const int d1 = TC_D1[q], d3 = TC_D3[q], xoff = TC_XOFF[q], zoff = TC_ZOFF[q], woff = TC_WOFF[q];
             const int first = TC_FIRST[q], last = TC_LAST[q];
-            // stage the path's input block: rows of 32 * d1 contiguous floats, coalesced
+            // stage the path's input block: rows of 32 * d1 contiguous floats, coalesced; the block stays when the previous
+            // path of this tile read the same one
+            const bool restage = q == 0 || TC_XOFF[q - 1] != xoff;
             __syncthreads();   // readers of the previous path's block are done
-            const int rowlen = 32 * d1;
+            const int rowlen = restage ? 32 * d1 : 0;
             for (int c = lane; c < rowlen; c += 32) {   // warp w copies rows w, w + 8, ...: 16 independent loads in flight
                 float v[16];
 #pragma unroll

@@ -440,6 +440,21 @@ std::string emit_tc(const Desc& d) {
     std::vector<int> order(d.ins.size());
     for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return d.ins[a].o < d.ins[b].o; });
+    // Inside an output block the order of the paths is free.  Paths that read the same input block are put next to each
+    // other, and a group starts with the input block the previous group ended with where it can: the kernel keeps the
+    // staged input block when the next path reads the same one.
+    for (size_t g0 = 0; g0 < order.size();) {
+        size_t g1 = g0;
+        while (g1 < order.size() && d.ins[order[g1]].o == d.ins[order[g0]].o) ++g1;
+        std::stable_sort(order.begin() + g0, order.begin() + g1, [&](int a, int b) { return d.ins[a].a < d.ins[b].a; });
+        if (g0 > 0) {
+            const int prev = d.ins[order[g0 - 1]].a;
+            std::stable_partition(order.begin() + g0, order.begin() + g1, [&](int q) { return d.ins[q].a == prev; });
+        }
+        // end the group with the input block that the next group can start with (the most frequent one is a good guess:
+        // leave the sorted order otherwise)
+        g0 = g1;
+    }
     std::vector<int> first(d.ins.size(), 0), last(d.ins.size(), 0);
     for (size_t q = 0; q < order.size(); ++q) {
         if (q == 0 || d.ins[order[q - 1]].o != d.ins[order[q]].o) first[order[q]] = 1;
