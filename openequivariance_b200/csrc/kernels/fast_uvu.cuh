@@ -37,7 +37,12 @@ struct FastParams {
     const float* Wdx;   // second-order backward: weights that scale dX (W scales the dY products)
     int accum;          // add to the outputs instead of overwriting them
     int pad;
+    const float* X2; const float* Y2; const float* W2;   // fused second-order forward: the cotangents of (dX, dY, dW)
 };
+// Fused second-order forward (FAST_DBL on a forward kernel): z = F(X2, Y, W) + F(X, Y, W2) + F(X, Y2, W) in one pass.
+// X and W are staged as usual; the rows of X2 and W2 are read by the consumers straight from global memory (the
+// producer brings them into the L2 ahead), Y2 is folded into a second coefficient table.
+#define FAST_FWD3 (FAST_DBL && FAST_KERNEL <= 2)
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
 OEQ_DEV unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -102,6 +107,9 @@ OEQ_DEV void tma_reduce_add(void* dst, const void* src_smem, unsigned bytes) {
     asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
                  "r"(bytes) : "memory");
 }
+OEQ_DEV void l2_prefetch(const void* src, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 OEQ_DEV void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> OEQ_DEV void tma_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 template <int N> OEQ_DEV void tma_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
@@ -119,15 +127,16 @@ constexpr int FAST_NCW = FAST_NT / 32;                    // consumer warps
 // Producer warps per CTA.  With two, they take the CTA's edges in turn: with 4 + 2 warps per CTA and
 // two CTAs per SM every scheduler hosts two consumer warps and one (half-loaded) producer; with a single producer warp two
 // of the four schedulers carried 40 % more instructions than the others and set the pace.
-// FAST_NP (problem header): 2 from five stages on (the look-ahead is then a multiple of two), else 1.
+// FAST_NP (problem header): 2 from four stages on (the look-ahead is then a multiple of two), else 1.
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
     float x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
     float w[WN];
-    float w2[FAST_DBL ? WN : 4];     // second-order backward only: the row of Wdx
     float cy[NCY];                   // folded coefficients of this edge: cy[q] = sum_j C[i_q][j][k_q] * y[j], one per (i, k) pair
     float y[FAST_YPAD];
+    float cy2[FAST_FWD3 ? NCY : 4];  // fused second-order forward: coefficients folded with Y2
+    float y2[FAST_FWD3 ? FAST_YPAD : 4];
     float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
     long long edge, row, col;
     int first, last, pad0, pad1;
@@ -148,7 +157,7 @@ static_assert(sizeof(FastShared) <= 232448, "stages exceed shared memory");
 static_assert(FAST_KERNEL == 6 || sizeof(FastShared) <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
 // TMA look-ahead in edges.  One stage stays in hand: in the backward pass for the dX row that is still leaving shared
 // memory (FAST_S >= FAST_D + 2); the forward pass measured fastest two edges ahead (7.07 ms against 7.23 / 7.36 ms at 3 / 4).
-constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 5) ? 2 : 1)
+constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 4) ? 2 : 1)
                        : (FAST_NP == 2)   ? ((FAST_S - 2) & ~1)
                                           : ((FAST_S >= 4) ? FAST_S - 2 : 1);
 // FAST_XPC / FAST_GPC (problem header): registers per channel for an X / dX row and for a Z / G row
@@ -253,14 +262,22 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
             st.edge = e; st.row = row; st.col = col;
             st.first = (ia == 0) || (KIND == FAST_TP);   // consumers also compare rows; see fast_backward
             st.last = (ia == n - 1) || (row != nxt) || (KIND == FAST_TP);
-            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN * (FAST_DBL ? 2 : 1)) * sizeof(float)));
+            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN) * sizeof(float)));
             // weight rows are read once: they should leave the L2 before the sender rows, which neighbouring receivers reuse
             if (KIND == FAST_TP) tma_load_hint(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s], pol_stream);
             else tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
             tma_load_hint(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s], pol_stream);
-            if (FAST_DBL) tma_load_hint(st.w2, p.Wdx + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s], pol_stream);
+            // second-order backward: the row of Wdx is read by the consumers straight from global memory (a second staged
+            // weight row would leave room for three stages only); bring it into the L2 ahead of them
+            if (FAST_DBL && !FAST_FWD3) l2_prefetch(p.Wdx + e * WN, (unsigned)(WN * sizeof(float)));
+            if (FAST_FWD3) {
+                l2_prefetch(p.W2 + e * WN, (unsigned)(WN * sizeof(float)));
+                l2_prefetch(p.X2 + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)));
+            }
         }
         for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y[j], p.Y + e * L2_DIM + j);
+        if (FAST_FWD3)
+            for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y2[j], p.Y2 + e * L2_DIM + j);
         ldgsts_commit();
         return true;
     };
@@ -279,6 +296,12 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
 #pragma unroll
                 for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tab_c[t][m], st.y[tab_j[t][m]], v);
                 st.cy[q] = v;
+                if (FAST_FWD3) {
+                    float v2 = tab_c[t][0] * st.y2[tab_j[t][0]];
+#pragma unroll
+                    for (int m = 1; m < FAST_CYT; ++m) v2 = fmaf(tab_c[t][m], st.y2[tab_j[t][m]], v2);
+                    st.cy2[FAST_FWD3 ? q : 0] = v2;
+                }
             }
         }
         __syncwarp();
@@ -394,13 +417,33 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
             if constexpr ((GRP == 0 ? FP_FWD_NEEDS_X0[B] : FP_FWD_NEEDS_X1[B]) != 0) {
                 float xb[FAST_CH * B1::D];
                 block_load<B1>(st.x, u, xb);
+#if FAST_FWD3
+                float x2b[FAST_CH * B1::D];
+                {
+                    const float* x2row = p.X2 + st.col * L1_DIM;
+#pragma unroll
+                    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                        for (int i1 = 0; i1 < B1::D; ++i1)
+                            x2b[ch * B1::D + i1] = __ldg(x2row + feat_idx<B1::OFF, B1::MUL, B1::D>(chan(u, ch), i1));
+                }
+                const float4* cy4b = reinterpret_cast<const float4*>(st.cy2);
+                const float* w2row = p.W2 + st.edge * WN;
+#endif
                 static_for<0, NINS>([&](auto ic) {
                     constexpr int I = decltype(ic)::value;
                     using F = FIns<I>;
                     if constexpr (F::A == B && FP_INS_GF[I] == GRP) {
                         float wv[FAST_CH];
                         weight_load<F::WOFF>(st.w, u, wv);
+#if FAST_FWD3
+                        float w2v[FAST_CH];
+#pragma unroll
+                        for (int ch = 0; ch < FAST_CH; ++ch) w2v[ch] = __ldg(w2row + F::WOFF + chan(u, ch));
+                        F::fwd3(xb, x2b, cy4, cy4b, wv, w2v, acc + F::GO);
+#else
                         F::fwd(xb, cy4, wv, acc + F::GO);
+#endif
                     }
                 });
             }
@@ -517,6 +560,18 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
         for (int j = 0; j < FAST_NYP; ++j) dyr[j] = 0.f;
         const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
         float* dwrow = p.dW + e * WN;
+        // second-order backward: this thread's entries of the Wdx row, all requested now and used path by path
+        float wdxv[FAST_DBL ? FAST_CH * NINS : 1];
+        if (FAST_DBL) {
+            const float* wdxrow = p.Wdx + e * WN;
+            static_for<0, NINS>([&](auto ic) {
+                constexpr int I = decltype(ic)::value;
+                if constexpr (FP_INS_GB[I] == GRP) {
+#pragma unroll
+                    for (int ch = 0; ch < FAST_CH; ++ch) wdxv[FAST_DBL ? ch * NINS + I : 0] = __ldg(wdxrow + FIns<I>::WOFF + chan(u, ch));
+                }
+            });
+        }
         // Paths are taken input block by input block: one block of x and of dx is in registers at a time, and the
         // block's dx overwrites its x in the stage as soon as its paths are done.
         static_for<0, NB1>([&](auto bc) {
@@ -535,7 +590,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
 #pragma unroll
                         for (int ch = 0; ch < FAST_CH; ++ch) {
                             wv[ch] = st.w[F::WOFF + chan(u, ch)];
-                            wx[ch] = FAST_DBL ? st.w2[F::WOFF + chan(u, ch)] : wv[ch];
+                            wx[ch] = FAST_DBL ? wdxv[FAST_DBL ? ch * NINS + I : 0] : wv[ch];
                         }
                         F::bwd(xb, g + F::GO, cy4, wv, wx, dxb, dyr + F::Y0, dw);
 #pragma unroll

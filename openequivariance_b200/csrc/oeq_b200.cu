@@ -93,11 +93,13 @@ struct Desc {
     int fast_ng = 1;     // thread groups sharing an edge
     int fast_ch = 1;     // channels carried by one consumer thread
     size_t fast_smem = 0;
-    int fast_S2 = 0;         // stages of the second-order backward kernels (their stage carries a second weight row)
+    int fast_S2 = 0;         // stages of the second-order backward kernels
     size_t fast_smem2 = 0;
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
+    int fast_S4 = 0;         // stages of the fused second-order forward (its stage carries a second coefficient table)
+    size_t fast_smem4 = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
 };
 
@@ -180,7 +182,7 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
             const int ch = (!g_single_group && U % 64 == 0 && d.ins.size() >= 2) ? 2 : 1;
             const int ng = ch == 2 ? 2 : 1;
             const int nthreads = ng * U / ch;
-            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (nthreads / 32) * nyp) + 56) + 15) & ~(size_t)15;
+            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (nthreads / 32) * nyp) + 72) + 15) & ~(size_t)15;
             int ctas = 256 / U;
             ctas = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas);
             while (ctas > 1 && ctas * (nthreads + 32) * (ch == 2 ? 168 : 128) > 65536) --ctas;   // registers per thread
@@ -195,11 +197,16 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 d.fast = true;
                 d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
                 d.fast_smem = (size_t)S * (stage + 24) + 128;
-                const size_t stage2 = stage + 4 * (size_t)d.wn;
+                const size_t stage2 = stage;   // the second weight row of these passes is not staged
                 int S2 = (int)((232448 / ctas - 1024 - 256) / (stage2 + 24));
                 if (S2 > 6) S2 = 6;
                 d.fast_S2 = S2;    // < 3: second-order passes fall back to the general kernels
                 d.fast_smem2 = (size_t)S2 * (stage2 + 24) + 128;
+                const size_t stage4 = stage + 4 * (size_t)(ncy + ((d.dim[1] + 3) & ~3));
+                int S4 = (int)((232448 / ctas - 1024 - 256) / (stage4 + 24));
+                if (S4 > 6) S4 = 6;
+                d.fast_S4 = S4;    // < 3: the second-order forward is composed of three passes
+                d.fast_smem4 = (size_t)S4 * (stage4 + 24) + 128;
                 int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 24));
                 if (S3 > 6) S3 = 6;
                 d.fast_S3 = S3;    // < 2: atomic forward falls back to the general kernel
@@ -293,8 +300,8 @@ std::string emit_header(const Desc& d) {
 
 // Tables and per-instruction register kernels for the channel-parallel family (kernels/fast_uvu.cuh).
 // cy[i,k] = sum_j C[i,j,k] y[j] is formed once per edge by the producer warp; the consumer code below reads it as float4.
-// Producer warps of a kernel with `stages` stages: two from five stages on (its look-ahead is then a multiple of two).
-int fast_producers(int stages) { return (stages >= 5 && !g_single_producer) ? 2 : 1; }
+// Producer warps of a kernel with `stages` stages: two from four stages on (its look-ahead is then a multiple of two).
+int fast_producers(int stages) { return (stages >= 4 && !g_single_producer) ? 2 : 1; }
 
 std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_t smem_bytes) {
     std::ostringstream s;
@@ -356,6 +363,19 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
             for (int k = 0; k < D3; ++k) s << "      ac[" << k << "] = fmaf(wc, t" << k << ", ac[" << k << "]);\n";
         }
         s << "    }\n  }\n";
+        // ---- fused second-order forward: acc += cy(y) . (w x2 + w2 x) + cy(y2) . (w x)
+        if (dbl) {
+            s << "  static OEQ_DEV void fwd3(const float* x, const float* x2, const float4* cy, const float4* cyb, const float* w, const float* w2, float* acc) {\n";
+            for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "]; const float4 b" << q << " = cyb[CY4 + " << q << "];\n";
+            s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
+            s << "      const float* xc = x + ch * D1; const float* yc = x2 + ch * D1; float* ac = acc + ch * FAST_GPC; const float wc = w[ch]; const float vc = w2[ch];\n";
+            for (int i = 0; i < D1; ++i)
+                s << "      const float xa" << i << " = fmaf(vc, xc[" << i << "], wc * yc[" << i << "]); const float xb" << i << " = wc * xc[" << i << "];\n";
+            auto Bc = [&](int z) { std::ostringstream t; t << "b" << (z / 4) << "." << comp[z % 4]; return t.str(); };
+            for (int z = 0; z < np; ++z)
+                s << "      ac[" << P[z].k << "] = fmaf(" << C(z) << ", xa" << P[z].i << ", fmaf(" << Bc(z) << ", xb" << P[z].i << ", ac[" << P[z].k << "]));\n";
+            s << "    }\n  }\n";
+        }
         // ---- backward
         const bool scale_g = D3 <= D1;
         const int nqv = scale_g ? D3 : D1;
@@ -501,11 +521,12 @@ enum Family {
     FAM_FAST_SCATTER,
     FAM_FAST_BWD2_TP, FAM_FAST_BWD2_DET, FAM_FAST_BWD2_ATOMIC,   // second-order variants of the backward kernels
     FAM_UVW_TC,                                                  // tcgen05 'uvw' forward
+    FAM_FAST_FWD3_TP, FAM_FAST_FWD3_DET,                         // fused second-order forward (three terms in one pass)
     FAM_COUNT
 };
 const char* const kFamilyNames[FAM_COUNT] = {"generic", "fast_fwd_tp", "fast_fwd_det", "fast_fwd_atomic", "fast_bwd_tp",
                                              "fast_bwd_det", "fast_bwd_atomic", "fast_scatter", "fast_bwd2_tp",
-                                             "fast_bwd2_det", "fast_bwd2_atomic", "uvw_tc"};
+                                             "fast_bwd2_det", "fast_bwd2_atomic", "uvw_tc", "fast_fwd3_tp", "fast_fwd3_det"};
 const char* family_name(int f) { return (f >= 0 && f < FAM_COUNT) ? kFamilyNames[f] : "?"; }
 int family_from_name(const std::string& n) {
     for (int f = 0; f < FAM_COUNT; ++f)
@@ -527,13 +548,14 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         // Forward kernels carry two channels per thread in two block-owning groups (their code is small enough to stay
         // in the instruction cache); the backward kernels, three times larger, keep one channel per thread and one
         // code stream, which measured faster than the split variants (those stalled on instruction fetch).
-        const bool fwd = fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC;
-        const bool dbl = fam >= FAM_FAST_BWD2_TP;
-        const int stages = dbl ? d.fast_S2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
-        const size_t smem = dbl ? d.fast_smem2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
+        const bool fwd3 = fam == FAM_FAST_FWD3_TP || fam == FAM_FAST_FWD3_DET;
+        const bool fwd = fwd3 || (fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC);
+        const bool dbl = fwd3 || (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC);
+        const int stages = fwd3 ? d.fast_S4 : dbl ? d.fast_S2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
+        const size_t smem = fwd3 ? d.fast_smem4 : dbl ? d.fast_smem2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
         src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, smem);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
-        src += "#define FAST_KERNEL " + std::to_string(dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
+        src += "#define FAST_KERNEL " + std::to_string(fwd3 ? fam - FAM_FAST_FWD3_TP : dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
         src += K_FAST_UVU;
     }
@@ -776,6 +798,7 @@ struct FastParams {
     const void* Wdx;   // second-order backward: weights that scale dX (W itself scales the dY products)
     int accum;         // add to the outputs instead of overwriting them
     int pad;
+    const void* X2; const void* Y2; const void* W2;   // fused second-order forward
 };
 
 // One host-mapped status word per device: kernels store a non-zero code when a bounded wait runs out.
@@ -824,8 +847,9 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (status_override) p.status = status_override;
     else if ((rc = status_word(&p.status))) return rc;
     Program* prog;
-    const size_t smem = dbl ? d.fast_smem2 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
-    if ((rc = get_program(e, dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel, &prog))) return rc;
+    const bool fwd3 = dbl && kernel < 2;   // fused second-order forward (batch and sorted-convolution variants)
+    const size_t smem = fwd3 ? d.fast_smem4 : dbl ? d.fast_smem2 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
+    if ((rc = get_program(e, fwd3 ? FAM_FAST_FWD3_TP + kernel : dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel, &prog))) return rc;
     cudaKernel_t k;
     if ((rc = get_kernel(prog, names[kernel], smem, &k))) return rc;
     long long grid = (long long)sm_count() * d.fast_ctas;
@@ -833,7 +857,7 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (grid > work) grid = work;
     void* args[] = {&p};
     const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
-    const int producers = fast_producers(dbl ? d.fast_S2 : (kernel == 2 ? d.fast_S3 : d.fast_S));
+    const int producers = fast_producers(fwd3 ? d.fast_S4 : dbl ? d.fast_S2 : (kernel == 2 ? d.fast_S3 : d.fast_S));
     return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
 
@@ -980,6 +1004,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
         else if (fam != FAM_GENERIC && !d.fast) continue;
         if (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC && d.fast_S2 < 3) continue;
         if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;
+        if ((fam == FAM_FAST_FWD3_TP || fam == FAM_FAST_FWD3_DET) && d.fast_S4 < 3) continue;
         std::string cubin;
         int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
         if (rc) return -rc;
@@ -1044,12 +1069,18 @@ int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int6
     if (use_fast(d) && d.fast_S2 >= 3 && aligned16({x, x2, W, W2, dx})) {
         // same decomposition on the channel-parallel kernels: three forward passes (store, add, add) and two
         // second-order backward passes (the second adds); see the general path below for the algebra
-        FastParams f{x2, y, W, nullptr, dg, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
-        if ((rc = fast_launch(e, 0, f, st))) return rc;
-        f.X = x; f.Y = y2; f.accum = 1;
-        if ((rc = fast_launch(e, 0, f, st))) return rc;
-        f.Y = y; f.W = W2;
-        if ((rc = fast_launch(e, 0, f, st))) return rc;
+        if (d.fast_S4 >= 3 && aligned16({dg})) {   // all three terms of dg in one pass
+            FastParams f{x, y, W, nullptr, dg, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
+            f.X2 = x2; f.Y2 = y2; f.W2 = W2;
+            if ((rc = fast_launch(e, 0, f, st, nullptr, true))) return rc;
+        } else {
+            FastParams f{x2, y, W, nullptr, dg, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
+            if ((rc = fast_launch(e, 0, f, st))) return rc;
+            f.X = x; f.Y = y2; f.accum = 1;
+            if ((rc = fast_launch(e, 0, f, st))) return rc;
+            f.Y = y; f.W = W2;
+            if ((rc = fast_launch(e, 0, f, st))) return rc;
+        }
         FastParams b{x2, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
         b.Wdx = W2;
         if ((rc = fast_launch(e, 3, b, st, nullptr, true))) return rc;
@@ -1199,12 +1230,18 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
             CUDA_TRY(cudaMemsetAsync(dG, 0, n_nodes * d.dim[2] * d.elt(), st));
             CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
         }
-        FastParams f{X2, Y, W, nullptr, dG, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
-        if ((rc = fast_launch(e, kf, f, st))) return rc;
-        f.X = X; f.Y = Y2; f.accum = 1;
-        if ((rc = fast_launch(e, kf, f, st))) return rc;
-        f.Y = Y; f.W = W2;
-        if ((rc = fast_launch(e, kf, f, st))) return rc;
+        if (d.det && d.fast_S4 >= 3) {   // all three terms of dG in one pass
+            FastParams f{X, Y, W, nullptr, dG, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+            f.X2 = X2; f.Y2 = Y2; f.W2 = W2;
+            if ((rc = fast_launch(e, kf, f, st, nullptr, true))) return rc;
+        } else {
+            FastParams f{X2, Y, W, nullptr, dG, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+            if ((rc = fast_launch(e, kf, f, st))) return rc;
+            f.X = X; f.Y = Y2; f.accum = 1;
+            if ((rc = fast_launch(e, kf, f, st))) return rc;
+            f.Y = Y; f.W = W2;
+            if ((rc = fast_launch(e, kf, f, st))) return rc;
+        }
         FastParams b{X2, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
         b.Wdx = W2;
         if ((rc = fast_launch(e, kb, b, st, nullptr, true))) return rc;
