@@ -34,12 +34,14 @@ struct FastParams {
     const IDX* rows; const IDX* cols;
     long long N; long long E;
     int* status;
-    const float* Wdx;   // second-order backward: weights that scale dX (W scales the dY products)
-    int accum;          // add to the outputs instead of overwriting them
+    const float* Wdx;   // unused (kept for layout compatibility with the host structure)
+    int accum;          // forward kernels: add to the output rows instead of overwriting them
     int pad;
-    const float* X2; const float* Y2; const float* W2;   // fused second-order forward: the cotangents of (dX, dY, dW)
+    const float* X2; const float* Y2; const float* W2;   // second-order kernels: the cotangents of (dX, dY, dW)
 };
-// Fused second-order forward (FAST_DBL on a forward kernel): z = F(X2, Y, W) + F(X, Y, W2) + F(X, Y2, W) in one pass.
+// Second-order kernels (FAST_DBL), one pass each:
+//   forward   z = F(X2, Y, W) + F(X, Y, W2) + F(X, Y2, W)
+//   backward  (dX, dY, dW) = Bwd(X2, Y, W | g) with dX scaled by W2  +  Bwd(X, Y2, W2 | g) with dX scaled by W
 // X and W are staged as usual; the rows of X2 and W2 are read by the consumers straight from global memory (the
 // producer brings them into the L2 ahead), Y2 is folded into a second coefficient table.
 #define FAST_FWD3 (FAST_DBL && FAST_KERNEL <= 2)
@@ -135,8 +137,8 @@ struct __align__(16) FastStage {
     float w[WN];
     float cy[NCY];                   // folded coefficients of this edge: cy[q] = sum_j C[i_q][j][k_q] * y[j], one per (i, k) pair
     float y[FAST_YPAD];
-    float cy2[FAST_FWD3 ? NCY : 4];  // fused second-order forward: coefficients folded with Y2
-    float y2[FAST_FWD3 ? FAST_YPAD : 4];
+    float cy2[FAST_DBL ? NCY : 4];   // second-order kernels: coefficients folded with Y2
+    float y2[FAST_DBL ? FAST_YPAD : 4];
     float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
     long long edge, row, col;
     int first, last, pad0, pad1;
@@ -267,16 +269,15 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
             if (KIND == FAST_TP) tma_load_hint(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s], pol_stream);
             else tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
             tma_load_hint(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s], pol_stream);
-            // second-order backward: the row of Wdx is read by the consumers straight from global memory (a second staged
-            // weight row would leave room for three stages only); bring it into the L2 ahead of them
-            if (FAST_DBL && !FAST_FWD3) l2_prefetch(p.Wdx + e * WN, (unsigned)(WN * sizeof(float)));
-            if (FAST_FWD3) {
+            // second-order kernels: the rows of X2 and W2 are read by the consumers straight from global memory (staging
+            // them too would leave room for two stages only); bring them into the L2 ahead of the consumers
+            if (FAST_DBL) {
                 l2_prefetch(p.W2 + e * WN, (unsigned)(WN * sizeof(float)));
                 l2_prefetch(p.X2 + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)));
             }
         }
         for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y[j], p.Y + e * L2_DIM + j);
-        if (FAST_FWD3)
+        if (FAST_DBL)
             for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y2[j], p.Y2 + e * L2_DIM + j);
         ldgsts_commit();
         return true;
@@ -296,11 +297,11 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
 #pragma unroll
                 for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tab_c[t][m], st.y[tab_j[t][m]], v);
                 st.cy[q] = v;
-                if (FAST_FWD3) {
+                if (FAST_DBL) {
                     float v2 = tab_c[t][0] * st.y2[tab_j[t][0]];
 #pragma unroll
                     for (int m = 1; m < FAST_CYT; ++m) v2 = fmaf(tab_c[t][m], st.y2[tab_j[t][m]], v2);
-                    st.cy2[FAST_FWD3 ? q : 0] = v2;
+                    st.cy2[FAST_DBL ? q : 0] = v2;
                 }
             }
         }
@@ -318,13 +319,12 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
 #pragma unroll
             for (int w = 0; w < FAST_NCW; ++w) tot += st.dyp[w][lane];
             float* dst = p.dY + st.edge * L2_DIM + lane;
-            *dst = (FAST_DBL && p.accum) ? *dst + tot : tot;   // only second-order passes add to their outputs
+            *dst = tot;
         }
         if (lane == 0) {
-            // each per-edge row has a single writer, so adding to it (second pass of a double backward) stays deterministic
             float* row = (KIND == FAST_TP) ? p.dX + st.edge * L1_DIM : (KIND == FAST_DET) ? p.scratch + st.edge * L1_DIM
                                                                                         : p.dX + st.col * L1_DIM;
-            if (KIND == FAST_ATOMIC || (FAST_DBL && p.accum)) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
+            if (KIND == FAST_ATOMIC) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
             else tma_store_hint(row, st.x, (unsigned)(L1_DIM * sizeof(float)), pol_stream);
         }
         tma_commit();
@@ -560,10 +560,11 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
         for (int j = 0; j < FAST_NYP; ++j) dyr[j] = 0.f;
         const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
         float* dwrow = p.dW + e * WN;
-        // second-order backward: this thread's entries of the Wdx row, all requested now and used path by path
+        // second-order backward: this thread's entries of the W2 row, all requested now and used path by path
         float wdxv[FAST_DBL ? FAST_CH * NINS : 1];
+        const float4* cy4b = reinterpret_cast<const float4*>(st.cy2);
         if (FAST_DBL) {
-            const float* wdxrow = p.Wdx + e * WN;
+            const float* wdxrow = p.W2 + e * WN;
             static_for<0, NINS>([&](auto ic) {
                 constexpr int I = decltype(ic)::value;
                 if constexpr (FP_INS_GB[I] == GRP) {
@@ -582,6 +583,17 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                 block_load<B1>(st.x, u, xb);
 #pragma unroll
                 for (int q = 0; q < FAST_CH * B1::D; ++q) dxb[q] = 0.f;
+#if FAST_DBL
+                float x2b[FAST_CH * B1::D];
+                {
+                    const float* x2row = p.X2 + st.col * L1_DIM;
+#pragma unroll
+                    for (int ch = 0; ch < FAST_CH; ++ch)
+#pragma unroll
+                        for (int i1 = 0; i1 < B1::D; ++i1)
+                            x2b[ch * B1::D + i1] = __ldg(x2row + feat_idx<B1::OFF, B1::MUL, B1::D>(chan(u, ch), i1));
+                }
+#endif
                 static_for<0, NINS>([&](auto ic) {
                     constexpr int I = decltype(ic)::value;
                     using F = FIns<I>;
@@ -592,13 +604,13 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                             wv[ch] = st.w[F::WOFF + chan(u, ch)];
                             wx[ch] = FAST_DBL ? wdxv[FAST_DBL ? ch * NINS + I : 0] : wv[ch];
                         }
+#if FAST_DBL
+                        F::bwd3(xb, x2b, g + F::GO, cy4, cy4b, wv, wx, dxb, dyr + F::Y0, dw);
+#else
                         F::bwd(xb, g + F::GO, cy4, wv, wx, dxb, dyr + F::Y0, dw);
+#endif
 #pragma unroll
-                        for (int ch = 0; ch < FAST_CH; ++ch) {
-                            float* dst = dwrow + F::WOFF + chan(u, ch);
-                            if (FAST_DBL && p.accum) *dst += dw[ch];
-                            else __stcs(dst, dw[ch]);   // written once, not read again by this kernel
-                        }
+                        for (int ch = 0; ch < FAST_CH; ++ch) __stcs(dwrow + F::WOFF + chan(u, ch), dw[ch]);   // written once, not read again here
                     }
                 });
                 block_store<B1, false, false>(st.x, u, [&](int ch, int i1) { return dxb[ch * B1::D + i1]; });

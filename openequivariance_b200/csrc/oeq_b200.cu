@@ -93,12 +93,10 @@ struct Desc {
     int fast_ng = 1;     // thread groups sharing an edge
     int fast_ch = 1;     // channels carried by one consumer thread
     size_t fast_smem = 0;
-    int fast_S2 = 0;         // stages of the second-order backward kernels
-    size_t fast_smem2 = 0;
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
-    int fast_S4 = 0;         // stages of the fused second-order forward (its stage carries a second coefficient table)
+    int fast_S4 = 0;         // stages of the second-order kernels (their stage carries a second coefficient table)
     size_t fast_smem4 = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
 };
@@ -197,15 +195,10 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 d.fast = true;
                 d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
                 d.fast_smem = (size_t)S * (stage + 24) + 128;
-                const size_t stage2 = stage;   // the second weight row of these passes is not staged
-                int S2 = (int)((232448 / ctas - 1024 - 256) / (stage2 + 24));
-                if (S2 > 6) S2 = 6;
-                d.fast_S2 = S2;    // < 3: second-order passes fall back to the general kernels
-                d.fast_smem2 = (size_t)S2 * (stage2 + 24) + 128;
                 const size_t stage4 = stage + 4 * (size_t)(ncy + ((d.dim[1] + 3) & ~3));
                 int S4 = (int)((232448 / ctas - 1024 - 256) / (stage4 + 24));
                 if (S4 > 6) S4 = 6;
-                d.fast_S4 = S4;    // < 3: the second-order forward is composed of three passes
+                d.fast_S4 = S4;    // < 3: second-order passes run on the general kernels
                 d.fast_smem4 = (size_t)S4 * (stage4 + 24) + 128;
                 int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 24));
                 if (S3 > 6) S3 = 6;
@@ -411,7 +404,41 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
             s << " }\n";
             z = m;
         }
-        s << "  }\n};\n";
+        s << "  }\n";
+        // ---- fused second-order backward: s = cy(y).g and t = cy(y2).g;  dx += w2 s + w t;  dW = x2.s + x.t;
+        //      dy[j] += C (w x2 + w2 x)[i] g[k]
+        if (dbl) {
+            s << "  static OEQ_DEV void bwd3(const float* x, const float* x2, const float* g, const float4* cy, const float4* cyb, const float* w, const float* w2, float* dx, float* dy, float* dw) {\n";
+            for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "]; const float4 b" << q << " = cyb[CY4 + " << q << "];\n";
+            auto Bc = [&](int z) { std::ostringstream t; t << "b" << (z / 4) << "." << comp[z % 4]; return t.str(); };
+            s << "    float qv[FAST_CH][" << D1 << "];\n";
+            s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
+            s << "      const float* xc = x + ch * D1; const float* yc = x2 + ch * D1; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * D1; const float wc = w[ch]; const float vc = w2[ch];\n";
+            for (int i = 0; i < D1; ++i) s << "      float s" << i << " = 0.f, t" << i << " = 0.f;\n";
+            for (int z = 0; z < np; ++z)
+                s << "      s" << P[z].i << " = fmaf(" << C(z) << ", gc[" << P[z].k << "], s" << P[z].i << "); t" << P[z].i << " = fmaf("
+                  << Bc(z) << ", gc[" << P[z].k << "], t" << P[z].i << ");\n";
+            s << "      float dwv = 0.f;\n";
+            for (int i = 0; i < D1; ++i) {
+                s << "      dwv = fmaf(yc[" << i << "], s" << i << ", fmaf(xc[" << i << "], t" << i << ", dwv));\n";
+                s << "      dxc[" << i << "] = fmaf(vc, s" << i << ", fmaf(wc, t" << i << ", dxc[" << i << "]));\n";
+                s << "      qv[ch][" << i << "] = fmaf(vc, xc[" << i << "], wc * yc[" << i << "]);\n";
+            }
+            s << "      dw[ch] = dwv;\n    }\n";
+            for (size_t z = 0; z < byik.size();) {
+                size_t m = z;
+                s << "    { float pr = 0.f;\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = fmaf(qv[ch][" << byik[z].i
+                  << "], g[ch * FAST_GPC + " << byik[z].k << "], pr);\n     ";
+                while (m < byik.size() && byik[m].i == byik[z].i && byik[m].k == byik[z].k) {
+                    s << " dy[" << byik[m].j << "] = fmaf(" << hexf(byik[m].c) << "f, pr, dy[" << byik[m].j << "]);";
+                    ++m;
+                }
+                s << " }\n";
+                z = m;
+            }
+            s << "  }\n";
+        }
+        s << "};\n";
     }
     // Thread groups: with FAST_NG = 2 two sets of FU threads share an edge.  Backward: input blocks are dealt to the
     // groups (longest-processing-time first on CG nonzeros) so every dX block has one writer; forward: output blocks.
@@ -551,8 +578,8 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         const bool fwd3 = fam == FAM_FAST_FWD3_TP || fam == FAM_FAST_FWD3_DET;
         const bool fwd = fwd3 || (fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC);
         const bool dbl = fwd3 || (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC);
-        const int stages = fwd3 ? d.fast_S4 : dbl ? d.fast_S2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
-        const size_t smem = fwd3 ? d.fast_smem4 : dbl ? d.fast_smem2 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
+        const int stages = dbl ? d.fast_S4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
+        const size_t smem = dbl ? d.fast_smem4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
         src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, smem);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(fwd3 ? fam - FAM_FAST_FWD3_TP : dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
@@ -848,7 +875,7 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     else if ((rc = status_word(&p.status))) return rc;
     Program* prog;
     const bool fwd3 = dbl && kernel < 2;   // fused second-order forward (batch and sorted-convolution variants)
-    const size_t smem = fwd3 ? d.fast_smem4 : dbl ? d.fast_smem2 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
+    const size_t smem = dbl ? d.fast_smem4 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
     if ((rc = get_program(e, fwd3 ? FAM_FAST_FWD3_TP + kernel : dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel, &prog))) return rc;
     cudaKernel_t k;
     if ((rc = get_kernel(prog, names[kernel], smem, &k))) return rc;
@@ -857,7 +884,7 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     if (grid > work) grid = work;
     void* args[] = {&p};
     const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
-    const int producers = fast_producers(fwd3 ? d.fast_S4 : dbl ? d.fast_S2 : (kernel == 2 ? d.fast_S3 : d.fast_S));
+    const int producers = fast_producers(dbl ? d.fast_S4 : (kernel == 2 ? d.fast_S3 : d.fast_S));
     return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
 
@@ -1002,7 +1029,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
         if (fam == FAM_UVW_TC) { if (!d.tc) continue; }
         else if (fam != FAM_GENERIC && !d.fast) continue;
-        if (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC && d.fast_S2 < 3) continue;
+        if (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC && d.fast_S4 < 3) continue;
         if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;
         if ((fam == FAM_FAST_FWD3_TP || fam == FAM_FAST_FWD3_DET) && d.fast_S4 < 3) continue;
         std::string cubin;
@@ -1066,7 +1093,7 @@ int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int6
     if (d.shared) CUDA_TRY(cudaMemsetAsync(dW, 0, d.wn * d.elt(), st));
     if (batch == 0) return OEQB_OK;
     int rc;
-    if (use_fast(d) && d.fast_S2 >= 3 && aligned16({x, x2, W, W2, dx})) {
+    if (use_fast(d) && d.fast_S4 >= 3 && aligned16({x, x2, W, W2, dx})) {
         // same decomposition on the channel-parallel kernels: three forward passes (store, add, add) and two
         // second-order backward passes (the second adds); see the general path below for the algebra
         if (d.fast_S4 >= 3 && aligned16({dg})) {   // all three terms of dg in one pass
@@ -1081,10 +1108,8 @@ int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int6
             f.Y = y; f.W = W2;
             if ((rc = fast_launch(e, 0, f, st))) return rc;
         }
-        FastParams b{x2, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
-        b.Wdx = W2;
-        if ((rc = fast_launch(e, 3, b, st, nullptr, true))) return rc;
-        b.X = x; b.Y = y2; b.W = W2; b.Wdx = W; b.accum = 1;
+        FastParams b{x, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
+        b.X2 = x2; b.Y2 = y2; b.W2 = W2;   // both second-order backward terms in one pass
         return fast_launch(e, 3, b, st, nullptr, true);
     }
     CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
@@ -1111,7 +1136,7 @@ int64_t oeqb_conv_workspace_bytes(const void* desc, size_t desc_len, int64_t key
     if (int rc = get_entry(desc, desc_len, key, &e)) return -(int64_t)rc;
     const Desc& d = e->d;
     // Deterministic backward on the channel-parallel path: one dX row per edge plus the sender offsets.
-    if ((direction == 1 || (direction == 2 && d.fast_S2 >= 3)) && d.conv && d.det && use_fast(d))
+    if ((direction == 1 || (direction == 2 && d.fast_S4 >= 3)) && d.conv && d.det && use_fast(d))
         return (int64_t)(round_up((size_t)n_edges * d.dim[0] * d.elt()) + round_up((size_t)(n_nodes + 1) * 8));
     return 0;
 }
@@ -1215,7 +1240,7 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
         if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
     }
     int rc;
-    if (use_fast(d) && d.fast_S2 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, dX, dG, workspace})) {
+    if (use_fast(d) && d.fast_S4 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, dX, dG, workspace})) {
         // channel-parallel kernels: dG from three forward passes, (dX, dY, dW) from two second-order backward passes
         const int kf = d.det ? 1 : 2, kb = d.det ? 4 : 5;
         void* colptr = nullptr;
@@ -1242,10 +1267,8 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
             f.Y = Y; f.W = W2;
             if ((rc = fast_launch(e, kf, f, st))) return rc;
         }
-        FastParams b{X2, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
-        b.Wdx = W2;
-        if ((rc = fast_launch(e, kb, b, st, nullptr, true))) return rc;
-        b.X = X; b.Y = Y2; b.W = W2; b.Wdx = W; b.accum = 1;
+        FastParams b{X, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
+        b.X2 = X2; b.Y2 = Y2; b.W2 = W2;   // both second-order backward terms in one pass
         if ((rc = fast_launch(e, kb, b, st, nullptr, true))) return rc;
         if (d.det) return fast_scatter(e, workspace, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
         return OEQB_OK;
