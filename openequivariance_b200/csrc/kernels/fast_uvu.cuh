@@ -34,7 +34,6 @@ struct FastParams {
     const IDX* rows; const IDX* cols;
     long long N; long long E;
     int* status;
-    const float* Wdx;   // unused (kept for layout compatibility with the host structure)
     int accum;          // forward kernels: add to the output rows instead of overwriting them
     int pad;
     const float* X2; const float* Y2; const float* W2;   // second-order kernels: the cotangents of (dX, dY, dW)

@@ -822,8 +822,7 @@ struct FastParams {
     const void* rows; const void* cols;
     long long N; long long E;
     int* status;
-    const void* Wdx;   // second-order backward: weights that scale dX (W itself scales the dY products)
-    int accum;         // add to the outputs instead of overwriting them
+    int accum;         // forward kernels: add to the output rows instead of overwriting them
     int pad;
     const void* X2; const void* Y2; const void* W2;   // fused second-order forward
 };
