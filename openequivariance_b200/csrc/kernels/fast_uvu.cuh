@@ -228,7 +228,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         OEQ_DEV void next() { s += FAST_NP; if (s >= FAST_S) { s -= FAST_S; par ^= 1u; } }
     };
     RingPos pos_a{pid, 0u}, pos_b{pid, 0u}, pos_c{pid, 0u};   // this producer's edges are pid, pid + FAST_NP, ...
-    long long cur_blk = -1;
+    long long cur_blk = -1, prefetched_row = -1;
 
     auto phase_a = [&](long long ia) -> bool {   // claim a stage for edge ia and start its copies
         const int s = pos_a.s;
@@ -260,6 +260,11 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
             }
         }
         if (lane == 0) {
+            if (BWD && KIND != FAST_TP && row != prefetched_row) {
+                // a receiver the consumers will reach in a few edges: bring its gradient row into the L2 now
+                l2_prefetch(p.G + row * L3_DIM, (unsigned)(L3_DIM * sizeof(float)));
+                prefetched_row = row;
+            }
             st.edge = e; st.row = row; st.col = col;
             st.first = (ia == 0) || (KIND == FAST_TP);   // consumers also compare rows; see fast_backward
             st.last = (ia == n - 1) || (row != nxt) || (KIND == FAST_TP);

@@ -1194,7 +1194,7 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, dY, dW, rows, cols}, "oeqb_conv_backward")) return rc;
     }
-    const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W, dX, workspace});
+    const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W, G, dX, workspace});
     if (d.det && fast) {
         const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
         const size_t need = scratch_bytes + round_up((size_t)(n_nodes + 1) * 8);
@@ -1239,7 +1239,7 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
         if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
     }
     int rc;
-    if (use_fast(d) && d.fast_S4 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, dX, dG, workspace})) {
+    if (use_fast(d) && d.fast_S4 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, G, dX, dG, workspace})) {
         // channel-parallel kernels: dG from three forward passes, (dX, dY, dW) from two second-order backward passes
         const int kf = d.det ? 1 : 2, kb = d.det ? 4 : 5;
         void* colptr = nullptr;
@@ -1322,8 +1322,8 @@ int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, i
                                  "with a caller-provided workspace",
                     need, (long long)n_edges, (long long)d.dim[0], (long long)n_nodes + 1, (size_t)OEQB_NOALLOC_SCRATCH_BYTES);
     if (int rc = check_ptrs({X, Y, W, G, dX, dY, dW, rows, cols}, "oeqb_conv_backward_noalloc")) return rc;
-    if (!aligned16({X, W, dX}))
-        return fail(OEQB_EINVAL, "oeqb_conv_backward_noalloc: X, W and dX must be 16-byte aligned");
+    if (!aligned16({X, W, G, dX}))
+        return fail(OEQB_EINVAL, "oeqb_conv_backward_noalloc: X, W, G and dX must be 16-byte aligned");
     void* base = nullptr;
     if (int rc = noalloc_scratch(&base)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
