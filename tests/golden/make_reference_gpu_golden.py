@@ -7,7 +7,7 @@ The reference checkout cannot travel to a GPU machine as a dependency of the tes
     cp -r <reference>/openequivariance/openequivariance baseline/_ref/
     # on the GPU machine, from the repository root
     TORCH_EXTENSIONS_DIR=$PWD/baseline/_ref/_torch_ext OEQ_JIT_EXTENSION=1 PYTHONPATH=$PWD/baseline/_ref:$PWD \
-        python tests/golden/make_reference_gpu_golden.py --out gpurun_out/reference_gpu.npz [--bench]
+        python tests/golden/make_reference_gpu_golden.py --out out/reference_gpu.npz [--bench]
 
 and the resulting ``reference_gpu.npz`` is committed next to this file.  Inputs are seeded; weights are stored in e3nn
 order (the reference's ``reorder_weights_from_e3nn`` is applied before its kernels run, ``reorder_weights_to_e3nn``
@@ -147,7 +147,7 @@ def bench(n_nodes, steps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/reference_gpu.npz")
+    ap.add_argument("--out", default="out/reference_gpu.npz")
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--nodes", type=int, default=50000)
     ap.add_argument("--steps", type=int, default=5)
