@@ -160,6 +160,8 @@ def main():
     for name, problem, batch in cases():
         run_tp(name, problem, batch, store)
     run_conv(store)
+    import os
+    os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
     np.savez_compressed(args.out, **{k.replace("/", "__"): v for k, v in store.items()})
     print("fixtures:", len(store), "arrays ->", args.out)
     if args.bench:
