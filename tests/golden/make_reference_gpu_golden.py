@@ -145,10 +145,61 @@ def bench(n_nodes, steps):
     return results
 
 
+def bench_tp(steps):
+    """Reference kernels on the two batched tensor-product configurations (same shapes and input distributions as
+    ``bench.py --workload tp_uvu / tp_uvw``): forward, backward, double backward, median of ``steps`` CUDA-event timings with
+    a 256 MB buffer written between iterations."""
+    import openequivariance as oeq
+    from openequivariance.benchmark.problems import ChannelwiseTPP, FullyConnectedTPProblem
+    dev = torch.device("cuda", 0)
+    ops = torch.ops.libtorch_tp_jit
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+    feats = "128x0e+128x1o+128x2e+128x3o"
+    ir = "32x0e+32x0o+32x1e+32x1o+32x2e+32x2o"
+    cases = {
+        "tp_uvu": (ChannelwiseTPP(feats, "1x0e+1x1o+1x2e+1x3o", feats), 200000),
+        "tp_uvw": (FullyConnectedTPProblem(ir, "1x0e+1x1o+1x2e", ir, shared_weights=True, internal_weights=False), 50000),
+    }
+    out = {}
+    for name, (problem, B) in cases.items():
+        gen = torch.Generator(device=dev).manual_seed(5)
+        mk = lambda *shape: torch.randn(*shape, device=dev, generator=gen)
+        wshape = (problem.weight_numel,) if problem.shared_weights else (B, problem.weight_numel)
+        X, Y, W = mk(B, problem.irreps_in1.dim), mk(B, problem.irreps_in2.dim), mk(*wshape)
+        G, X2, Y2, W2 = mk(B, problem.irreps_out.dim), mk(B, problem.irreps_in1.dim), mk(B, problem.irreps_in2.dim), mk(*wshape)
+        tp = oeq.TensorProduct(problem)
+        passes = {
+            "forward": lambda: ops.jit_tp_forward(tp.kernel, tp.hash, X, Y, W, tp.L3_dim),
+            "backward": lambda: ops.jit_tp_backward(tp.kernel, tp.hash, X, Y, W, G),
+            "double_backward": lambda: ops.jit_tp_double_backward(tp.kernel, tp.hash, X, Y, W, G, X2, Y2, W2),
+        }
+        res = {}
+        for pname, fn in passes.items():
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(steps):
+                flush.fill_(1.0)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); r = fn(); b.record()
+                torch.cuda.synchronize()
+                del r
+                ts.append(a.elapsed_time(b))
+            ts.sort()
+            res[pname + "_ms"] = ts[len(ts) // 2]
+        res["batch"] = B
+        out[name] = res
+        del X, Y, W, G, X2, Y2, W2
+        torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="out/reference_gpu.npz")
     ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--bench-tp", action="store_true", help="time the reference's batched tensor-product kernels only")
     ap.add_argument("--nodes", type=int, default=50000)
     ap.add_argument("--steps", type=int, default=5)
     args = ap.parse_args()
@@ -156,6 +207,9 @@ def main():
     if not oeq.BUILT_EXTENSION:
         print(json.dumps({"reference": "unavailable", "why": str(oeq.BUILT_EXTENSION_ERROR)[:500]}))
         return 1
+    if args.bench_tp:
+        print(json.dumps({"reference_tp_on_gpu": bench_tp(args.steps)}))
+        return 0
     store = {}
     for name, problem, batch in cases():
         run_tp(name, problem, batch, store)
