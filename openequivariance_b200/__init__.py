@@ -9,7 +9,7 @@ import numpy as np
 
 from .core.irreps import Irrep, Irreps, _MulIr
 from .core.problem import Instruction, TPProblem
-from .core.graph import CoordGraph
+from .core.graph import CoordGraph, prepare_graph
 from .core.utils import torch_to_oeq_dtype
 
 __version__ = "0.1.0"
@@ -47,5 +47,5 @@ def torch_ext_so_path():
         return None
 
 
-__all__ = ["TPProblem", "Irreps", "Irrep", "TensorProduct", "TensorProductConv", "CoordGraph",
+__all__ = ["TPProblem", "Irreps", "Irrep", "TensorProduct", "TensorProductConv", "CoordGraph", "prepare_graph",
            "torch_to_oeq_dtype", "torch_ext_so_path", "transpose_irreps"]

@@ -43,6 +43,21 @@ def transpose_permutation(rows, cols):
     return np.lexsort((rows, cols))
 
 
+def prepare_graph(rows: torch.Tensor, cols: torch.Tensor, n_nodes: int):
+    """Edge list in any order -> what the deterministic convolution needs, on the tensors' device and without a host
+    synchronisation: ``rows, cols`` sorted by (row, col), ``transpose_perm`` (positions, in that order, of the edges listed
+    by (col, row)) and ``order`` (the permutation that was applied, for re-ordering per-edge tensors such as ``Y`` and ``W``).
+
+    Device counterpart of ``CoordGraph`` (``ConvolutionBase.py:57-82`` of the reference sorts a Python list); two stable
+    key sorts (torch's device radix sort), index dtype preserved.  ``n_nodes`` bounds the ids (``n_nodes**2 < 2**63``)."""
+    assert rows.shape == cols.shape and rows.dim() == 1
+    r64, c64 = rows.to(torch.int64), cols.to(torch.int64)
+    order = torch.argsort(r64 * n_nodes + c64, stable=True)
+    r, c = r64[order], c64[order]
+    perm = torch.argsort(c * n_nodes + r, stable=True)
+    return {"rows": r.to(rows.dtype), "cols": c.to(cols.dtype), "transpose_perm": perm.to(rows.dtype), "order": order}
+
+
 class CoordGraph:
     """Adjacency of a point cloud, row-major sorted, with the permutation to column-major order.
 
