@@ -163,24 +163,25 @@ constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 4) ? 2 : 1)
                                           : ((FAST_S >= 4) ? FAST_S - 2 : 1);
 // FAST_XPC / FAST_GPC (problem header): registers per channel for an X / dX row and for a Z / G row
 
-// transposed butterfly: on return lane L (L < N) holds in v[0] the sum over all 32 lanes of element L
+// Transposed butterfly over a warp: on return v[0] of lane L holds the sum over all 32 lanes of element L / (32 / N)
+// (N a power of two <= 32; the 32 / N lanes of a group hold the same total).  Each halving step exchanges half of the
+// values a lane still carries, starting with the most distant partner, so 16 values cost 8 + 4 + 2 + 1 shuffles plus one
+// for the last lane bit; the order of the additions is fixed, hence reproducible.
 template <int N>
 OEQ_DEV void warp_reduce_transpose(float (&v)[N], int lane) {
+    int d = 16;
 #pragma unroll
-    for (int m = 16; m >= N; m >>= 1) {
-#pragma unroll
-        for (int t = 0; t < N; ++t) v[t] += __shfl_xor_sync(0xffffffffu, v[t], m);
-    }
-#pragma unroll
-    for (int h = N / 2; h >= 1; h >>= 1) {
-        const bool up = (lane & h) != 0;
+    for (int h = N / 2; h >= 1; h >>= 1, d >>= 1) {
+        const bool up = (lane & d) != 0;
 #pragma unroll
         for (int t = 0; t < h; ++t) {
             const float send = up ? v[t] : v[t + h];
             const float keep = up ? v[t + h] : v[t];
-            v[t] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+            v[t] = keep + __shfl_xor_sync(0xffffffffu, send, d);
         }
     }
+#pragma unroll
+    for (; d >= 1; d >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], d);
 }
 
 // ---- work split -------------------------------------------------------------------------------------------
@@ -621,7 +622,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
             }
         });
         warp_reduce_transpose<FAST_NYP>(dyr, lane);
-        if (lane < FAST_NYP) st.dyp[warp][lane] = dyr[0];
+        if ((lane & (32 / FAST_NYP - 1)) == 0) st.dyp[warp][lane / (32 / FAST_NYP)] = dyr[0];
         fence_async_smem();          // the dX row is read from shared memory by the async proxy (TMA)
         mbar_arrive(&sh.empty[s]);
     }
