@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--cpu-sample-edges", type=int, default=16000)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle spot check of the benchmarked step's outputs")
     ap.add_argument("--workload", default="conv",
                     choices=["conv", "conv_streamed", "tp_uvu", "tp_uvw", "tp_uvw64", "tp_readme"],
                     help="conv = headline fused convolution; conv_streamed = fixed-size graph (default 2,000,000 nodes) whose "
@@ -338,6 +339,8 @@ def bench_single(args, n_nodes, deterministic, dev):
         "fast_path": int(native.query(conv.kernel_string.encode(), conv.hash).fast_path),
     }
 
+    if not args.no_parity:
+        result["parity"] = parity_of_step(problem, conv, step, X, Y, W, G, rows, cols, n_nodes)
     if not args.no_e2e:
         result["e2e"] = bench_e2e(args, conv, problem, X, Y, W, G, rows, cols, perm if deterministic else None, dev, E)
     if not args.no_cpu_baseline:
@@ -349,6 +352,21 @@ def bench_single(args, n_nodes, deterministic, dev):
                                   "sample": f"{n_s} edges (receiver-contiguous slab of the same synthetic graph), "
                                             "torch-CPU fp32 einsum oracle, fwd+bwd; e3nn unavailable on this box"}
     return result
+
+
+def parity_of_step(problem, conv, step, X, Y, W, G, rows, cols, n_nodes):
+    """Outside the timed region: the outputs of one more benchmarked step against the fp64 oracle on two node slabs
+    (receiver slabs for Z, dY, dW; sender slabs for dX).  Relative L2 error per output, largest over the slabs."""
+    import torch
+    from oracle import slab_check
+    Z, dX, dY, dW = step()
+    torch.cuda.synchronize()
+    width = min(160, max(n_nodes // 4, 1))
+    slabs = [(0, width), (n_nodes // 2, min(n_nodes // 2 + width, n_nodes))]
+    err = slab_check.check_slabs(problem, X, Y, W, G, rows, cols, {"Z": Z, "dX": dX, "dY": dY, "dW": dW}, slabs,
+                                 to_e3nn=conv.reorder_weights_to_e3nn, from_e3nn=conv.reorder_weights_from_e3nn)
+    return {"rel_l2": err, "max_rel_l2": max(err.values()), "tolerance": 1e-5, "ok": bool(max(err.values()) <= 1e-5),
+            "against": "fp64 CPU oracle on node slabs %s of the benchmarked graph" % (slabs,)}
 
 
 def bench_e2e(args, conv, problem, X, Y, W, G, rows, cols, perm, dev, E):

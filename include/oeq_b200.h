@@ -126,12 +126,18 @@ OEQB_API int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, 
  *   - No cudaMalloc / cudaFree / allocator call is made, on any call.  All calls share the one array, and it keeps the
  *     previous call's contents: the library re-zeroes the one word that must start at zero and overwrites the rest.
  *     Two calls whose kernels overlap on the GPU (different streams, or different host threads) race on the array.
- *   - Results are the same as oeqb_conv_backward's.  A kernel wait that runs out is recorded inside the array and is
- *     not reported by this entry point. */
+ *   - Results are the same as oeqb_conv_backward's, bit for bit.  A kernel wait that runs out is recorded in the last
+ *     word of the array; oeqb_noalloc_status (below) reads it. */
 OEQB_API int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
                                const void* X, const void* Y, const void* W, const void* G,
                                void* dX, void* dY, void* dW,
                                const void* rows, const void* cols, const void* transpose_perm, void* stream);
+
+/* Companion of oeqb_conv_backward_noalloc (no counterpart in the reference either): reports whether a kernel of the
+ * last allocation-free call on the current device abandoned a bounded wait.  Call it after synchronising with the
+ * stream that call ran on.  It copies one 4-byte word out of the built-in array (a blocking copy; nothing is
+ * allocated) and returns OEQB_OK or OEQB_EKERNEL; the word is cleared by the next oeqb_conv_backward_noalloc call. */
+OEQB_API int oeqb_noalloc_status(void);
 
 /* Second-order pass of the convolution; argument meaning as oeqb_tp_double_backward with node-level X, X2,
  * dX, G, dG.  Replaces JITConvImpl::double_backward (convolution.hpp:138-176) behind

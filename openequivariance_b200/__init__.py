@@ -14,8 +14,8 @@ from .core.utils import torch_to_oeq_dtype
 
 __version__ = "0.1.0"
 
-BUILT_EXTENSION = False
-BUILT_EXTENSION_ERROR = None
+# BUILT_EXTENSION / BUILT_EXTENSION_ERROR are resolved on first access (module __getattr__ below): the native library
+# is loaded when something needs it, so a process that only uses the problem definitions never maps it.
 # The reference reports whether its extension linked libpython; this library has no Python dependency.
 LINKED_LIBPYTHON = False
 LINKED_LIBPYTHON_ERROR = None
@@ -28,14 +28,19 @@ if os.environ.get("OEQ_NOTORCH") != "1":
     from ._torch.TensorProductConv import TensorProductConv
     from ._torch.layout import transpose_irreps
 
-    try:
-        native.load()
-        BUILT_EXTENSION, BUILT_EXTENSION_ERROR = True, None
-    except Exception as _exc:  # noqa: BLE001 - recorded; every kernel call will raise
-        BUILT_EXTENSION, BUILT_EXTENSION_ERROR = False, _exc
-
     torch.serialization.add_safe_globals(
         [TensorProduct, TensorProductConv, TPProblem, Irrep, Irreps, _MulIr, Instruction, np.float32, np.float64])
+
+
+def __getattr__(name):
+    if name in ("BUILT_EXTENSION", "BUILT_EXTENSION_ERROR"):
+        from . import native as _n
+        try:
+            _n.load()
+        except Exception:  # noqa: BLE001 - recorded in native.BUILT_EXTENSION_ERROR; every kernel call raises
+            pass
+        return getattr(_n, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 def torch_ext_so_path():

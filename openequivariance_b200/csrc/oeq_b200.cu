@@ -1328,13 +1328,28 @@ int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, i
     if (int rc = noalloc_scratch(&base)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     void* colptr = (char*)base + scratch_bytes;
-    int* status = (int*)((char*)base + scratch_bytes + colptr_bytes);
+    // The kernels' status word sits in the last slot of the array, wherever the graph's rows end, so that
+    // oeqb_noalloc_status can find it without knowing the sizes of the call that wrote it.
+    int* status = (int*)((char*)base + (size_t)OEQB_NOALLOC_SCRATCH_BYTES - kAlign);
     // The array keeps whatever the previous call left.  Per-edge rows and sender offsets are overwritten in full by
     // the kernels below; only the status word has to start at zero.
     CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
     FastParams f{X, Y, W, G, nullptr, dX, dY, dW, base, rows, cols, n_nodes, n_edges, nullptr};
     if (int rc = fast_launch(e, 4, f, st, status)) return rc;
     return fast_scatter(e, base, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
+}
+
+int oeqb_noalloc_status(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    void* base = nullptr;
+    if (int rc = noalloc_scratch(&base)) return rc;
+    int code = 0;
+    // 4 bytes out of the built-in array into a stack variable: a copy, not an allocation
+    CUDA_TRY(cudaMemcpy(&code, (char*)base + (size_t)OEQB_NOALLOC_SCRATCH_BYTES - kAlign, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code != 0)
+        return fail(OEQB_EKERNEL, "oeqb_conv_backward_noalloc: a kernel of the last call on this device gave up a bounded "
+                                  "wait (code %d); its outputs are invalid", code);
+    return OEQB_OK;
 }
 
 }  // extern "C"

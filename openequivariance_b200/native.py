@@ -36,6 +36,7 @@ _PROTOTYPES = {
     "oeqb_conv_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11 + [c_int64, _P]),
     "oeqb_conv_double_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 15 + [c_int64, _P]),
     "oeqb_conv_backward_noalloc": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11),
+    "oeqb_noalloc_status": (c_int, []),
     "oeqb_emit_source": (c_int, [c_char_p, c_size_t, c_char_p, c_char_p, c_size_t, POINTER(c_size_t)]),
     "oeqb_precompile": (c_int, _DESC),
     "oeqb_set_option": (c_int, [c_char_p, c_char_p]),
@@ -60,9 +61,14 @@ def load(build_if_missing: bool = True):
     if _lib is not None:
         return _lib
     try:
-        if build_if_missing and not os.path.exists(LIB_PATH):
+        if build_if_missing:
+            # rebuild when the library is missing or older than its sources (only where a compiler is at hand:
+            # a machine that received the built library keeps it)
             from . import build_native
-            build_native.build(verbose=False)
+            nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+            if not os.path.exists(LIB_PATH) or (os.path.exists(nvcc) and os.environ.get("OEQB_NO_REBUILD") != "1"
+                                                and build_native.needs_build()):
+                build_native.build(verbose=False)
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in _PROTOTYPES.items():
             fn = getattr(lib, name)

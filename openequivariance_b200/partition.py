@@ -34,6 +34,19 @@ import torch.distributed as dist
 from .core.graph import transpose_permutation
 
 
+def require_fp32_int64(conv, *index_tensors):
+    """The partitioned and the streamed drivers allocate fp32 buffers and compute byte offsets for fp32 rows and int64
+    indices.  A convolution of another precision, or 32-bit index arrays, would make the kernels read those buffers
+    past their end, so both are refused here, before anything is launched."""
+    import numpy as np
+    dt = np.dtype(conv.config.irrep_dtype)
+    if dt != np.dtype(np.float32) or np.dtype(conv.config.weight_dtype) != np.dtype(np.float32):
+        raise TypeError(f"partitioned / streamed convolution supports float32 problems only, got {dt}")
+    for t in index_tensors:
+        if t is not None and t.dtype != torch.int64:
+            raise TypeError(f"partitioned / streamed convolution needs int64 index arrays, got {t.dtype}")
+
+
 def owner_range(n_nodes: int, world: int, rank: int):
     return (n_nodes * rank) // world, (n_nodes * (rank + 1)) // world
 
@@ -190,6 +203,7 @@ class PartitionedConv:
         single-GPU emulation test, which plays all ranks in one process)."""
         from . import native
         assert conv.deterministic, "the partitioned convolution is built on the deterministic kernels"
+        require_fp32_int64(conv, plan.rows_local, plan.cols_local, plan.perm_local)
         self.conv, self.plan, self.device, self.group = conv, plan, device, group
         self._exchange = exchange or (lambda pl, x: exchange_halo(pl, x, group))
         self._give_back = give_back or (lambda pl, dx: return_halo_gradients(pl, dx, group))

@@ -63,7 +63,9 @@ class StreamedConv:
 
     def __init__(self, conv, rows: torch.Tensor, cols: torch.Tensor, n_receivers: int, chunk_nodes: int, device):
         from . import native
+        from .partition import require_fp32_int64
         assert conv.deterministic, "the streamed convolution is built on the deterministic kernels"
+        require_fp32_int64(conv, rows, cols)
         self.native, self.lib = native, native.load()
         self.desc, self.key = conv.kernel_string.encode(), conv.hash
         self.L1, self.L2, self.L3, self.wn = conv.L1.dim, conv.L2.dim, conv.L3.dim, conv.weight_numel

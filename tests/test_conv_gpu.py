@@ -68,7 +68,7 @@ def test_conv_forward_backward(name, mode, dt, graph):
     want = tp_oracle.forward(p, x, y[order], w if p.shared_weights else w[order], graph=(gr.rows, gr.cols))
     got = np.zeros((N, p.irreps_out.dim), dtype=dt)
     conv.forward_cpu(x, y[order], w if p.shared_weights else w[order], got, gr)
-    tol = REL_L2[dt] * (3 if mode == "atomic" else 1)
+    tol = REL_L2[dt]
     assert rel_l2(got, want) <= tol
     wdx, wdy, wdw = tp_oracle.backward(p, x, y[order], w if p.shared_weights else w[order], g, graph=(gr.rows, gr.cols))
     dx, dy, dw = np.zeros_like(x), np.zeros_like(y), np.zeros_like(w)
@@ -90,7 +90,7 @@ def test_conv_double_backward(name, mode, dt, graph):
     want = tp_oracle.double_backward(p, x, y, to_e3nn(w), g, x2, y2, to_e3nn(w2), graph=(graph.rows, graph.cols))
     got = conv.double_backward_cpu(x, y, g, w, w2, x2, y2, graph)
     want = (want[0], want[1], conv.reorder_weights_from_e3nn(want[2]), want[3])
-    tol = 1e-11 if dt == np.float64 else 2e-5
+    tol = 1e-11 if dt == np.float64 else REL_L2[dt]
     for a, b, what in zip(got, want, ("dx", "dy", "dW", "dg")):
         assert rel_l2(a, b) <= tol, what
 

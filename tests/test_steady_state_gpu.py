@@ -1,0 +1,123 @@
+"""Parity of the channel-parallel convolution kernels at steady state: a graph large enough that every CTA walks
+hundreds of edges, so the shared-memory ring wraps many times, both producer warps drain and refill stages and the
+receiver hand-over logic runs in the regime the benchmark measures (the small-graph tests give each CTA one or two
+edges).  MACE-like signature (the benchmark's) and a two-block signature; deterministic and atomic variants; first and
+second order.
+
+Two references: the general kernels of this library over the whole graph (``force_generic``), and the fp64 oracle on
+node slabs (``oracle/slab_check.py``).  Tolerance: relative L2 <= 1e-5 against the oracle (fp32), the bound the
+reference's own conv tests use for e3nn (tests/conv_test.py:50-97 thresholds).
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import rel_l2, tp_problem_matrix
+from oracle import slab_check
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+N_NODES = 8000           # ~255k edges: ~860 edges per CTA on 296 CTAs
+SLABS = [(0, 200), (3900, 4100), (7800, 8000)]
+
+
+def _workload(name, n_nodes, seed, shuffle):
+    from openequivariance_b200.core.graph import periodic_radius_graph, spherical_harmonics
+    dev = torch.device("cuda", 0)
+    problem = dict(tp_problem_matrix())[name]
+    g = periodic_radius_graph(n_nodes, mean_degree=32.0, cutoff=5.0, seed=seed, device=dev)
+    rows, cols, perm = g["rows"], g["cols"], g["transpose_perm"]
+    E = rows.numel()
+    lmax = max(ir.l for _, ir in problem.irreps_in2)
+    Y = spherical_harmonics(lmax, g["vec"]).float().contiguous()
+    assert Y.shape[1] == problem.irreps_in2.dim
+    gen = torch.Generator(device=dev).manual_seed(seed + 1)
+    if shuffle:
+        order = torch.randperm(E, device=dev, generator=gen)
+        rows, cols, Y, perm = rows[order].contiguous(), cols[order].contiguous(), Y[order].contiguous(), None
+    X = torch.randn(n_nodes, problem.irreps_in1.dim, device=dev, generator=gen)
+    W = torch.randn(E, problem.weight_numel, device=dev, generator=gen)
+    G = torch.randn(n_nodes, problem.irreps_out.dim, device=dev, generator=gen)
+    return problem, X, Y, W, G, rows, cols, perm
+
+
+def _first_order(conv, X, Y, W, G, rows, cols, perm):
+    x, y, w = (t.detach().clone().requires_grad_(True) for t in (X, Y, W))
+    Z = conv(x, y, w, rows, cols, perm)
+    dX, dY, dW = torch.autograd.grad(Z, [x, y, w], G)
+    return {"Z": Z.detach(), "dX": dX, "dY": dY, "dW": dW}
+
+
+def _second_order(conv, X, Y, W, G, X2, Y2, W2, rows, cols, perm):
+    ops = torch.ops.libtorch_tp_jit
+    ws = conv.workspace_buffer
+    p = perm if perm is not None else torch.zeros(1, dtype=torch.int64, device=X.device)
+    dX, dY, dW, dG = ops.jit_conv_double_backward(conv.kernel, conv.hash, X, Y, W, G, X2, Y2, W2, rows, cols, ws, p)
+    return {"dX": dX, "dY": dY, "dW": dW, "dG": dG}
+
+
+@pytest.mark.parametrize("name,mode", [("mace_like", "deterministic"), ("mace_like", "atomic"),
+                                       ("mace_medium", "deterministic")])
+def test_first_order_at_steady_state(name, mode):
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    problem, X, Y, W, G, rows, cols, perm = _workload(name, N_NODES, 21, shuffle=mode == "atomic")
+    conv = oeq.TensorProductConv(problem, deterministic=mode == "deterministic")
+    assert native.query(conv.kernel_string.encode(), conv.hash).fast_path == 1
+    fast = _first_order(conv, X, Y, W, G, rows, cols, perm)
+    if mode == "deterministic":     # and reproducible at this size too
+        again = _first_order(conv, X, Y, W, G, rows, cols, perm)
+        for k in fast:
+            assert torch.equal(fast[k], again[k]), k
+        del again
+    err = slab_check.check_slabs(problem, X, Y, W, G, rows, cols, fast, SLABS,
+                                 to_e3nn=conv.reorder_weights_to_e3nn, from_e3nn=conv.reorder_weights_from_e3nn)
+    assert max(err.values()) <= TOL, err
+    native.set_option("force_generic", "1")
+    try:
+        general = _first_order(conv, X, Y, W, G, rows, cols, perm)
+    finally:
+        native.set_option("force_generic", "0")
+    for k in fast:
+        e = rel_l2(fast[k].cpu().numpy(), general[k].cpu().numpy())
+        assert e <= TOL, (k, e)
+
+
+@pytest.mark.parametrize("mode", ["deterministic", "atomic"])
+def test_second_order_at_steady_state(mode):
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    n_nodes = 4000
+    problem, X, Y, W, G, rows, cols, perm = _workload("mace_like", n_nodes, 33, shuffle=mode == "atomic")
+    gen = torch.Generator(device=X.device).manual_seed(5)
+    X2, Y2, W2 = (torch.randn(t.shape, device=t.device, generator=gen) for t in (X, Y, W))
+    conv = oeq.TensorProductConv(problem, deterministic=mode == "deterministic")
+    fast = _second_order(conv, X, Y, W, G, X2, Y2, W2, rows, cols, perm)
+    err = slab_check.check_slabs(problem, X, Y, W, G, rows, cols, fast, [(0, 120), (3880, 4000)], second=(X2, Y2, W2),
+                                 to_e3nn=conv.reorder_weights_to_e3nn, from_e3nn=conv.reorder_weights_from_e3nn)
+    assert max(err.values()) <= TOL, err
+    native.set_option("force_generic", "1")
+    try:
+        general = _second_order(conv, X, Y, W, G, X2, Y2, W2, rows, cols, perm)
+    finally:
+        native.set_option("force_generic", "0")
+    for k in fast:
+        e = rel_l2(fast[k].cpu().numpy(), general[k].cpu().numpy())
+        assert e <= TOL, (k, e)
+
+
+def test_fp64_accuracy_pass_on_10k_nodes():
+    """The fp64 accuracy pass of the partitioned configuration: a 10,000-node graph of the same density, deterministic
+    convolution in double precision, forward and backward, against the oracle on node slabs.  Bound: 1e-12."""
+    import openequivariance_b200 as oeq
+    from helpers import with_dtype
+    n_nodes = 10_000
+    problem, X, Y, W, G, rows, cols, perm = _workload("mace_like", n_nodes, 44, shuffle=False)
+    problem = with_dtype(problem, np.float64)
+    X, Y, W, G = (t.double() for t in (X, Y, W, G))
+    conv = oeq.TensorProductConv(problem, deterministic=True)
+    out = _first_order(conv, X, Y, W, G, rows, cols, perm)
+    err = slab_check.check_slabs(problem, X, Y, W, G, rows, cols, out, [(0, 150), (5000, 5150), (9850, 10_000)],
+                                 to_e3nn=conv.reorder_weights_to_e3nn, from_e3nn=conv.reorder_weights_from_e3nn)
+    assert max(err.values()) <= 1e-12, err

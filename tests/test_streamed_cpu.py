@@ -44,3 +44,32 @@ def test_empty_receivers_and_empty_graph():
     empty = torch.zeros(0, dtype=torch.int64)
     plans = plan_chunks(empty, empty, 3, 2)
     assert [(p.n0, p.n1, p.e0, p.e1) for p in plans] == [(0, 2, 0, 0), (2, 3, 0, 0)]
+
+
+def test_drivers_refuse_other_precisions_and_index_widths():
+    """fp64 problems and int32 index arrays would make the kernels read the drivers' fp32 / int64 buffers past their
+    end; both constructors must refuse them before anything is launched."""
+    import types
+
+    import numpy as np
+    import pytest
+    import torch
+
+    from openequivariance_b200.partition import PartitionedConv, build_plan
+    from openequivariance_b200.streamed import StreamedConv
+
+    def fake_conv(dt):
+        return types.SimpleNamespace(deterministic=True, config=types.SimpleNamespace(irrep_dtype=dt, weight_dtype=dt))
+
+    rows = torch.tensor([0, 0, 1, 2, 2, 3], dtype=torch.int64)
+    cols = torch.tensor([1, 2, 0, 0, 3, 2], dtype=torch.int64)
+    plan = build_plan(rows, cols, 4, 1, 0)
+    with pytest.raises(TypeError, match="float32"):
+        PartitionedConv(fake_conv(np.float64), plan, "cpu")
+    with pytest.raises(TypeError, match="float32"):
+        StreamedConv(fake_conv(np.float64), rows, cols, 4, 2, "cpu")
+    with pytest.raises(TypeError, match="int64"):
+        StreamedConv(fake_conv(np.float32), rows.int(), cols.int(), 4, 2, "cpu")
+    plan.cols_local = plan.cols_local.int()
+    with pytest.raises(TypeError, match="int64"):
+        PartitionedConv(fake_conv(np.float32), plan, "cpu")
