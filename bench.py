@@ -51,6 +51,9 @@ def parse_args():
                          "per-edge weights do not fit in memory, walked in receiver chunks and split over the GPUs; "
                          "tp_* = batched tensor-product configurations (secondary lines)")
     ap.add_argument("--chunk-nodes", type=int, default=50000, help="conv_streamed: receivers per chunk")
+    ap.add_argument("--strong-nodes", type=int, default=2_000_000,
+                    help="size of the fixed graph of the strong_scaling object (split over the GPUs)")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong_scaling object")
     ap.add_argument("--batch", type=int, default=0)
     return ap.parse_args()
 
@@ -219,6 +222,11 @@ def run_ours(args):
         result = bench_partitioned(args, n_nodes * world, dev, rank, world)
     else:
         result = bench_single(args, n_nodes, deterministic, dev)
+    if args.workload == "conv" and deterministic and not args.no_strong:
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        result["strong_scaling"] = strong_scaling_object(args, dev, rank, world)
 
     if rank == 0:
         print(json.dumps(result), flush=True)
@@ -482,23 +490,22 @@ def bench_partitioned(args, n_nodes_total, dev, rank, world):
     }
 
 
-def bench_streamed(args, dev, rank, world):
-    """Fixed-size graph (strong scaling): ``--nodes`` nodes in total (default 2,000,000, ~64M edges), receivers split
-    over the ranks as x-slabs and, inside a rank, walked in chunks of ``--chunk-nodes`` receivers.  The per-edge weights
-    (754 GB in fp32 at the default size) are never resident: each chunk's rows are drawn on the device from a generator
-    keyed by (seed, rank, chunk) right before the chunk's forward pass; the loss 0.5*|Z|^2 is separable over receivers, so
-    the chunk's backward pass follows at once and reuses them.  ``value`` counts the time of the convolution passes
-    (gather of the chunk's sender rows, kernels, accumulation of dX, halo traffic); drawing the weights is timed
-    separately and reported in ``config``."""
+def run_streamed(args, dev, rank, world, n_total, steps, warmup):
+    """Fixed-size graph (strong scaling): ``n_total`` nodes (~32 edges each), receivers split over the ranks as x-slabs
+    and, inside a rank, walked in chunks of ``--chunk-nodes`` receivers.  The per-edge weights (754 GB in fp32 at
+    2,000,000 nodes) are never resident: each chunk's rows are drawn on the device from a generator keyed by (seed, rank,
+    chunk) right before the chunk's forward pass; the loss 0.5*|Z|^2 is separable over receivers, so the chunk's
+    backward pass follows at once and reuses them.  The halo rows travel on a side stream while a chunk without halo
+    senders is computed, and the halo gradients go back while the remaining interior chunks run.  Returns timings;
+    drawing the weights is timed separately."""
     import torch
     import openequivariance_b200 as oeq
     from openequivariance_b200 import native
     from openequivariance_b200.core import problems as P
     from openequivariance_b200.core.graph import periodic_radius_graph, spherical_harmonics
-    from openequivariance_b200.partition import build_plan, exchange_halo, return_halo_gradients
+    from openequivariance_b200.partition import add_halo_gradients, build_plan, exchange_halo, send_halo_gradients
     from openequivariance_b200.streamed import StreamedConv
 
-    n_total = args.nodes or 2_000_000
     problem = P.mace_like_problem()
     g = periodic_radius_graph(n_total, mean_degree=32.0, cutoff=5.0, seed=0, device=dev)
     E_total = int(g["rows"].numel())
@@ -521,6 +528,14 @@ def bench_streamed(args, dev, rank, world):
     wgen = torch.Generator(device=dev)
     rng_events = []
     checksum = torch.zeros((), dtype=torch.float64, device=dev)
+    # chunk order: one chunk without halo senders first (it hides the arrival of the halo rows), then every chunk that
+    # reads halo rows (after them the halo gradients are final and can travel), then the rest
+    halo_chunks = sc.chunks_touching(plan.n_owned) if world > 1 else []
+    interior = [c for c in range(len(sc.plans)) if c not in halo_chunks]
+    order = interior[:1] + halo_chunks + interior[1:]
+    main = torch.cuda.current_stream(dev)
+    comm = torch.cuda.Stream(device=dev)
+    state = {}
 
     def weights(c, out):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -533,28 +548,76 @@ def bench_streamed(args, dev, rank, world):
     def on_chunk(c, p, Z_c, dW_c):
         checksum.add_(Z_c[::97, ::13].double().sum())
 
-    def step():
-        exchange_halo(plan, x_local)
-        sc.step(x_local, Y, weights, lambda c, Z_c: Z_c, dx_local, None, on_chunk)
-        return return_halo_gradients(plan, dx_local)
+    def before_chunk(c):
+        if halo_chunks and c == halo_chunks[0]:
+            main.wait_stream(comm)                       # halo rows have landed
 
-    for _ in range(args.warmup):
+    def after_chunk(c):
+        if halo_chunks and c == halo_chunks[-1]:
+            comm.wait_stream(main)                       # halo rows of dx_local are final
+            with torch.cuda.stream(comm):
+                state["recv"] = send_halo_gradients(plan, dx_local)
+
+    def step():
+        state["recv"] = {}
+        if world > 1:
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                state["keep"] = exchange_halo(plan, x_local)
+            if not halo_chunks or not interior:
+                main.wait_stream(comm)
+        sc.step(x_local, Y, weights, lambda c, Z_c: Z_c, dx_local, None, on_chunk, order=order,
+                before_chunk=before_chunk, after_chunk=after_chunk)
+        if world > 1:
+            if not halo_chunks:
+                state["recv"] = send_halo_gradients(plan, dx_local)
+            main.wait_stream(comm)
+            return add_halo_gradients(plan, dx_local, state["recv"])
+        return dx_local
+
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize(dev)
     rng_events.clear()
     sampler = ClockSampler(dev.index or 0)
     launches0 = native.launch_count()
     sampler.start()
-    ms_wall = timed_region(step, args.steps, 0, dev, world)
+    ms_wall = timed_region(step, steps, 0, dev, world)
     clocks = sampler.stop()
     launches = native.launch_count() - launches0
-    rng_ms = sum(a.elapsed_time(b) for a, b in rng_events) / args.steps
+    rng_ms = sum(a.elapsed_time(b) for a, b in rng_events) / steps
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([rng_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MIN)      # conservative: subtract the smallest generation time of any rank
         rng_ms = float(t.item())
-    ms = ms_wall - rng_ms
+    out = {"problem": problem, "nodes": n_total, "edges": E_total, "ms_wall": ms_wall, "rng_ms": rng_ms,
+           "ms": ms_wall - rng_ms, "clocks": clocks, "launches": launches, "chunks_rank0": len(sc.plans),
+           "halo_rows_rank0": plan.n_halo, "checksum": float(checksum.item()), "steps": steps}
+    del sc, x_local, dx_local, Y, plan
+    torch.cuda.empty_cache()
+    return out
+
+
+def strong_scaling_object(args, dev, rank, world):
+    """The fixed 2,000,000-node / ~64M-edge graph on ``world`` GPUs: part of every line this benchmark prints, so that a
+    run at N = 1, 2, 4, 8 yields the strong-scaling curve next to the weak-scaling headline."""
+    r = run_streamed(args, dev, rank, world, args.strong_nodes, max(5, min(args.steps, 5)), 1)
+    return {"nodes": r["nodes"], "edges": r["edges"], "steps": r["steps"], "warmup": 1, "n_gpus": world,
+            "ms_per_step": r["ms"], "ms_per_step_with_weight_generation": r["ms_wall"],
+            "edges_per_s": r["edges"] / (r["ms"] * 1e-3),
+            "edges_per_s_with_weight_generation": r["edges"] / (r["ms_wall"] * 1e-3),
+            "chunk_nodes": args.chunk_nodes, "chunks_rank0": r["chunks_rank0"], "halo_rows_rank0": r["halo_rows_rank0"],
+            "z_checksum_rank0": r["checksum"],
+            "note": "deterministic fused conv fwd+bwd, receivers split into x-slabs per GPU and chunks per slab, per-edge "
+                    "weights drawn per chunk on the device (their generation time is measured and reported both ways)"}
+
+
+def bench_streamed(args, dev, rank, world):
+    """``--workload conv_streamed``: the fixed-size graph as the printed line (see ``run_streamed``)."""
+    n_total = args.nodes or 2_000_000
+    r = run_streamed(args, dev, rank, world, n_total, args.steps, args.warmup)
+    problem, E_total, ms, ms_wall, rng_ms = r["problem"], r["edges"], r["ms"], r["ms_wall"], r["rng_ms"]
     fwd_b, bwd_b = algorithmic_bytes(problem, n_total, E_total, True)
     peaks = {}
     try:
@@ -569,15 +632,15 @@ def bench_streamed(args, dev, rank, world):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "streamed fused conv fwd+bwd (deterministic), MACE-like, fixed graph split into x-slabs per "
                                "GPU and receiver chunks per slab; weights drawn per chunk on the device",
-                   "nodes": n_total, "edges": E_total, "chunk_nodes": args.chunk_nodes, "chunks_rank0": len(sc.plans),
-                   "weights_bytes_total": E_total * problem.weight_numel * 4, "halo_rows_rank0": plan.n_halo,
+                   "nodes": n_total, "edges": E_total, "chunk_nodes": args.chunk_nodes, "chunks_rank0": r["chunks_rank0"],
+                   "weights_bytes_total": E_total * problem.weight_numel * 4, "halo_rows_rank0": r["halo_rows_rank0"],
                    "ms_per_step_with_weight_generation": ms_wall, "weight_generation_ms_per_step": rng_ms,
-                   "z_checksum_rank0": float(checksum.item()), "l2_policy": "inputs larger than L2"},
+                   "z_checksum_rank0": r["checksum"], "l2_policy": "inputs larger than L2"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "kernel": "per GPU: all chunks' conv fwd+bwd incl. sender gather and dX accumulation; "
                                                 "the weights count as read once per edge although they are drawn on the device",
                      "peak_kind": "measured" if "hbm_gbs" in peaks else "fallback"},
-        "clocks": clocks, "gpu_launches": launches,
+        "clocks": r["clocks"], "gpu_launches": r["launches"],
         "e2e": {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "skipped": "end-to-end staging from host memory is measured on the headline workload only"},
     }

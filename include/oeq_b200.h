@@ -149,6 +149,30 @@ OEQB_API int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_
                               const void* rows, const void* cols, const void* transpose_perm,
                               void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Orders an edge list for the convolution on the device, without a host synchronisation.  rows / cols [n_edges]
+ * (idx_dtype 3 = int32, 4 = int64, values in [0, n_nodes)) in any order.  Outputs, same index type, [n_edges] each:
+ * order (the permutation that sorts the edges by (row, col); apply it to per-edge tensors such as Y and W),
+ * sorted_rows / sorted_cols (the sorted list) and transpose_perm (positions, in the sorted list, of the edges
+ * listed by (col, row)): exactly the arrays of the reference's CoordGraph (core/ConvolutionBase.py:57-82, which
+ * sorts a Python list on the host).  Duplicate edges keep their input order.  workspace: device scratch of at least
+ * oeqb_graph_workspace_bytes(n_nodes, n_edges) bytes, 16-byte aligned.  An index out of range is skipped (nothing is
+ * read or written out of bounds) and reported by the next call of this library or by oeqb_check_status. */
+OEQB_API int64_t oeqb_graph_workspace_bytes(int64_t n_nodes, int64_t n_edges);
+OEQB_API int oeqb_prepare_graph(int idx_dtype, int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols,
+                                void* sorted_rows, void* sorted_cols, void* order, void* transpose_perm,
+                                void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Kernels of this library report run-time failures (a bounded wait that ran out, an index out of range) through a
+ * host-visible word per device that the next entry-point call inspects.  This call inspects it now: after the
+ * caller has synchronised with the stream, it tells whether the work issued so far on the current device failed.
+ * Returns OEQB_OK, OEQB_EKERNEL or OEQB_EINVAL and clears the word.  The reference exits the process on a device
+ * error instead (extension/backend/backend_cuda.hpp:30-46). */
+OEQB_API int oeqb_check_status(void);
+
+/* How many calls so far took a slower route than the problem's specialised kernels (operands that are not 16-byte
+ * aligned, no workspace for grouping an unsorted edge list).  With the "log" option each one is also printed. */
+OEQB_API int64_t oeqb_slow_path_count(void);
+
 /* Writes the CUDA source the library would hand to NVRTC for `kind` (a kernel-family name such as
  * "generic_forward") into buf (NUL-terminated, truncated to cap); *needed receives the full length
  * including the NUL.  Lets the specialised source be inspected or compiled offline with nvcc.  Plays the

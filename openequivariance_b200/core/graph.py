@@ -48,9 +48,31 @@ def prepare_graph(rows: torch.Tensor, cols: torch.Tensor, n_nodes: int):
     synchronisation: ``rows, cols`` sorted by (row, col), ``transpose_perm`` (positions, in that order, of the edges listed
     by (col, row)) and ``order`` (the permutation that was applied, for re-ordering per-edge tensors such as ``Y`` and ``W``).
 
-    Device counterpart of ``CoordGraph`` (``ConvolutionBase.py:57-82`` of the reference sorts a Python list); two stable
-    key sorts (torch's device radix sort), index dtype preserved.  ``n_nodes`` bounds the ids (``n_nodes**2 < 2**63``)."""
+    Device counterpart of ``CoordGraph`` (``ConvolutionBase.py:57-82`` of the reference sorts a Python list).  CUDA
+    tensors (int32 / int64) go through the library's own kernels (``oeqb_prepare_graph``: counting sort by node, then a
+    rank-in-segment pass; stable for duplicate edges); CPU tensors take two stable key sorts, for host-side planning
+    and tests.  Index dtype preserved."""
     assert rows.shape == cols.shape and rows.dim() == 1
+    if rows.is_cuda:
+        import ctypes
+
+        from .. import native
+        assert rows.dtype == cols.dtype and rows.dtype in (torch.int32, torch.int64), "index arrays must be int32 or int64"
+        lib = native.load()
+        E = int(rows.numel())
+        r_in, c_in = rows.contiguous(), cols.contiguous()
+        out = {k: torch.empty_like(r_in) for k in ("rows", "cols", "transpose_perm", "order")}
+        if E == 0:
+            return out
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        with torch.cuda.device(rows.device):
+            need = int(lib.oeqb_graph_workspace_bytes(n_nodes, E))
+            ws = torch.empty(max(need, 1), dtype=torch.uint8, device=rows.device)
+            rc = lib.oeqb_prepare_graph(3 if rows.dtype == torch.int32 else 4, n_nodes, E, ptr(r_in), ptr(c_in),
+                                        ptr(out["rows"]), ptr(out["cols"]), ptr(out["order"]), ptr(out["transpose_perm"]),
+                                        ptr(ws), need, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        native.check(rc, "oeqb_prepare_graph")
+        return out
     r64, c64 = rows.to(torch.int64), cols.to(torch.int64)
     order = torch.argsort(r64 * n_nodes + c64, stable=True)
     r, c = r64[order], c64[order]

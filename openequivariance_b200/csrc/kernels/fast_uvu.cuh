@@ -37,6 +37,8 @@ struct FastParams {
     int accum;          // forward kernels: add to the output rows instead of overwriting them
     int pad;
     const float* X2; const float* Y2; const float* W2;   // second-order kernels: the cotangents of (dX, dY, dW)
+    const IDX* eorder;  // convolutions over an unsorted edge list: position -> edge id, grouped by receiver (or null:
+                        // position = edge id).  rows / cols / Y / W / dY / dW are indexed by edge id.
 };
 // Second-order kernels (FAST_DBL), one pass each:
 //   forward   z = F(X2, Y, W) + F(X, Y, W2) + F(X, Y2, W)
@@ -123,12 +125,26 @@ template <int N> OEQ_DEV void ldgsts_wait() { asm volatile("cp.async.wait_group 
 
 // ---- shared-memory stage ----------------------------------------------------------------------------------
 constexpr int FAST_GT = FU / FAST_CH;                      // threads per group: each carries FAST_CH channels
-constexpr int FAST_NT = FAST_NG * FAST_GT;                // consumer threads
-constexpr int FAST_NCW = FAST_NT / 32;                    // consumer warps
+constexpr int FAST_NT = FAST_NG * FAST_GT;                // consumer threads (of one edge stream)
+constexpr int FAST_NCW = FAST_NT / 32;                    // consumer warps (of one edge stream)
 // Producer warps per CTA.  With two, they take the CTA's edges in turn: with 4 + 2 warps per CTA and
 // two CTAs per SM every scheduler hosts two consumer warps and one (half-loaded) producer; with a single producer warp two
 // of the four schedulers carried 40 % more instructions than the others and set the pace.
 // FAST_NP (problem header): 2 from four stages on (the look-ahead is then a multiple of two), else 1.
+// Edge streams per CTA (FAST_V, problem header).  With FAST_V > 1 one CTA per SM hosts FAST_V independent sets of
+// FAST_NT consumer threads, each with its own ring of stages, range of edges and producer warp (the sets share nothing but
+// the SM), followed by one warpgroup of producer warps.  The point is the register file: producer warps need few
+// registers but a launch gives every thread the same number, so right after the role split the producer warpgroup hands
+// its surplus to the consumer warpgroups (setmaxnreg); that pays for a third consumer set per SM (12 consumer warps
+// instead of 8) where two CTAs of 4 + 2 warps filled the register file.  The register numbers below only add up when the
+// launch gave every thread exactly FAST_REG_LAUNCH registers (the host checks the compiled kernel before using it).
+constexpr int FAST_PW = (FAST_V == 1) ? FAST_NP : 4;                 // producer warps in the CTA
+constexpr int FAST_THREADS = FAST_V * FAST_NT + 32 * FAST_PW;
+constexpr int FAST_REG_LAUNCH = 65536 / (FAST_V * 128 + 128) / 8 * 8;   // FAST_V > 1: registers per thread at launch
+constexpr int FAST_REG_PRODUCER = 56;
+constexpr int FAST_REG_CONSUMER = (FAST_REG_LAUNCH + (FAST_REG_LAUNCH - FAST_REG_PRODUCER) / FAST_V) / 8 * 8;
+static_assert(FAST_V == 1 || (FAST_NT == 128 && FAST_NP == 1), "edge streams are warpgroups with one producer warp each");
+static_assert(FAST_V <= 4, "one producer warp per stream out of a single warpgroup");
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
@@ -154,8 +170,8 @@ struct __align__(16) FastShared {
     int abort_flag;
     int pad[3];
 };
-static_assert(sizeof(FastShared) <= 232448, "stages exceed shared memory");
-static_assert(FAST_KERNEL == 6 || sizeof(FastShared) <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
+static_assert(FAST_V * sizeof(FastShared) <= 232448, "stages exceed shared memory");
+static_assert(FAST_KERNEL == 6 || FAST_V * sizeof(FastShared) <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
 // TMA look-ahead in edges.  One stage stays in hand: in the backward pass for the dX row that is still leaving shared
 // memory (FAST_S >= FAST_D + 2); the forward pass measured fastest two edges ahead (7.07 ms against 7.23 / 7.36 ms at 3 / 4).
 constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 4) ? 2 : 1)
@@ -188,14 +204,15 @@ OEQ_DEV void warp_reduce_transpose(float (&v)[N], int lane) {
 // Edge / receiver range of a CTA.  Deterministic forward: ranges are snapped to receiver boundaries (a receiver's
 // edges never straddle two CTAs) and together cover every receiver, including those without edges.
 template <int KIND, bool SNAP>
-OEQ_DEV void cta_range(const FastParams& p, long long* out) {
-    const long long G = gridDim.x, b = blockIdx.x;
+OEQ_DEV void cta_range(const FastParams& p, long long* out, const int stream) {
+    const long long G = (long long)gridDim.x * FAST_V, b = (long long)blockIdx.x * FAST_V + stream;
     long long e0 = (p.E * b) / G, e1 = (p.E * (b + 1)) / G, n0 = 0, n1 = 0;
     if (KIND == FAST_DET && SNAP) {
-        n0 = (e0 == 0) ? 0 : (long long)p.rows[e0 - 1] + 1;
-        n1 = (b == G - 1) ? p.N : ((e1 == 0) ? 0 : (long long)p.rows[e1 - 1] + 1);
-        e0 = lower_bound_ll(p.E, n0, [&](long long k) { return p.rows[k]; });
-        e1 = lower_bound_ll(p.E, n1, [&](long long k) { return p.rows[k]; });
+        auto row_at = [&](long long k) { return (long long)p.rows[p.eorder ? (long long)p.eorder[k] : k]; };
+        n0 = (e0 == 0) ? 0 : row_at(e0 - 1) + 1;
+        n1 = (b == G - 1) ? p.N : ((e1 == 0) ? 0 : row_at(e1 - 1) + 1);
+        e0 = lower_bound_ll(p.E, n0, row_at);
+        e1 = lower_bound_ll(p.E, n1, row_at);
     }
     out[0] = e0; out[1] = e1; out[2] = n0; out[3] = n1;
 }
@@ -207,18 +224,23 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
     const long long e0 = sh.range[0], n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
     const unsigned long long pol_stream = l2_evict_first();
-    IDX colv = 0, rowv = 0, rown = 0;
+    IDX colv = 0, rowv = 0, rown = 0, eidv = 0;
     // this lane's share of the coefficient table stays in registers for the whole kernel
+    // (with several edge streams per CTA the producer warps run on a small register budget and read the table from
+    // memory, where it stays in the L1, every time)
     constexpr int CY_PER_LANE = (NCY + 31) / 32;
-    float tab_c[CY_PER_LANE][FAST_CYT];
-    int tab_j[CY_PER_LANE][FAST_CYT];
+    constexpr bool TAB_IN_REGS = FAST_V == 1;
+    float tab_c[TAB_IN_REGS ? CY_PER_LANE : 1][FAST_CYT];
+    int tab_j[TAB_IN_REGS ? CY_PER_LANE : 1][FAST_CYT];
+    if (TAB_IN_REGS) {
 #pragma unroll
-    for (int t = 0; t < CY_PER_LANE; ++t) {
-        const int q = lane + 32 * t;
+        for (int t = 0; t < CY_PER_LANE; ++t) {
+            const int q = lane + 32 * t;
 #pragma unroll
-        for (int m = 0; m < FAST_CYT; ++m) {
-            tab_c[t][m] = (q < NCY) ? FAST_CYC[q * FAST_CYT + m] : 0.f;
-            tab_j[t][m] = (q < NCY) ? FAST_CYJ[q * FAST_CYT + m] : 0;
+            for (int m = 0; m < FAST_CYT; ++m) {
+                tab_c[TAB_IN_REGS ? t : 0][m] = (q < NCY) ? FAST_CYC[q * FAST_CYT + m] : 0.f;
+                tab_j[TAB_IN_REGS ? t : 0][m] = (q < NCY) ? FAST_CYJ[q * FAST_CYT + m] : 0;
+            }
         }
     }
 
@@ -236,19 +258,29 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         const unsigned par_prev = pos_a.par ^ 1u;   // parity of the stage's previous use
         pos_a.next();
         FastStage& st = sh.st[s];
-        const long long e = e0 + ia;
+        long long e = e0 + ia;                           // position in the list; below: the edge's id
         if ((ia >> 5) != cur_blk && KIND != FAST_TP) {   // indices of 32 consecutive edges, one per lane
             cur_blk = ia >> 5;
             const long long me = e0 + (cur_blk << 5) + lane;
-            colv = (me < p.E) ? p.cols[me] : (IDX)0;
-            rowv = (me < p.E) ? p.rows[me] : (IDX)0;
-            rown = (me + 1 < p.E) ? p.rows[me + 1] : (IDX)-1;
+            if (p.eorder) {
+                const IDX id = (me < p.E) ? p.eorder[me] : (IDX)0;
+                const IDX idn = (me + 1 < p.E) ? p.eorder[me + 1] : (IDX)0;
+                eidv = id;
+                colv = (me < p.E) ? p.cols[id] : (IDX)0;
+                rowv = (me < p.E) ? p.rows[id] : (IDX)0;
+                rown = (me + 1 < p.E) ? p.rows[idn] : (IDX)-1;
+            } else {
+                colv = (me < p.E) ? p.cols[me] : (IDX)0;
+                rowv = (me < p.E) ? p.rows[me] : (IDX)0;
+                rown = (me + 1 < p.E) ? p.rows[me + 1] : (IDX)-1;
+            }
         }
         long long col = e, row = e, nxt = -1;
         if (KIND != FAST_TP) {
             col = (long long)__shfl_sync(0xffffffffu, colv, (int)(ia & 31));
             row = (long long)__shfl_sync(0xffffffffu, rowv, (int)(ia & 31));
             nxt = (long long)__shfl_sync(0xffffffffu, rown, (int)(ia & 31));
+            if (p.eorder) e = (long long)__shfl_sync(0xffffffffu, eidv, (int)(ia & 31));
         }
         if (ia >= FAST_S) {
             if (!BWD) {
@@ -298,14 +330,21 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         for (int t = 0; t < CY_PER_LANE; ++t) {
             const int q = lane + 32 * t;
             if (q < NCY) {
-                float v = tab_c[t][0] * st.y[tab_j[t][0]];
+                float tc[FAST_CYT];
+                int tj[FAST_CYT];
 #pragma unroll
-                for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tab_c[t][m], st.y[tab_j[t][m]], v);
+                for (int m = 0; m < FAST_CYT; ++m) {
+                    tc[m] = TAB_IN_REGS ? tab_c[TAB_IN_REGS ? t : 0][m] : __ldg(&FAST_CYC[q * FAST_CYT + m]);
+                    tj[m] = TAB_IN_REGS ? tab_j[TAB_IN_REGS ? t : 0][m] : __ldg(&FAST_CYJ[q * FAST_CYT + m]);
+                }
+                float v = tc[0] * st.y[tj[0]];
+#pragma unroll
+                for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tc[m], st.y[tj[m]], v);
                 st.cy[q] = v;
                 if (FAST_DBL) {
-                    float v2 = tab_c[t][0] * st.y2[tab_j[t][0]];
+                    float v2 = tc[0] * st.y2[tj[0]];
 #pragma unroll
-                    for (int m = 1; m < FAST_CYT; ++m) v2 = fmaf(tab_c[t][m], st.y2[tab_j[t][m]], v2);
+                    for (int m = 1; m < FAST_CYT; ++m) v2 = fmaf(tc[m], st.y2[tj[m]], v2);
                     st.cy2[FAST_DBL ? q : 0] = v2;
                 }
             }
@@ -511,22 +550,40 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
     if (KIND == FAST_ATOMIC && tid == 0) tma_wait_all<0>();
 }
 
+// Role split of a CTA: threads [0, FAST_V * FAST_NT) are the consumers of stream tid / FAST_NT, the warps behind them the
+// producers (FAST_V == 1: FAST_NP of them for the one stream; else one per stream out of a warpgroup of four).
+OEQ_DEV void fast_regs_producer() {
+    if (FAST_V > 1) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FAST_REG_PRODUCER));
+}
+OEQ_DEV void fast_regs_consumer() {
+    if (FAST_V > 1) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FAST_REG_CONSUMER));
+}
+
 template <int KIND>
 OEQ_DEV void fast_forward_body(const FastParams& p) {
     extern __shared__ __align__(16) unsigned char fast_smem_raw[];
-    FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
+    FastShared* shs = reinterpret_cast<FastShared*>(fast_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31;
-    if (tid == 0) {
+    if (tid < FAST_V) {   // thread v sets up stream v
+        FastShared& sh = shs[tid];
         for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); }
         mbar_init(&sh.zfull, FAST_NT);
         mbar_init(&sh.zfree, 1);
         sh.abort_flag = 0;
-        cta_range<KIND, true>(p, sh.range);
+        cta_range<KIND, true>(p, sh.range, tid);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid >= FAST_NT) { fast_producer<KIND, false>(p, sh, lane, (tid - FAST_NT) >> 5); return; }
-    if (FAST_NG == 1 || tid < FAST_GT) fast_forward_group<KIND, 0>(p, sh, tid); else fast_forward_group<KIND, 1>(p, sh, tid);
+    if (tid >= FAST_V * FAST_NT) {
+        fast_regs_producer();
+        const int pw = (tid - FAST_V * FAST_NT) >> 5;
+        if (pw < FAST_V * FAST_NP) fast_producer<KIND, false>(p, shs[pw / FAST_NP], lane, pw % FAST_NP);
+        return;
+    }
+    fast_regs_consumer();
+    FastShared& sh = shs[tid / FAST_NT];
+    const int ltid = tid % FAST_NT;
+    if (FAST_NG == 1 || ltid < FAST_GT) fast_forward_group<KIND, 0>(p, sh, ltid); else fast_forward_group<KIND, 1>(p, sh, ltid);
 }
 
 // ---- backward ---------------------------------------------------------------------------------------------
@@ -631,35 +688,59 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
 template <int KIND>
 OEQ_DEV void fast_backward_body(const FastParams& p) {
     extern __shared__ __align__(16) unsigned char fast_smem_raw[];
-    FastShared& sh = *reinterpret_cast<FastShared*>(fast_smem_raw);
+    FastShared* shs = reinterpret_cast<FastShared*>(fast_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31;
-    if (tid == 0) {
+    if (tid < FAST_V) {   // thread v sets up stream v
+        FastShared& sh = shs[tid];
         for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); mbar_init(&sh.drained[s], 1); }
         sh.abort_flag = 0;
-        cta_range<KIND, false>(p, sh.range);
+        cta_range<KIND, false>(p, sh.range, tid);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid >= FAST_NT) { fast_producer<KIND, true>(p, sh, lane, (tid - FAST_NT) >> 5); return; }
-    if (FAST_NG == 1 || tid < FAST_GT) fast_backward_group<KIND, 0>(p, sh, tid); else fast_backward_group<KIND, 1>(p, sh, tid);
+    if (tid >= FAST_V * FAST_NT) {
+        fast_regs_producer();
+        const int pw = (tid - FAST_V * FAST_NT) >> 5;
+        if (pw < FAST_V * FAST_NP) fast_producer<KIND, true>(p, shs[pw / FAST_NP], lane, pw % FAST_NP);
+        return;
+    }
+    fast_regs_consumer();
+    FastShared& sh = shs[tid / FAST_NT];
+    const int ltid = tid % FAST_NT;
+    if (FAST_NG == 1 || ltid < FAST_GT) fast_backward_group<KIND, 0>(p, sh, ltid); else fast_backward_group<KIND, 1>(p, sh, ltid);
 }
 
 // ---- entry points (one per program: FAST_KERNEL selects which) ----------------------------------------------
-#if FAST_KERNEL == 0
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_fwd_tp(const FastParams p) { fast_forward_body<FAST_TP>(p); }
+// Kernel names carry "forward" / "backward" / "double_backward" like the reference's (its profiling helpers and stream
+// tests select kernels by those substrings: core/utils.py:174-203, tests/stream_test.py:97-319).  The second-order
+// programs (FAST_DBL) are the fused passes A (the three terms of dG) and B (both terms of dX, dY, dW).
+#define FAST_ENTRY(NAME, BODY) \
+    extern "C" __global__ void __launch_bounds__(FAST_THREADS, FAST_CTAS) NAME(const FastParams p) { BODY(p); }
+#if FAST_KERNEL == 0 && !FAST_DBL
+FAST_ENTRY(oeq_fast_forward_tp, fast_forward_body<FAST_TP>)
+#elif FAST_KERNEL == 1 && !FAST_DBL
+FAST_ENTRY(oeq_fast_forward_det, fast_forward_body<FAST_DET>)
+#elif FAST_KERNEL == 2 && !FAST_DBL
+FAST_ENTRY(oeq_fast_forward_atomic, fast_forward_body<FAST_ATOMIC>)
+#elif FAST_KERNEL == 3 && !FAST_DBL
+FAST_ENTRY(oeq_fast_backward_tp, fast_backward_body<FAST_TP>)
+#elif FAST_KERNEL == 4 && !FAST_DBL
+FAST_ENTRY(oeq_fast_backward_det, fast_backward_body<FAST_DET>)
+#elif FAST_KERNEL == 5 && !FAST_DBL
+FAST_ENTRY(oeq_fast_backward_atomic, fast_backward_body<FAST_ATOMIC>)
+#elif FAST_KERNEL == 0
+FAST_ENTRY(oeq_fast_double_backward_A_tp, fast_forward_body<FAST_TP>)
 #elif FAST_KERNEL == 1
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_fwd_det(const FastParams p) { fast_forward_body<FAST_DET>(p); }
-#elif FAST_KERNEL == 2
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_fwd_atomic(const FastParams p) { fast_forward_body<FAST_ATOMIC>(p); }
+FAST_ENTRY(oeq_fast_double_backward_A_det, fast_forward_body<FAST_DET>)
 #elif FAST_KERNEL == 3
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_bwd_tp(const FastParams p) { fast_backward_body<FAST_TP>(p); }
+FAST_ENTRY(oeq_fast_double_backward_B_tp, fast_backward_body<FAST_TP>)
 #elif FAST_KERNEL == 4
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_bwd_det(const FastParams p) { fast_backward_body<FAST_DET>(p); }
+FAST_ENTRY(oeq_fast_double_backward_B_det, fast_backward_body<FAST_DET>)
 #elif FAST_KERNEL == 5
-extern "C" __global__ void __launch_bounds__(FAST_NT + 32 * FAST_NP, FAST_CTAS) oeq_fast_bwd_atomic(const FastParams p) { fast_backward_body<FAST_ATOMIC>(p); }
+FAST_ENTRY(oeq_fast_double_backward_B_atomic, fast_backward_body<FAST_ATOMIC>)
 #elif FAST_KERNEL == 6
 // Deterministic scatter of the per-edge dX rows: colptr[c] = first position k (in sender-major order) whose sender >= c
-extern "C" __global__ void oeq_fast_colptr(const IDX* cols, const IDX* perm, long long E, long long N, long long* colptr) {
+extern "C" __global__ void oeq_fixup_backward_offsets(const IDX* cols, const IDX* perm, long long E, long long N, long long* colptr) {
     const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (k > E) return;
     const long long prev = (k == 0) ? -1 : (long long)cols[perm[k - 1]];
@@ -667,7 +748,7 @@ extern "C" __global__ void oeq_fast_colptr(const IDX* cols, const IDX* perm, lon
     for (long long c = prev + 1; c <= cur; ++c) colptr[c] = k;
 }
 // dX[c] = sum over the sender's edges, in sender-major list order, of the per-edge rows in scratch
-extern "C" __global__ void __launch_bounds__(256) oeq_fast_dx_reduce(const float* scratch, const IDX* perm, const long long* colptr,
+extern "C" __global__ void __launch_bounds__(256) oeq_fixup_backward_reduce(const float* scratch, const IDX* perm, const long long* colptr,
                                                                      long long N, float* dX) {
     constexpr int NQ = L1_DIM / 4;
     for (long long c = blockIdx.x; c < N; c += gridDim.x) {

@@ -25,12 +25,15 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <set>
+#include <tuple>
 #include <sstream>
 #include <string>
 #include <vector>
 
 #include "../../include/oeq_b200.h"
 #include "kernels_embed.inc"  // generated at build time: K_COMMON, K_GENERIC, K_FAST_UVU as raw strings
+#include "graph_prep.cuh"     // problem-independent kernels: grouping / sorting of edge lists
 
 namespace {
 
@@ -42,6 +45,8 @@ bool g_force_generic = false;
 bool g_no_tc = false;          // tuning aid: keep 'uvw' forward on the general kernel
 bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
 bool g_single_producer = false;   // tuning aid: one producer warp per CTA in the forward kernels too
+int g_validate = 1;            // index checks of convolution calls: 0 never, 1 first call per edge list, 2 every call
+int g_streams = 3;             // edge streams per CTA on the channel-parallel path (1: two CTAs per SM instead)
 std::string g_cache_dir;
 std::mutex g_mutex;
 
@@ -98,6 +103,9 @@ struct Desc {
     size_t fast_smem3 = 0;
     int fast_S4 = 0;         // stages of the second-order kernels (their stage carries a second coefficient table)
     size_t fast_smem4 = 0;
+    int fast_V = 1;          // edge streams per CTA of the first-order kernels (see kernels/fast_uvu.cuh); 1 = none
+    int fast_SV = 0;         // stages per stream when fast_V > 1
+    size_t fast_smemV = 0;
     size_t elt() const { return dtype == 2 ? 8 : 4; }
 };
 
@@ -200,6 +208,13 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 if (S4 > 6) S4 = 6;
                 d.fast_S4 = S4;    // < 3: second-order passes run on the general kernels
                 d.fast_smem4 = (size_t)S4 * (stage4 + 24) + 128;
+                // Several edge streams in one CTA per SM: consumer sets of exactly one warpgroup, three stages each
+                if (g_streams > 1 && g_streams <= 4 && nthreads == 128 && U == 128) {
+                    const int V = g_streams;
+                    int SV = (int)(((232448 - 1024) / V - 256) / (stage + 24));
+                    if (SV > 4) SV = 4;
+                    if (SV >= 3) { d.fast_V = V; d.fast_SV = SV; d.fast_smemV = (size_t)V * ((size_t)SV * (stage + 24) + 128 + 64); }
+                }
                 int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 24));
                 if (S3 > 6) S3 = 6;
                 d.fast_S3 = S3;    // < 2: atomic forward falls back to the general kernel
@@ -296,15 +311,16 @@ std::string emit_header(const Desc& d) {
 // Producer warps of a kernel with `stages` stages: two from four stages on (its look-ahead is then a multiple of two).
 int fast_producers(int stages) { return (stages >= 4 && !g_single_producer) ? 2 : 1; }
 
-std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_t smem_bytes) {
+std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_t smem_bytes, int streams) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
     s << "#define FAST_DBL " << (dbl ? 1 : 0) << "\n";
-    s << "constexpr int FAST_NP = " << fast_producers(stages) << ";\n";
+    s << "constexpr int FAST_V = " << streams << ";\n";
+    s << "constexpr int FAST_NP = " << (streams > 1 ? 1 : fast_producers(stages)) << ";\n";
     s << "constexpr size_t FAST_SMEM_BYTES = " << smem_bytes << ";\n";
     s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << stages
-      << ", FAST_CTAS = " << d.fast_ctas << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
+      << ", FAST_CTAS = " << (streams > 1 ? 1 : d.fast_ctas) << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
     // Folded-coefficient table: slot q of an edge holds sum_t FAST_CYC[q][t] * y[FAST_CYJ[q][t]], one slot per (i, k) pair
     std::ostringstream cyc, cyj;
@@ -562,7 +578,15 @@ int family_from_name(const std::string& n) {
     return -1;
 }
 
-std::string family_source(const Desc& d, const std::string& header, int fam) {
+// Edge streams per CTA for a kernel family: the first-order kernels except the atomic forward (whose staged output
+// row leaves no room for three rings); 1 when the problem or the caller rules them out.
+int family_streams(const Desc& d, int fam, bool allow) {
+    const bool eligible = fam == FAM_FAST_FWD_TP || fam == FAM_FAST_FWD_DET || fam == FAM_FAST_BWD_TP ||
+                          fam == FAM_FAST_BWD_DET || fam == FAM_FAST_BWD_ATOMIC;
+    return (allow && eligible && d.fast && d.fast_V > 1) ? d.fast_V : 1;
+}
+
+std::string family_source(const Desc& d, const std::string& header, int fam, bool allow_streams = true) {
     std::string src = header;
     if (fam == FAM_GENERIC) {
         src += K_COMMON;
@@ -578,9 +602,10 @@ std::string family_source(const Desc& d, const std::string& header, int fam) {
         const bool fwd3 = fam == FAM_FAST_FWD3_TP || fam == FAM_FAST_FWD3_DET;
         const bool fwd = fwd3 || (fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC);
         const bool dbl = fwd3 || (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC);
-        const int stages = dbl ? d.fast_S4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
-        const size_t smem = dbl ? d.fast_smem4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, smem);
+        const int V = family_streams(d, fam, allow_streams);
+        const int stages = V > 1 ? d.fast_SV : dbl ? d.fast_S4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
+        const size_t smem = V > 1 ? d.fast_smemV : dbl ? d.fast_smem4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, smem, V);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(fwd3 ? fam - FAM_FAST_FWD3_TP : dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
@@ -679,12 +704,15 @@ struct Program {
     std::map<std::string, cudaKernel_t> kernels;
     std::map<std::string, int> smem_set;  // kernel -> bitmask of devices whose smem attribute was raised
     std::string cubin;                    // kept alive for lazy per-context loading
+    bool regs_checked = false;            // multi-stream kernels: register count verified against the hand-over scheme
 };
 
 struct Entry {
     Desc d;
     std::string header;
     std::unique_ptr<Program> prog[FAM_COUNT];
+    std::unique_ptr<Program> prog_single[FAM_COUNT];   // the same families built with one edge stream per CTA
+    bool streams_off = false;                           // a multi-stream kernel came out with the wrong register count
 };
 
 std::map<int64_t, std::unique_ptr<Entry>> g_entries;
@@ -704,16 +732,17 @@ int get_entry(const void* desc, size_t len, int64_t key, Entry** out) {
 }
 
 // Caller holds g_mutex.
-int get_program(Entry* e, int fam, Program** out) {
-    if (e->prog[fam]) { *out = e->prog[fam].get(); return OEQB_OK; }
+int get_program(Entry* e, int fam, Program** out, bool allow_streams = true) {
+    std::unique_ptr<Program>& slot = allow_streams ? e->prog[fam] : e->prog_single[fam];
+    if (slot) { *out = slot.get(); return OEQB_OK; }
     auto p = std::make_unique<Program>();
-    const std::string src = family_source(e->d, e->header, fam);
+    const std::string src = family_source(e->d, e->header, fam, allow_streams);
     int rc = compile_cubin(src, family_name(fam), p->cubin);
     if (rc) return rc;
     cudaError_t ce = cudaLibraryLoadData(&p->lib, p->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
     if (ce != cudaSuccess) return fail(OEQB_ECOMPILE, "cudaLibraryLoadData(%s): %s", family_name(fam), cudaGetErrorString(ce));
     *out = p.get();
-    e->prog[fam] = std::move(p);
+    slot = std::move(p);
     return OEQB_OK;
 }
 
@@ -825,7 +854,11 @@ struct FastParams {
     int accum;         // forward kernels: add to the output rows instead of overwriting them
     int pad;
     const void* X2; const void* Y2; const void* W2;   // fused second-order forward
+    const void* eorder;                               // unsorted edge lists: position -> edge id, grouped by receiver
 };
+
+constexpr size_t kAlign = 256;
+size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 // One host-mapped status word per device: kernels store a non-zero code when a bounded wait runs out.
 int* g_status_host[64] = {nullptr};
@@ -847,9 +880,34 @@ int status_word(int** dev_ptr) {
     const int code = *(volatile int*)g_status_host[dev];
     if (code != 0) {
         *(volatile int*)g_status_host[dev] = 0;
+        if (code == gprep::STATUS_BAD_INDEX)
+            return fail(OEQB_EINVAL, "an earlier call was given an index array (rows / cols / transpose_perm) with a value "
+                                     "out of range, or a receiver list that is not sorted; its outputs are invalid");
         return fail(OEQB_EKERNEL, "an earlier kernel gave up a bounded wait (code %d); its outputs are invalid", code);
     }
-    *dev_ptr = g_status_dev[dev];
+    if (dev_ptr) *dev_ptr = g_status_dev[dev];
+    return OEQB_OK;
+}
+
+// Groups an unsorted edge list by receiver into ws (layout: [order: E indices][scratch of the grouping]); *order receives
+// the position -> edge id list.  Returns OEQB_OK, or a negative number when the workspace is too small (the caller then
+// takes the path that needs none).
+size_t atomic_order_bytes(const Desc& d, long long N, long long E) {
+    return round_up((size_t)(E > 0 ? E : 1) * (d.idx == 3 ? 4 : 8)) + gprep::group_workspace_bytes(N, E);
+}
+int group_by_receiver(const Desc& d, long long N, long long E, const void* rows, void* ws, long long ws_bytes,
+                      cudaStream_t st, const void** order) {
+    if (!ws || ws_bytes < (long long)atomic_order_bytes(d, N, E) || ((uintptr_t)ws & 15u)) return -1;
+    int* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    void* scratch = (char*)ws + round_up((size_t)E * (d.idx == 3 ? 4 : 8));
+    long long launches = 0;
+    bool ok;
+    if (d.idx == 3) ok = gprep::group_by_key<int>((const int*)rows, nullptr, E, N, (int*)ws, nullptr, nullptr, scratch, status, st, nullptr, &launches);
+    else ok = gprep::group_by_key<long long>((const long long*)rows, nullptr, E, N, (long long*)ws, nullptr, nullptr, scratch, status, st, nullptr, &launches);
+    g_launches.fetch_add(launches, std::memory_order_relaxed);
+    if (!ok) return fail(OEQB_ECUDA, "grouping the edge list by receiver failed: %s", cudaGetErrorString(cudaGetLastError()));
+    *order = ws;
     return OEQB_OK;
 }
 
@@ -861,22 +919,52 @@ bool aligned16(std::initializer_list<const void*> ptrs) {
 
 bool use_fast(const Desc& d) { return d.fast && !g_force_generic; }
 
-constexpr size_t kAlign = 256;
-size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 // kernel: 0 fwd_tp, 1 fwd_det, 2 fwd_atomic, 3 bwd_tp, 4 bwd_det, 5 bwd_atomic
 int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status_override = nullptr, bool dbl = false) {
-    static const char* names[6] = {"oeq_fast_fwd_tp", "oeq_fast_fwd_det", "oeq_fast_fwd_atomic",
-                                   "oeq_fast_bwd_tp", "oeq_fast_bwd_det", "oeq_fast_bwd_atomic"};
+    static const char* names1[6] = {"oeq_fast_forward_tp", "oeq_fast_forward_det", "oeq_fast_forward_atomic",
+                                    "oeq_fast_backward_tp", "oeq_fast_backward_det", "oeq_fast_backward_atomic"};
+    static const char* names2[6] = {"oeq_fast_double_backward_A_tp", "oeq_fast_double_backward_A_det", "",
+                                    "oeq_fast_double_backward_B_tp", "oeq_fast_double_backward_B_det",
+                                    "oeq_fast_double_backward_B_atomic"};
+    const char* const* names = dbl ? names2 : names1;
     const Desc& d = e->d;
     int rc;
     if (status_override) p.status = status_override;
     else if ((rc = status_word(&p.status))) return rc;
     Program* prog;
     const bool fwd3 = dbl && kernel < 2;   // fused second-order forward (batch and sorted-convolution variants)
-    const size_t smem = dbl ? d.fast_smem4 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
-    if ((rc = get_program(e, fwd3 ? FAM_FAST_FWD3_TP + kernel : dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel, &prog))) return rc;
+    const int fam = fwd3 ? FAM_FAST_FWD3_TP + kernel : dbl ? FAM_FAST_BWD2_TP + (kernel - 3) : FAM_FAST_FWD_TP + kernel;
     cudaKernel_t k;
+    int V = family_streams(d, fam, !e->streams_off);
+    if (V > 1) {
+        // One CTA per SM with V consumer warpgroups and a producer warpgroup that hands registers over (setmaxnreg).
+        // The hand-over only balances when the launch allocates exactly 65536 / threads registers per thread: a kernel
+        // compiled to anything else is not used (its consumers would wait for registers that are never released).
+        if ((rc = get_program(e, fam, &prog, true))) return rc;
+        if ((rc = get_kernel(prog, names[kernel], d.fast_smemV, &k))) return rc;
+        if (!prog->regs_checked) {
+            cudaFuncAttributes attr;
+            CUDA_TRY(cudaFuncGetAttributes(&attr, (const void*)k));
+            const int threads = V * 128 + 128, want = 65536 / threads / 8 * 8;
+            prog->regs_checked = true;
+            if (attr.numRegs != want || attr.maxThreadsPerBlock < threads) {
+                if (g_log) fprintf(stderr, "[oeq_b200] %s: multi-stream kernel has %d registers (%d needed); using the "
+                                           "two-CTA variant\n", family_name(fam), attr.numRegs, want);
+                e->streams_off = true;
+                V = 1;
+            }
+        }
+    }
+    if (V > 1) {
+        long long grid = sm_count();
+        const long long work = ((p.E > 0 ? p.E : 1) + V - 1) / V;
+        if (grid > work) grid = work;
+        void* args[] = {&p};
+        return launch(k, (unsigned)grid, (unsigned)(V * 128 + 128), d.fast_smemV, args, st);
+    }
+    const size_t smem = dbl ? d.fast_smem4 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
+    if ((rc = get_program(e, fam, &prog, false))) return rc;
     if ((rc = get_kernel(prog, names[kernel], smem, &k))) return rc;
     long long grid = (long long)sm_count() * d.fast_ctas;
     const long long work = p.E > 0 ? p.E : 1;
@@ -894,8 +982,8 @@ int fast_scatter(Entry* e, const void* scratch, const void* cols, const void* pe
     Program* prog;
     if ((rc = get_program(e, FAM_FAST_SCATTER, &prog))) return rc;
     cudaKernel_t k1, k2;
-    if ((rc = get_kernel(prog, "oeq_fast_colptr", 0, &k1))) return rc;
-    if ((rc = get_kernel(prog, "oeq_fast_dx_reduce", 0, &k2))) return rc;
+    if ((rc = get_kernel(prog, "oeq_fixup_backward_offsets", 0, &k1))) return rc;
+    if ((rc = get_kernel(prog, "oeq_fixup_backward_reduce", 0, &k2))) return rc;
     {
         void* args[] = {(void*)&cols, (void*)&perm, &E, &N, &colptr};
         if ((rc = launch(k1, (unsigned)((E + 1 + 255) / 256), 256, 0, args, st))) return rc;
@@ -955,6 +1043,57 @@ int tc_forward(Entry* e, TcParams p, cudaStream_t st) {
     return launch(k, (unsigned)grid, 256, smem, args, st);
 }
 
+// A problem that the specialised kernels serve took a slower route: counted (oeqb_slow_path_count) and, with the log
+// option, reported, so that a performance cliff caused by an unaligned buffer or a missing workspace is visible.
+std::atomic<long long> g_slow_paths{0};
+void note_slow_path(const char* where, const char* why) {
+    g_slow_paths.fetch_add(1, std::memory_order_relaxed);
+    if (g_log) fprintf(stderr, "[oeq_b200] %s: %s\n", where, why);
+}
+
+// Index validation of a convolution call (caller holds g_mutex).  The channel-parallel kernels turn rows / cols /
+// transpose_perm straight into addresses of bulk copies, so a bad entry would be a wild access on a shared GPU.  One
+// small kernel checks the arrays, the host waits for it and reads the status word, and the call is refused with
+// OEQB_EINVAL before any of the main kernels is launched.  The wait makes this a synchronising step, so by default it runs
+// once per edge list (identified by its addresses and sizes; option "validate": 0 never, 2 every call) and never while
+// the stream is being captured.
+struct GraphKey {
+    int dev; const void* rows; const void* cols; const void* perm; long long E, N; int sorted;
+    bool operator<(const GraphKey& o) const {
+        return std::tie(dev, rows, cols, perm, E, N, sorted) < std::tie(o.dev, o.rows, o.cols, o.perm, o.E, o.N, o.sorted);
+    }
+};
+std::set<GraphKey> g_validated;
+
+int validate_graph(const Desc& d, long long N, long long E, const void* rows, const void* cols, const void* perm,
+                   bool need_sorted, cudaStream_t st, const char* what) {
+    if (g_validate <= 0 || E <= 0) return OEQB_OK;
+    GraphKey key{0, rows, cols, perm, E, N, need_sorted ? 1 : 0};
+    CUDA_TRY(cudaGetDevice(&key.dev));
+    if (g_validate == 1 && g_validated.count(key)) return OEQB_OK;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return OEQB_OK;
+    int* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    const unsigned grid = (unsigned)((E + 255) / 256 < 2048 ? (E + 255) / 256 : 2048);
+    if (d.idx == 3) gprep::validate_edges<int><<<grid, 256, 0, st>>>((const int*)rows, (const int*)cols, (const int*)perm, E, N, need_sorted, status);
+    else gprep::validate_edges<long long><<<grid, 256, 0, st>>>((const long long*)rows, (const long long*)cols, (const long long*)perm, E, N, need_sorted, status);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(st));
+    int dev = key.dev;
+    const int code = *(volatile int*)g_status_host[dev];
+    if (code == gprep::STATUS_BAD_INDEX) {
+        *(volatile int*)g_status_host[dev] = 0;
+        return fail(OEQB_EINVAL, "%s: rows / cols must lie in [0, n_nodes = %lld)%s%s; nothing was launched", what, N,
+                    need_sorted ? ", rows must be sorted (deterministic convolution)" : "",
+                    perm ? ", transpose_perm in [0, n_edges)" : "");
+    }
+    if (g_validated.size() >= 256) g_validated.clear();
+    g_validated.insert(key);
+    return OEQB_OK;
+}
+
 int check_ptrs(std::initializer_list<const void*> ptrs, const char* what) {
     for (const void* p : ptrs)
         if (!p) return fail(OEQB_EINVAL, "%s: null pointer argument", what);
@@ -979,6 +1118,8 @@ int oeqb_set_option(const char* name, const char* value) {
     else if (n == "log") g_log = atoi(value) != 0;
     else if (n == "single_group") g_single_group = atoi(value) != 0;
     else if (n == "single_producer") g_single_producer = atoi(value) != 0;
+    else if (n == "streams") g_streams = atoi(value);
+    else if (n == "validate") g_validate = atoi(value);
     else if (n == "no_tc") g_no_tc = atoi(value) != 0;
     else return fail(OEQB_EINVAL, "unknown option '%s'", name);
     return OEQB_OK;
@@ -1035,6 +1176,11 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
         int rc = compile_cubin(family_source(d, header, fam), family_name(fam), cubin);
         if (rc) return -rc;
         ++done;
+        if (family_streams(d, fam, true) > 1) {   // the one-stream variant too: it is the fallback
+            rc = compile_cubin(family_source(d, header, fam, false), family_name(fam), cubin);
+            if (rc) return -rc;
+            ++done;
+        }
     }
     return done;
 }
@@ -1137,6 +1283,8 @@ int64_t oeqb_conv_workspace_bytes(const void* desc, size_t desc_len, int64_t key
     // Deterministic backward on the channel-parallel path: one dX row per edge plus the sender offsets.
     if ((direction == 1 || (direction == 2 && d.fast_S4 >= 3)) && d.conv && d.det && use_fast(d))
         return (int64_t)(round_up((size_t)n_edges * d.dim[0] * d.elt()) + round_up((size_t)(n_nodes + 1) * 8));
+    // Unsorted (atomic) convolutions on the channel-parallel path: room to group the edge list by receiver first.
+    if (d.conv && !d.det && use_fast(d) && n_edges > 0) return (int64_t)atomic_order_bytes(d, n_nodes, n_edges);
     return 0;
 }
 
@@ -1150,7 +1298,6 @@ static int conv_check(const Desc& d, int64_t n_nodes, int64_t n_edges, const voi
 int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
                       const void* X, const void* Y, const void* W, void* Z, const void* rows, const void* cols,
                       const void* transpose_perm, void* workspace, int64_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
@@ -1160,7 +1307,9 @@ int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_
     if (int rc = check_ptrs({X, Z}, "oeqb_conv_forward")) return rc;
     if (n_edges > 0) if (int rc = check_ptrs({Y, W, rows, cols}, "oeqb_conv_forward")) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    if (int rc = validate_graph(d, n_nodes, n_edges, rows, cols, nullptr, d.det != 0, st, "oeqb_conv_forward")) return rc;
     const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W});
+    if (use_fast(d) && n_edges > 0 && !fast) note_slow_path("oeqb_conv_forward", "X or W is not 16-byte aligned: general kernels");
     if (d.det) {
         if (fast) {
             FastParams f{X, Y, W, nullptr, Z, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
@@ -1168,6 +1317,19 @@ int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_
         }
         FwdParams p{X, Y, W, Z, rows, cols, n_nodes, n_edges, UNIT_SEGMENT, OUT_STORE};
         return generic_forward(e, p, st);
+    }
+    if (fast) {
+        // Group the edges by receiver on the device, then run the sorted-list kernel through that order: each
+        // receiver row is summed in registers and written once, instead of one 50 KB read-modify-write per edge.
+        const void* order = nullptr;
+        const int grc = group_by_receiver(d, n_nodes, n_edges, rows, workspace, workspace_bytes, st, &order);
+        if (grc > 0) return grc;
+        if (grc == 0) {
+            FastParams f{X, Y, W, nullptr, Z, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+            f.eorder = order;
+            return fast_launch(e, 1, f, st);
+        }
+        note_slow_path("oeqb_conv_forward", "no workspace for grouping the edges by receiver: per-edge scatter");
     }
     CUDA_TRY(cudaMemsetAsync(Z, 0, n_nodes * d.dim[2] * d.elt(), st));
     if (fast && d.fast_S3 >= 2 && aligned16({Z})) {
@@ -1193,8 +1355,10 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
     if (int rc = check_ptrs({X, G, dX}, "oeqb_conv_backward")) return rc;
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, dY, dW, rows, cols}, "oeqb_conv_backward")) return rc;
+        if (int rc = validate_graph(d, n_nodes, n_edges, rows, cols, d.det ? transpose_perm : nullptr, d.det != 0, st, "oeqb_conv_backward")) return rc;
     }
     const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W, G, dX, workspace});
+    if (use_fast(d) && n_edges > 0 && !fast) note_slow_path("oeqb_conv_backward", "an operand is not 16-byte aligned: general kernels");
     if (d.det && fast) {
         const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
         const size_t need = scratch_bytes + round_up((size_t)(n_nodes + 1) * 8);
@@ -1209,6 +1373,10 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
     if (!d.det && fast) {
         CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
         FastParams f{X, Y, W, G, nullptr, dX, dY, dW, nullptr, rows, cols, n_nodes, n_edges, nullptr};
+        // walked receiver by receiver (grouped on the device), a receiver's gradient row is read once, not once per edge
+        const int grc = group_by_receiver(d, n_nodes, n_edges, rows, workspace, workspace_bytes, st, &f.eorder);
+        if (grc > 0) return grc;
+        if (grc < 0) note_slow_path("oeqb_conv_backward", "no workspace for grouping the edges by receiver");
         return fast_launch(e, 5, f, st);
     }
     if (n_edges > 0) CUDA_TRY(cudaMemsetAsync(dY, 0, n_edges * d.dim[1] * d.elt(), st));
@@ -1237,12 +1405,17 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
     if (int rc = check_ptrs({X, G, X2, dX, dG}, "oeqb_conv_double_backward")) return rc;
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
+        if (int rc = validate_graph(d, n_nodes, n_edges, rows, cols, d.det ? transpose_perm : nullptr, d.det != 0, st, "oeqb_conv_double_backward")) return rc;
     }
     int rc;
     if (use_fast(d) && d.fast_S4 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, G, dX, dG, workspace})) {
-        // channel-parallel kernels: dG from three forward passes, (dX, dY, dW) from two second-order backward passes
-        const int kf = d.det ? 1 : 2, kb = d.det ? 4 : 5;
+        // channel-parallel kernels: dG from one fused second-order forward pass (three terms), (dX, dY, dW) from one
+        // fused second-order backward pass.  An unsorted edge list is grouped by receiver first and then walked through
+        // that order by the same kernels as a sorted one; without room for the grouping it takes three accumulating
+        // forward passes with a per-edge scatter.
+        const int kb = d.det ? 4 : 5;
         void* colptr = nullptr;
+        const void* order = nullptr;
         if (d.det) {
             const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
             const size_t need = scratch_bytes + round_up((size_t)(n_nodes + 1) * 8);
@@ -1251,23 +1424,26 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
                             (long long)workspace_bytes, need);
             colptr = (char*)workspace + scratch_bytes;
         } else {
-            CUDA_TRY(cudaMemsetAsync(dG, 0, n_nodes * d.dim[2] * d.elt(), st));
+            const int grc = group_by_receiver(d, n_nodes, n_edges, rows, workspace, workspace_bytes, st, &order);
+            if (grc > 0) return grc;
+            if (grc < 0) note_slow_path("oeqb_conv_double_backward", "no workspace for grouping the edges by receiver");
             CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
         }
-        if (d.det && d.fast_S4 >= 3) {   // all three terms of dG in one pass
+        if (d.det || order) {   // all three terms of dG in one pass over receiver-grouped edges
             FastParams f{X, Y, W, nullptr, dG, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
-            f.X2 = X2; f.Y2 = Y2; f.W2 = W2;
-            if ((rc = fast_launch(e, kf, f, st, nullptr, true))) return rc;
+            f.X2 = X2; f.Y2 = Y2; f.W2 = W2; f.eorder = order;
+            if ((rc = fast_launch(e, 1, f, st, nullptr, true))) return rc;
         } else {
+            CUDA_TRY(cudaMemsetAsync(dG, 0, n_nodes * d.dim[2] * d.elt(), st));
             FastParams f{X2, Y, W, nullptr, dG, nullptr, nullptr, nullptr, nullptr, rows, cols, n_nodes, n_edges, nullptr};
-            if ((rc = fast_launch(e, kf, f, st))) return rc;
+            if ((rc = fast_launch(e, 2, f, st))) return rc;
             f.X = X; f.Y = Y2; f.accum = 1;
-            if ((rc = fast_launch(e, kf, f, st))) return rc;
+            if ((rc = fast_launch(e, 2, f, st))) return rc;
             f.Y = Y; f.W = W2;
-            if ((rc = fast_launch(e, kf, f, st))) return rc;
+            if ((rc = fast_launch(e, 2, f, st))) return rc;
         }
         FastParams b{X, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
-        b.X2 = X2; b.Y2 = Y2; b.W2 = W2;   // both second-order backward terms in one pass
+        b.X2 = X2; b.Y2 = Y2; b.W2 = W2; b.eorder = order;   // both second-order backward terms in one pass
         if ((rc = fast_launch(e, kb, b, st, nullptr, true))) return rc;
         if (d.det) return fast_scatter(e, workspace, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
         return OEQB_OK;
@@ -1337,6 +1513,52 @@ int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, i
     FastParams f{X, Y, W, G, nullptr, dX, dY, dW, base, rows, cols, n_nodes, n_edges, nullptr};
     if (int rc = fast_launch(e, 4, f, st, status)) return rc;
     return fast_scatter(e, base, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
+}
+
+int oeqb_check_status(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return status_word(nullptr);
+}
+
+int64_t oeqb_slow_path_count(void) { return g_slow_paths.load(); }
+
+int64_t oeqb_graph_workspace_bytes(int64_t n_nodes, int64_t n_edges) {
+    if (n_nodes < 0 || n_edges < 0) return -(int64_t)fail(OEQB_EINVAL, "oeqb_graph_workspace_bytes: negative size");
+    return (int64_t)gprep::group_workspace_bytes(n_nodes, n_edges);
+}
+
+int oeqb_prepare_graph(int idx_dtype, int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols,
+                       void* sorted_rows, void* sorted_cols, void* order, void* transpose_perm, void* workspace,
+                       int64_t workspace_bytes, void* stream) {
+    if (idx_dtype != 3 && idx_dtype != 4) return fail(OEQB_EINVAL, "oeqb_prepare_graph: idx_dtype must be 3 (int32) or 4 (int64)");
+    if (n_nodes < 0 || n_edges < 0) return fail(OEQB_EINVAL, "oeqb_prepare_graph: negative size");
+    if (n_edges == 0) return OEQB_OK;
+    if (n_nodes == 0) return fail(OEQB_EINVAL, "oeqb_prepare_graph: edges without nodes");
+    if (int rc = check_ptrs({rows, cols, sorted_rows, sorted_cols, order, transpose_perm, workspace}, "oeqb_prepare_graph")) return rc;
+    if (workspace_bytes < (int64_t)gprep::group_workspace_bytes(n_nodes, n_edges) || ((uintptr_t)workspace & 15u))
+        return fail(OEQB_EINVAL, "oeqb_prepare_graph: workspace of %lld bytes is smaller than the %zu required (or not 16-byte aligned)",
+                    (long long)workspace_bytes, gprep::group_workspace_bytes(n_nodes, n_edges));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    long long launches = 0;
+    bool ok;
+    // pass 1: by (row, col) -> order, sorted rows / cols; pass 2: the sorted list by (col, row) -> transpose_perm
+    if (idx_dtype == 3) {
+        ok = gprep::group_by_key<int>((const int*)rows, (const int*)cols, n_edges, n_nodes, (int*)order, (int*)sorted_rows,
+                                      (int*)sorted_cols, workspace, status, st, nullptr, &launches) &&
+             gprep::group_by_key<int>((const int*)sorted_cols, (const int*)sorted_rows, n_edges, n_nodes, (int*)transpose_perm,
+                                      nullptr, nullptr, workspace, status, st, nullptr, &launches);
+    } else {
+        ok = gprep::group_by_key<long long>((const long long*)rows, (const long long*)cols, n_edges, n_nodes, (long long*)order,
+                                            (long long*)sorted_rows, (long long*)sorted_cols, workspace, status, st, nullptr, &launches) &&
+             gprep::group_by_key<long long>((const long long*)sorted_cols, (const long long*)sorted_rows, n_edges, n_nodes,
+                                            (long long*)transpose_perm, nullptr, nullptr, workspace, status, st, nullptr, &launches);
+    }
+    g_launches.fetch_add(launches, std::memory_order_relaxed);
+    if (!ok) return fail(OEQB_ECUDA, "oeqb_prepare_graph: kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return OEQB_OK;
 }
 
 int oeqb_noalloc_status(void) {

@@ -37,6 +37,10 @@ _PROTOTYPES = {
     "oeqb_conv_double_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 15 + [c_int64, _P]),
     "oeqb_conv_backward_noalloc": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11),
     "oeqb_noalloc_status": (c_int, []),
+    "oeqb_check_status": (c_int, []),
+    "oeqb_slow_path_count": (c_int64, []),
+    "oeqb_graph_workspace_bytes": (c_int64, [c_int64, c_int64]),
+    "oeqb_prepare_graph": (c_int, [c_int, c_int64, c_int64] + [_P] * 7 + [c_int64, _P]),
     "oeqb_emit_source": (c_int, [c_char_p, c_size_t, c_char_p, c_char_p, c_size_t, POINTER(c_size_t)]),
     "oeqb_precompile": (c_int, _DESC),
     "oeqb_set_option": (c_int, [c_char_p, c_char_p]),

@@ -163,12 +163,12 @@ def exchange_halo(plan: PartitionPlan, x_local: torch.Tensor, group=None):
     return keep
 
 
-def return_halo_gradients(plan: PartitionPlan, dx_local: torch.Tensor, group=None) -> torch.Tensor:
-    """Sends the halo part of ``dx_local`` back to the owners and adds what arrives into the owned part, peer by
-    peer in rank order (each peer's row list has unique targets, so the result does not depend on timing)."""
-    dx_owned = dx_local[:plan.n_owned]
+def send_halo_gradients(plan: PartitionPlan, dx_local: torch.Tensor, group=None):
+    """First half of ``return_halo_gradients``: sends the halo part of ``dx_local`` to the owners and receives what the
+    peers computed for this rank's rows.  Returns ``{peer: rows}`` for ``add_halo_gradients``.  Runs on the current
+    stream, so a caller can put it on a side stream once the halo rows of ``dx_local`` are final and keep computing."""
     if plan.world == 1:
-        return dx_owned
+        return {}
     ops, recv_bufs = [], {}
     for q in range(plan.world):
         ids = plan.send_ids[q]
@@ -184,9 +184,22 @@ def return_halo_gradients(plan: PartitionPlan, dx_local: torch.Tensor, group=Non
     if ops:
         for work in dist.batch_isend_irecv(ops):
             work.wait()
+    return recv_bufs
+
+
+def add_halo_gradients(plan: PartitionPlan, dx_local: torch.Tensor, recv_bufs) -> torch.Tensor:
+    """Second half: adds the received rows into the owned part, peer by peer in rank order (each peer's row list has
+    unique targets, so the result does not depend on timing)."""
+    dx_owned = dx_local[:plan.n_owned]
     for q in sorted(recv_bufs):
         dx_owned.index_add_(0, plan.send_ids[q], recv_bufs[q])
     return dx_owned
+
+
+def return_halo_gradients(plan: PartitionPlan, dx_local: torch.Tensor, group=None) -> torch.Tensor:
+    """Sends the halo part of ``dx_local`` back to the owners and adds what arrives into the owned part, peer by
+    peer in rank order."""
+    return add_halo_gradients(plan, dx_local, send_halo_gradients(plan, dx_local, group))
 
 
 # ---------------------------------------------------------------------------------------------- GPU execution

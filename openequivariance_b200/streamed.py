@@ -93,22 +93,38 @@ class StreamedConv:
     def _p(t, byte_offset=0):
         return ctypes.c_void_p(t.data_ptr() + byte_offset)
 
+    def chunks_touching(self, first_row: int) -> List[int]:
+        """Chunks one of whose senders has an id >= ``first_row`` (with ``first_row`` = the number of owned rows of a
+        partitioned graph: the chunks that read halo rows and write halo gradients).  One host synchronisation."""
+        tops = torch.stack([p.senders[-1] if p.senders.numel() else p.senders.new_tensor(-1) for p in self.plans])
+        return [c for c, top in enumerate(tops.tolist()) if top >= first_row]
+
     def step(self, X: torch.Tensor, Y: torch.Tensor, weights: Callable, cotangent: Callable, dX: torch.Tensor,
-             dY: Optional[torch.Tensor] = None, on_chunk: Optional[Callable] = None):
+             dY: Optional[torch.Tensor] = None, on_chunk: Optional[Callable] = None, order: Optional[List[int]] = None,
+             before_chunk: Optional[Callable] = None, after_chunk: Optional[Callable] = None):
         """One forward + backward pass over all chunks.
 
         ``X [n_nodes, L1]``, ``Y [E, L2]`` resident; ``weights(c, W_c)`` fills ``W_c [E_c, wn]``; ``cotangent(c, Z_c)``
         returns ``G_c`` (may alias ``Z_c``); ``dX [n_nodes, L1]`` is zeroed here and accumulated; ``dY [E, L2]``
-        optional.  ``on_chunk(c, plan, Z_c, dW_c)`` sees each chunk's outputs before the buffers are reused."""
+        optional.  ``on_chunk(c, plan, Z_c, dW_c)`` sees each chunk's outputs before the buffers are reused.
+        ``order`` lists the chunks in the order to run them (default: ascending; any fixed order gives reproducible
+        results, the association of the per-sender sums in ``dX`` follows it); ``before_chunk(c)`` / ``after_chunk(c)``
+        run on the host around each chunk's launches (a partitioned caller waits for halo rows / starts sending halo
+        gradients there)."""
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         dX.zero_()
-        for c, p in enumerate(self.plans):
+        for c in (range(len(self.plans)) if order is None else order):
+            p = self.plans[c]
             n_e, n_r, n_s = p.e1 - p.e0, p.n1 - p.n0, int(p.senders.numel())
             Z_c = self.Z[:n_r]
+            if before_chunk is not None:
+                before_chunk(c)
             if n_e == 0:
                 Z_c.zero_()
                 if on_chunk is not None:
                     on_chunk(c, p, Z_c, self.dW[:0])
+                if after_chunk is not None:
+                    after_chunk(c)
                 continue
             W_c, dW_c = self.W[:n_e], self.dW[:n_e]
             weights(c, W_c)
@@ -129,4 +145,6 @@ class StreamedConv:
             dX.index_add_(0, p.senders, self.dx_block[:n_s])   # unique indices: one add per row, chunks in order
             if on_chunk is not None:
                 on_chunk(c, p, Z_c, dW_c)
+            if after_chunk is not None:
+                after_chunk(c)
         return dX
