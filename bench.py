@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--cpu-sample-edges", type=int, default=16000)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-atomic", action="store_true", help="skip the atomic_variant object")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle spot check of the benchmarked step's outputs")
     ap.add_argument("--workload", default="conv",
                     choices=["conv", "conv_streamed", "tp_uvu", "tp_uvw", "tp_uvw64", "tp_readme"],
@@ -171,6 +172,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    os.environ["OEQ_NOTORCH"] = "1"      # problem definitions only: this arm maps none of the product's native libraries
     import torch
     from openequivariance_b200.core import problems as P
     problem = P.mace_like_problem()
@@ -349,6 +351,8 @@ def bench_single(args, n_nodes, deterministic, dev):
 
     if not args.no_parity:
         result["parity"] = parity_of_step(problem, conv, step, X, Y, W, G, rows, cols, n_nodes)
+    if deterministic and not args.no_atomic:
+        result["atomic_variant"] = bench_atomic_variant(args, problem, X, Y, W, G, rows, cols, gen, dev, n_nodes, E)
     if not args.no_e2e:
         result["e2e"] = bench_e2e(args, conv, problem, X, Y, W, G, rows, cols, perm if deterministic else None, dev, E)
     if not args.no_cpu_baseline:
@@ -360,6 +364,44 @@ def bench_single(args, n_nodes, deterministic, dev):
                                   "sample": f"{n_s} edges (receiver-contiguous slab of the same synthetic graph), "
                                             "torch-CPU fp32 einsum oracle, fwd+bwd; e3nn unavailable on this box"}
     return result
+
+
+def bench_atomic_variant(args, problem, X, Y, W, G, rows, cols, gen, dev, n_nodes, E):
+    """The other variant of the same configuration: ``TensorProductConv(deterministic=False)`` on the same graph with
+    its edges in a seeded random order (the library groups them by receiver on the device inside each call)."""
+    import torch
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    shuffle = torch.randperm(E, generator=gen).to(dev)
+    r, c, y, w = rows[shuffle].contiguous(), cols[shuffle].contiguous(), Y[shuffle].contiguous(), W[shuffle].contiguous()
+    conv = oeq.TensorProductConv(problem, deterministic=False)
+    ops = torch.ops.libtorch_tp_jit
+    need = native.load().oeqb_conv_workspace_bytes(conv.kernel_string.encode(), len(conv.kernel_string), conv.hash, 1, n_nodes, E)
+    ws = torch.empty(max(int(need), 1), dtype=torch.uint8, device=dev)
+    dummy = torch.zeros(1, dtype=torch.int64, device=dev)
+    L3 = problem.irreps_out.dim
+
+    def step():
+        Z = ops.jit_conv_forward(conv.kernel, conv.hash, X, y, w, L3, r, c, ws, dummy)
+        return Z, ops.jit_conv_backward(conv.kernel, conv.hash, X, y, w, G, r, c, ws, dummy)
+
+    steps = max(3, min(args.steps, 10))
+    ms = timed_region(step, steps, 3, dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    fwd, bwd = [], []
+    for _ in range(3):
+        ev[0].record()
+        Z = ops.jit_conv_forward(conv.kernel, conv.hash, X, y, w, L3, r, c, ws, dummy)
+        ev[1].record()
+        out = ops.jit_conv_backward(conv.kernel, conv.hash, X, y, w, G, r, c, ws, dummy)
+        ev[2].record()
+        torch.cuda.synchronize(dev)
+        fwd.append(ev[0].elapsed_time(ev[1]))
+        bwd.append(ev[1].elapsed_time(ev[2]))
+        del Z, out
+    return {"ms_per_step": ms, "edges_per_s": E / (ms * 1e-3), "steps": steps, "forward_ms": statistics.median(fwd),
+            "backward_ms": statistics.median(bwd), "edge_order": "seeded random permutation",
+            "note": "TensorProductConv(deterministic=False); the grouping of the edges by receiver is part of each call"}
 
 
 def parity_of_step(problem, conv, step, X, Y, W, G, rows, cols, n_nodes):
@@ -712,7 +754,15 @@ def bench_tp(args):
             times.append(a.elapsed_time(b))
         ms = statistics.median(times)
         gbs = B * bytes_per[name] / ms / 1e6
-        out[name] = {"ms": ms, "items_per_s": B / (ms * 1e-3), "algorithmic_gbs": gbs, "hbm_frac": gbs / peak}
+        # host cost of one op call (argument checks, descriptor lookup, marshalling, launch): time to enqueue 200 calls
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(200):
+            fn()
+        host_us = (time.perf_counter() - t0) / 200 * 1e6
+        torch.cuda.synchronize(dev)
+        out[name] = {"ms": ms, "items_per_s": B / (ms * 1e-3), "algorithmic_gbs": gbs, "hbm_frac": gbs / peak,
+                     "host_us_per_call": host_us}
     line = {"metric": "tp_items_per_s", "value": out["forward"]["items_per_s"], "unit": "items/s", "n_gpus": 1,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": out["forward"]["ms"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64" if dt == torch.float64 else "f32",

@@ -97,6 +97,15 @@ OEQB_API int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, i
                       const void* rows, const void* cols, const void* transpose_perm,
                       void* workspace, int64_t workspace_bytes, void* stream);
 
+/* oeqb_conv_forward for callers whose X has another number of rows than Z (no counterpart in the reference, whose
+ * X and Z always share the node count): n_nodes receivers = rows of Z, n_senders = rows of X.  The partitioned and
+ * the streamed drivers of this library call it with a block of gathered sender rows.  The only difference is the
+ * bound the index check applies to cols. */
+OEQB_API int oeqb_conv_forward_rect(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_senders,
+                           int64_t n_edges, const void* X, const void* Y, const void* W, void* Z,
+                           const void* rows, const void* cols, const void* transpose_perm,
+                           void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Gradients of the convolution.  G is dL/dZ [n_nodes, L3_dim].  dX [n_nodes, L1_dim], dY, dW like Y, W.
  * Deterministic descriptors need transpose_perm (position in the row-major edge list of the k-th edge in
  * column-major order) and a symmetric edge set is NOT required by this library.  All outputs are fully
@@ -107,6 +116,15 @@ OEQB_API int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, 
                        void* dX, void* dY, void* dW,
                        const void* rows, const void* cols, const void* transpose_perm,
                        void* workspace, int64_t workspace_bytes, void* stream);
+
+/* oeqb_conv_backward for callers whose G has another number of rows than X (companion of oeqb_conv_forward_rect, no
+ * counterpart in the reference): n_receivers = rows of G (bound of `rows`), n_nodes = rows of X and dX (bound of
+ * `cols`). */
+OEQB_API int oeqb_conv_backward_rect(const void* desc, size_t desc_len, int64_t key, int64_t n_receivers, int64_t n_nodes,
+                            int64_t n_edges, const void* X, const void* Y, const void* W, const void* G,
+                            void* dX, void* dY, void* dW,
+                            const void* rows, const void* cols, const void* transpose_perm,
+                            void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Allocation-free variant of oeqb_conv_backward for deterministic convolutions on the channel-parallel kernels.
  * It has no counterpart in the reference.
@@ -161,6 +179,19 @@ OEQB_API int64_t oeqb_graph_workspace_bytes(int64_t n_nodes, int64_t n_edges);
 OEQB_API int oeqb_prepare_graph(int idx_dtype, int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols,
                                 void* sorted_rows, void* sorted_cols, void* order, void* transpose_perm,
                                 void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Ragged grouped products of the symmetric contraction.  Nodes are sorted by group (chemical element); group g has
+ * ragged_counts[g] consecutive nodes (a HOST array of num_groups entries, as in the reference, which takes the
+ * bincount on the CPU).  dtype 1 = float32, 2 = float64; F = num_features.
+ *   ragged_inner = 0:  C[n, f, m]    = sum_k A[g(n), f, m, k] * B[n, f, k]      A [G, F, M, K], B [N, F, K], C [N, F, M]
+ *   ragged_inner = 1:  C[g, f, m, k] = sum_{n in g} A[n, f, m] * B[n, f, k]      A [N, F, M], B [N, F, K], C [G, F, M, K]
+ *   ragged_inner = 2:  C[n, f, k]    = sum_m A[g(n), f, m, k] * B[n, f, m]      A [G, F, M, K], B [N, F, M], C [N, F, K]
+ *                      (mode 0 with the weights transposed, without materialising the transpose: its vector gradient)
+ * All row-major and contiguous; C is fully written (zeros for empty groups).  The sum over nodes runs in node order
+ * (bitwise reproducible).  Limits: K <= 64, at most 256 groups.  Replaces GroupMMCUDA::group_gemm
+ * (extension/group_mm_cuda.hpp:33-126: one cuBLAS strided-batched GEMM per group from a host loop). */
+OEQB_API int oeqb_group_mm(int dtype, int ragged_inner, int64_t num_groups, int64_t num_features, int64_t M, int64_t K,
+                           const int64_t* ragged_counts, const void* A, const void* B, void* C, void* stream);
 
 /* Kernels of this library report run-time failures (a bounded wait that ran out, an index out of range) through a
  * host-visible word per device that the next entry-point call inspects.  This call inspects it now: after the

@@ -35,10 +35,34 @@ _SCHEMAS = {
                                 " Tensor workspace, Tensor transpose_perm) -> (Tensor, Tensor, Tensor, Tensor)",
 }
 
-_lib_def = torch.library.Library(NS, "DEF")
-for _name, _schema in _SCHEMAS.items():
-    _lib_def.define(_name + _schema)
-_lib_impl = torch.library.Library(NS, "IMPL", "CUDA")
+
+
+def _load_cpp_ops() -> bool:
+    """Loads ``csrc/liboeq_b200_torch.so`` (the operators registered from C++: ``csrc/torch_ops.cpp``) when it has been
+    built from the current sources.  ``OEQB_PYTHON_OPS=1`` keeps the Python implementation below instead."""
+    import os
+
+    from .. import build_native
+    if os.environ.get("OEQB_PYTHON_OPS") == "1" or not os.path.exists(build_native.TORCH_LIB):
+        return False
+    try:
+        if build_native.torch_ops_need_build():
+            return False
+        native.load()                       # the operator library links liboeq_b200.so: have it mapped first
+        torch.ops.load_library(build_native.TORCH_LIB)
+        return True
+    except Exception as exc:  # noqa: BLE001 - the Python implementation below serves instead
+        import sys
+        print(f"[oeq_b200] operator library not loaded ({exc}); using the Python operator layer", file=sys.stderr)
+        return False
+
+
+CPP_OPS = _load_cpp_ops()
+if not CPP_OPS:
+    _lib_def = torch.library.Library(NS, "DEF")
+    for _name, _schema in _SCHEMAS.items():
+        _lib_def.define(_name + _schema)
+    _lib_impl = torch.library.Library(NS, "IMPL", "CUDA")
 
 _ENUM_TO_TORCH = {1: torch.float32, 2: torch.float64, 3: torch.int32, 4: torch.int64, 5: torch.uint8}
 _TORCH_TO_ENUM = {v: k for k, v in _ENUM_TO_TORCH.items()}
@@ -232,10 +256,11 @@ def jit_conv_double_backward(json_bytes, hash, L1_in, L2_in, W, L3_grad, L1_dgra
     return dx, dy, dw, dg
 
 
-for _name, _fn in (("jit_tp_forward", jit_tp_forward), ("jit_tp_backward", jit_tp_backward),
-                   ("jit_tp_double_backward", jit_tp_double_backward), ("jit_conv_forward", jit_conv_forward),
-                   ("jit_conv_backward", jit_conv_backward), ("jit_conv_double_backward", jit_conv_double_backward)):
-    _lib_impl.impl(_name, _fn)
+if not CPP_OPS:
+    for _name, _fn in (("jit_tp_forward", jit_tp_forward), ("jit_tp_backward", jit_tp_backward),
+                       ("jit_tp_double_backward", jit_tp_double_backward), ("jit_conv_forward", jit_conv_forward),
+                       ("jit_conv_backward", jit_conv_backward), ("jit_conv_double_backward", jit_conv_double_backward)):
+        _lib_impl.impl(_name, _fn)
 
 
 # ---- fake (meta) kernels ----------------------------------------------------------------------------------

@@ -138,15 +138,15 @@ __global__ void rank_segments(const long long* __restrict__ ptr, const long long
     }
 }
 
-// Checks an edge list before any kernel turns its entries into addresses: rows / cols in [0, n_nodes), rows
+// Checks an edge list before any kernel turns its entries into addresses: rows in [0, n_nodes), cols in [0, n_senders), rows
 // non-decreasing where the kernels rely on a receiver-sorted list, transpose_perm (optional) in [0, n_edges).
 // Stores STATUS_BAD_INDEX in the status word on the first violation it sees; reads only [0, n_edges) of each array.
 template <typename IDX>
 __global__ void validate_edges(const IDX* __restrict__ rows, const IDX* __restrict__ cols, const IDX* __restrict__ perm,
-                               long long n_edges, long long n_nodes, int need_sorted, int* status) {
+                               long long n_edges, long long n_nodes, long long n_senders, int need_sorted, int* status) {
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n_edges; e += (long long)gridDim.x * blockDim.x) {
         const long long r = (long long)rows[e], c = (long long)cols[e];
-        bool bad = r < 0 || r >= n_nodes || c < 0 || c >= n_nodes;
+        bool bad = r < 0 || r >= n_nodes || c < 0 || c >= n_senders;
         if (need_sorted && e > 0 && (long long)rows[e - 1] > r) bad = true;
         if (perm) { const long long q = (long long)perm[e]; bad = bad || q < 0 || q >= n_edges; }
         if (bad) *(volatile int*)status = STATUS_BAD_INDEX;

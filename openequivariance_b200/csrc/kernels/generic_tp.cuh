@@ -125,6 +125,7 @@ struct BwdParams {
     const IDX* rows; const IDX* cols; const IDX* perm;
     long long n_units; long long n_edges;
     int unit_mode; int accum;
+    T* dW_part;   // shared weights, path-major kernel: [chunks][WN] partial sums, reduced in chunk order afterwards
 };
 
 extern "C" __global__ void __launch_bounds__(128) oeq_generic_backward(const BwdParams p) {
@@ -235,7 +236,9 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_backward(const Bwd
 // Backward for shared weights, path-major: a warp takes a chunk of consecutive items (or edges) and, for one
 // (instruction, v, tile of 32 w) at a time, runs over the chunk keeping that tile of dW in registers; only the chunk's
 // sums are added to global dW (one atomic per weight and chunk instead of one per weight and item, which is what the
-// reference does: templates/loop_unroll_tp.cuh:258-259).  dX and dY are added to per item, so the caller zeroes them.
+// reference does: templates/loop_unroll_tp.cuh:258-259).  With p.dW_part the chunk's sums are not added atomically but
+// stored as row `chunk` of a partials matrix that oeq_generic_dw_reduce sums in chunk order: dW is then bitwise
+// reproducible, whatever the grid.  dX and dY are added to per item, so the caller zeroes them.
 // Modes: OEQ_UNIT_ITEM (tensor product) and OEQ_UNIT_EDGE (atomic convolution).
 constexpr int OEQ_WTILE = 32;
 
@@ -326,19 +329,53 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_backward_shared(co
                             if (lane == 0) p.dy[e * L2_DIM + feat_idx<B2::OFF, B2::MUL, B2::D>(v, j)] += s;
                         }
                     }
+                    T* part = p.dW_part ? p.dW_part + unit * (long long)WN : nullptr;
 #if !OEQ_UVW
-                    if (active) atomicAdd(&p.dW[wi], dwacc);
+                    if (active) { if (part) part[wi] = dwacc; else atomicAdd(&p.dW[wi], dwacc); }
 #else
                     if (active) {
 #pragma unroll
                         for (int ww = 0; ww < OEQ_WTILE; ++ww)
-                            if (w0 + ww < In::WN_) atomicAdd(&p.dW[widx_uvw<In::U, In::V, In::WN_>(In::WOFF, c, v, w0 + ww)], dwacc[ww]);
+                            if (w0 + ww < In::WN_) {
+                                const int wi = widx_uvw<In::U, In::V, In::WN_>(In::WOFF, c, v, w0 + ww);
+                                if (part) part[wi] = dwacc[ww]; else atomicAdd(&p.dW[wi], dwacc[ww]);
+                            }
                     }
                     }   // w0 tiles
 #endif
                 }
             }
         });
+    }
+}
+
+// dW[i] (+)= sum over the chunks of the partial sums written by oeq_generic_backward_shared, in a fixed order: a block
+// takes 32 weights; its 8 warps each add one eighth of the chunks in chunk order, and the eight sub-totals are added in
+// warp order.  The order depends on the number of chunks only, so the result is bitwise reproducible.
+extern "C" __global__ void __launch_bounds__(256) oeq_generic_dw_reduce(const T* __restrict__ part, long long chunks, T* __restrict__ dW, int accum) {
+    __shared__ T sub[8][32];
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const long long i = blockIdx.x * 32LL + lane;
+    const long long per = (chunks + 7) / 8, c0 = seg * per, c1 = (c0 + per < chunks) ? c0 + per : chunks;
+    T acc = T(0);
+    if (i < WN) {
+        long long c = c0;
+        for (; c + 8 <= c1; c += 8) {
+            T v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = part[(c + q) * (long long)WN + i];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc += v[q];
+        }
+        for (; c < c1; ++c) acc += part[c * (long long)WN + i];
+    }
+    sub[seg][lane] = acc;
+    __syncthreads();
+    if (seg == 0 && i < WN) {
+        T tot = accum ? dW[i] : T(0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) tot += sub[q][lane];
+        dW[i] = tot;
     }
 }
 #endif  // OEQ_SHARED_W

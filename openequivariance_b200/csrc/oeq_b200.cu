@@ -34,6 +34,7 @@
 #include "../../include/oeq_b200.h"
 #include "kernels_embed.inc"  // generated at build time: K_COMMON, K_GENERIC, K_FAST_UVU as raw strings
 #include "graph_prep.cuh"     // problem-independent kernels: grouping / sorting of edge lists
+#include "group_mm.cuh"       // problem-independent kernels: ragged grouped products of the symmetric contraction
 
 namespace {
 
@@ -46,7 +47,8 @@ bool g_no_tc = false;          // tuning aid: keep 'uvw' forward on the general 
 bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
 bool g_single_producer = false;   // tuning aid: one producer warp per CTA in the forward kernels too
 int g_validate = 1;            // index checks of convolution calls: 0 never, 1 first call per edge list, 2 every call
-int g_streams = 3;             // edge streams per CTA on the channel-parallel path (1: two CTAs per SM instead)
+int g_streams = 1;             // edge streams per CTA on the channel-parallel path (1: two CTAs per SM; 2-4: one CTA with
+                               // that many consumer sets and a register hand-over; measured slower on the benchmark graph)
 std::string g_cache_dir;
 std::mutex g_mutex;
 
@@ -799,6 +801,7 @@ struct BwdParams {
     const void* rows; const void* cols; const void* perm;
     long long n_units; long long n_edges;
     int unit_mode; int accum;
+    void* dW_part;
 };
 enum { UNIT_ITEM = 0, UNIT_EDGE = 1, UNIT_SEGMENT = 2 };
 enum { OUT_STORE = 0, OUT_ADD = 1, OUT_ATOMIC = 2 };
@@ -826,17 +829,46 @@ int generic_backward(Entry* e, BwdParams p, cudaStream_t st) {
     Program* prog;
     int rc = get_program(e, FAM_GENERIC, &prog);
     if (rc) return rc;
-    if (e->d.shared && p.unit_mode != UNIT_SEGMENT && p.n_edges >= 256) {
-        // shared weights: path-major kernel that sums dW over a chunk of items in registers (32x fewer atomics).
-        // It adds to dX, so for the tensor product dX has to start at zero (the convolution zeroes it anyway).
+    if (e->d.shared && p.unit_mode != UNIT_SEGMENT) {
+        // shared weights: path-major kernel that sums dW over a chunk of items in registers and stores the chunk's sums
+        // as one row of a partials matrix; a second kernel adds the rows in chunk order, so dW is bitwise reproducible
+        // (the chunking does not depend on the grid).  The matrix lives in stream-ordered scratch for the call.
+        // The kernel adds to dX, so for the tensor product dX has to start at zero (the convolution zeroes it anyway).
         const Desc& d = e->d;
         if (p.unit_mode == UNIT_ITEM && !p.accum)
             CUDA_TRY(cudaMemsetAsync(p.dx, 0, (size_t)p.n_edges * d.dim[0] * d.elt(), st));
-        cudaKernel_t ks;
+        cudaKernel_t ks, kr;
         if ((rc = get_kernel(prog, "oeq_generic_backward_shared", 0, &ks))) return rc;
+        if ((rc = get_kernel(prog, "oeq_generic_dw_reduce", 0, &kr))) return rc;
         int chunk = 32;
+        long long chunks = (p.n_edges + chunk - 1) / chunk;
+        void* part = nullptr;
+        {
+            // keep freed scratch in the device's stream-ordered pool: by default the pool gives memory back to the
+            // driver at every synchronisation and the next call pays for mapping it again
+            static bool pool_kept[64] = {false};
+            int dev = 0;
+            CUDA_TRY(cudaGetDevice(&dev));
+            if (dev >= 0 && dev < 64 && !pool_kept[dev]) {
+                cudaMemPool_t pool;
+                CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, dev));
+                uint64_t keep = UINT64_MAX;
+                CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+                pool_kept[dev] = true;
+            }
+        }
+        CUDA_TRY(cudaMallocAsync(&part, (size_t)chunks * d.wn * d.elt(), st));
+        p.dW_part = part;
         void* args[] = {&p, &chunk};
-        return launch(ks, generic_grid((p.n_edges + chunk - 1) / chunk), 128, 0, args, st);
+        rc = launch(ks, generic_grid(chunks), 128, 0, args, st);
+        if (!rc) {
+            // the entry points zero dW before the first pass, so the reduce always adds to what is there
+            int accum = 1;
+            void* rargs[] = {&part, &chunks, &p.dW, &accum};
+            rc = launch(kr, (unsigned)((d.wn + 31) / 32), 256, 0, rargs, st);
+        }
+        cudaFreeAsync(part, st);
+        return rc;
     }
     cudaKernel_t k;
     if ((rc = get_kernel(prog, "oeq_generic_backward", 0, &k))) return rc;
@@ -1065,10 +1097,10 @@ struct GraphKey {
 };
 std::set<GraphKey> g_validated;
 
-int validate_graph(const Desc& d, long long N, long long E, const void* rows, const void* cols, const void* perm,
+int validate_graph(const Desc& d, long long N, long long NS, long long E, const void* rows, const void* cols, const void* perm,
                    bool need_sorted, cudaStream_t st, const char* what) {
     if (g_validate <= 0 || E <= 0) return OEQB_OK;
-    GraphKey key{0, rows, cols, perm, E, N, need_sorted ? 1 : 0};
+    GraphKey key{0, rows, cols, perm, E, N * 0x100000001LL + NS, need_sorted ? 1 : 0};
     CUDA_TRY(cudaGetDevice(&key.dev));
     if (g_validate == 1 && g_validated.count(key)) return OEQB_OK;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -1076,8 +1108,8 @@ int validate_graph(const Desc& d, long long N, long long E, const void* rows, co
     int* status = nullptr;
     if (int rc = status_word(&status)) return rc;
     const unsigned grid = (unsigned)((E + 255) / 256 < 2048 ? (E + 255) / 256 : 2048);
-    if (d.idx == 3) gprep::validate_edges<int><<<grid, 256, 0, st>>>((const int*)rows, (const int*)cols, (const int*)perm, E, N, need_sorted, status);
-    else gprep::validate_edges<long long><<<grid, 256, 0, st>>>((const long long*)rows, (const long long*)cols, (const long long*)perm, E, N, need_sorted, status);
+    if (d.idx == 3) gprep::validate_edges<int><<<grid, 256, 0, st>>>((const int*)rows, (const int*)cols, (const int*)perm, E, N, NS, need_sorted, status);
+    else gprep::validate_edges<long long><<<grid, 256, 0, st>>>((const long long*)rows, (const long long*)cols, (const long long*)perm, E, N, NS, need_sorted, status);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaStreamSynchronize(st));
@@ -1085,7 +1117,7 @@ int validate_graph(const Desc& d, long long N, long long E, const void* rows, co
     const int code = *(volatile int*)g_status_host[dev];
     if (code == gprep::STATUS_BAD_INDEX) {
         *(volatile int*)g_status_host[dev] = 0;
-        return fail(OEQB_EINVAL, "%s: rows / cols must lie in [0, n_nodes = %lld)%s%s; nothing was launched", what, N,
+        return fail(OEQB_EINVAL, "%s: rows must lie in [0, %lld) and cols in [0, %lld)%s%s; nothing was launched", what, N, NS,
                     need_sorted ? ", rows must be sorted (deterministic convolution)" : "",
                     perm ? ", transpose_perm in [0, n_edges)" : "");
     }
@@ -1298,6 +1330,15 @@ static int conv_check(const Desc& d, int64_t n_nodes, int64_t n_edges, const voi
 int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
                       const void* X, const void* Y, const void* W, void* Z, const void* rows, const void* cols,
                       const void* transpose_perm, void* workspace, int64_t workspace_bytes, void* stream) {
+    return oeqb_conv_forward_rect(desc, desc_len, key, n_nodes, n_nodes, n_edges, X, Y, W, Z, rows, cols, transpose_perm,
+                                  workspace, workspace_bytes, stream);
+}
+
+int oeqb_conv_forward_rect(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_senders,
+                           int64_t n_edges, const void* X, const void* Y, const void* W, void* Z, const void* rows,
+                           const void* cols, const void* transpose_perm, void* workspace, int64_t workspace_bytes,
+                           void* stream) {
+    if (n_senders < 0) return fail(OEQB_EINVAL, "oeqb_conv_forward_rect: negative size");
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
@@ -1307,7 +1348,7 @@ int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_
     if (int rc = check_ptrs({X, Z}, "oeqb_conv_forward")) return rc;
     if (n_edges > 0) if (int rc = check_ptrs({Y, W, rows, cols}, "oeqb_conv_forward")) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    if (int rc = validate_graph(d, n_nodes, n_edges, rows, cols, nullptr, d.det != 0, st, "oeqb_conv_forward")) return rc;
+    if (int rc = validate_graph(d, n_nodes, n_senders, n_edges, rows, cols, nullptr, d.det != 0, st, "oeqb_conv_forward")) return rc;
     const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W});
     if (use_fast(d) && n_edges > 0 && !fast) note_slow_path("oeqb_conv_forward", "X or W is not 16-byte aligned: general kernels");
     if (d.det) {
@@ -1344,6 +1385,15 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
                        const void* X, const void* Y, const void* W, const void* G, void* dX, void* dY, void* dW,
                        const void* rows, const void* cols, const void* transpose_perm, void* workspace,
                        int64_t workspace_bytes, void* stream) {
+    return oeqb_conv_backward_rect(desc, desc_len, key, n_nodes, n_nodes, n_edges, X, Y, W, G, dX, dY, dW, rows, cols,
+                                   transpose_perm, workspace, workspace_bytes, stream);
+}
+
+int oeqb_conv_backward_rect(const void* desc, size_t desc_len, int64_t key, int64_t n_receivers, int64_t n_nodes,
+                            int64_t n_edges, const void* X, const void* Y, const void* W, const void* G, void* dX,
+                            void* dY, void* dW, const void* rows, const void* cols, const void* transpose_perm,
+                            void* workspace, int64_t workspace_bytes, void* stream) {
+    if (n_receivers < 0) return fail(OEQB_EINVAL, "oeqb_conv_backward_rect: negative size");
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
     if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
@@ -1355,7 +1405,7 @@ int oeqb_conv_backward(const void* desc, size_t desc_len, int64_t key, int64_t n
     if (int rc = check_ptrs({X, G, dX}, "oeqb_conv_backward")) return rc;
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, dY, dW, rows, cols}, "oeqb_conv_backward")) return rc;
-        if (int rc = validate_graph(d, n_nodes, n_edges, rows, cols, d.det ? transpose_perm : nullptr, d.det != 0, st, "oeqb_conv_backward")) return rc;
+        if (int rc = validate_graph(d, n_receivers, n_nodes, n_edges, rows, cols, d.det ? transpose_perm : nullptr, d.det != 0, st, "oeqb_conv_backward")) return rc;
     }
     const bool fast = use_fast(d) && n_edges > 0 && aligned16({X, W, G, dX, workspace});
     if (use_fast(d) && n_edges > 0 && !fast) note_slow_path("oeqb_conv_backward", "an operand is not 16-byte aligned: general kernels");
@@ -1405,7 +1455,7 @@ int oeqb_conv_double_backward(const void* desc, size_t desc_len, int64_t key, in
     if (int rc = check_ptrs({X, G, X2, dX, dG}, "oeqb_conv_double_backward")) return rc;
     if (n_edges > 0) {
         if (int rc = check_ptrs({Y, W, Y2, W2, dY, dW, rows, cols}, "oeqb_conv_double_backward")) return rc;
-        if (int rc = validate_graph(d, n_nodes, n_edges, rows, cols, d.det ? transpose_perm : nullptr, d.det != 0, st, "oeqb_conv_double_backward")) return rc;
+        if (int rc = validate_graph(d, n_nodes, n_nodes, n_edges, rows, cols, d.det ? transpose_perm : nullptr, d.det != 0, st, "oeqb_conv_double_backward")) return rc;
     }
     int rc;
     if (use_fast(d) && d.fast_S4 >= 3 && (d.det || d.fast_S3 >= 2) && n_edges > 0 && aligned16({X, X2, W, W2, G, dX, dG, workspace})) {
@@ -1558,6 +1608,48 @@ int oeqb_prepare_graph(int idx_dtype, int64_t n_nodes, int64_t n_edges, const vo
     }
     g_launches.fetch_add(launches, std::memory_order_relaxed);
     if (!ok) return fail(OEQB_ECUDA, "oeqb_prepare_graph: kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return OEQB_OK;
+}
+
+int oeqb_group_mm(int dtype, int ragged_inner, int64_t num_groups, int64_t num_features, int64_t M, int64_t K,
+                  const int64_t* ragged_counts, const void* A, const void* B, void* C, void* stream) {
+    if (dtype != 1 && dtype != 2) return fail(OEQB_EINVAL, "oeqb_group_mm: dtype must be 1 (float32) or 2 (float64)");
+    if (ragged_inner < 0 || ragged_inner > 2) return fail(OEQB_EINVAL, "oeqb_group_mm: ragged_inner must be 0, 1 or 2");
+    if (num_groups < 0 || num_features < 0 || M < 0 || K < 0) return fail(OEQB_EINVAL, "oeqb_group_mm: negative size");
+    if (num_groups > gmm::MAX_GROUPS) return fail(OEQB_EUNSUPPORTED, "oeqb_group_mm: at most %d groups", gmm::MAX_GROUPS);
+    if (K > 64) return fail(OEQB_EUNSUPPORTED, "oeqb_group_mm: K = %lld exceeds 64", (long long)K);
+    if (num_features > 65535) return fail(OEQB_EUNSUPPORTED, "oeqb_group_mm: more than 65535 feature channels");
+    if (num_groups == 0 || num_features == 0 || (M == 0 && ragged_inner != 2)) return OEQB_OK;
+    if (!ragged_counts) return fail(OEQB_EINVAL, "oeqb_group_mm: null ragged_counts");
+    gmm::Offsets offs;
+    offs.n_groups = (int)num_groups;
+    offs.off[0] = 0;
+    for (int64_t g = 0; g < num_groups; ++g) {
+        if (ragged_counts[g] < 0) return fail(OEQB_EINVAL, "oeqb_group_mm: negative group size");
+        offs.off[g + 1] = offs.off[g] + ragged_counts[g];
+    }
+    const long long n_nodes = offs.off[num_groups];
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t elt = dtype == 2 ? 8 : 4;
+    if (ragged_inner == 1) {
+        // groups without nodes keep zeros; the kernel writes every row of a non-empty group
+        if (int rc = check_ptrs({C}, "oeqb_group_mm")) return rc;
+        if (K == 0) return OEQB_OK;
+    }
+    if (n_nodes == 0) {
+        if (ragged_inner == 1) CUDA_TRY(cudaMemsetAsync(C, 0, (size_t)num_groups * num_features * M * K * elt, st));
+        return OEQB_OK;
+    }
+    if (int rc = check_ptrs({A, B, C}, "oeqb_group_mm")) return rc;
+    if (ragged_inner == 2) {
+        if (K == 0) return OEQB_OK;
+        if (M == 0) { CUDA_TRY(cudaMemsetAsync(C, 0, (size_t)n_nodes * num_features * K * elt, st)); return OEQB_OK; }
+    }
+    if (K == 0) { CUDA_TRY(cudaMemsetAsync(C, 0, (size_t)n_nodes * num_features * M * elt, st)); return OEQB_OK; }
+    cudaError_t ce = dtype == 2 ? gmm::dispatch<double>(ragged_inner, offs, n_nodes, num_features, (int)M, (int)K, A, B, C, st)
+                                : gmm::dispatch<float>(ragged_inner, offs, n_nodes, num_features, (int)M, (int)K, A, B, C, st);
+    if (ce != cudaSuccess) return fail(OEQB_ECUDA, "oeqb_group_mm: kernel launch failed: %s", cudaGetErrorString(ce));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     return OEQB_OK;
 }
 

@@ -33,11 +33,14 @@ _PROTOTYPES = {
     "oeqb_tp_double_backward": (c_int, _DESC + [c_int64] + [_P] * 12),
     "oeqb_conv_workspace_bytes": (c_int64, _DESC + [c_int, c_int64, c_int64]),
     "oeqb_conv_forward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 8 + [c_int64, _P]),
+    "oeqb_conv_forward_rect": (c_int, _DESC + [c_int64, c_int64, c_int64] + [_P] * 8 + [c_int64, _P]),
     "oeqb_conv_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11 + [c_int64, _P]),
+    "oeqb_conv_backward_rect": (c_int, _DESC + [c_int64, c_int64, c_int64] + [_P] * 11 + [c_int64, _P]),
     "oeqb_conv_double_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 15 + [c_int64, _P]),
     "oeqb_conv_backward_noalloc": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11),
     "oeqb_noalloc_status": (c_int, []),
     "oeqb_check_status": (c_int, []),
+    "oeqb_group_mm": (c_int, [c_int, c_int, c_int64, c_int64, c_int64, c_int64, POINTER(c_int64), _P, _P, _P, _P]),
     "oeqb_slow_path_count": (c_int64, []),
     "oeqb_graph_workspace_bytes": (c_int64, [c_int64, c_int64]),
     "oeqb_prepare_graph": (c_int, [c_int, c_int64, c_int64] + [_P] * 7 + [c_int64, _P]),
@@ -70,9 +73,15 @@ def load(build_if_missing: bool = True):
             # a machine that received the built library keeps it)
             from . import build_native
             nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-            if not os.path.exists(LIB_PATH) or (os.path.exists(nvcc) and os.environ.get("OEQB_NO_REBUILD") != "1"
-                                                and build_native.needs_build()):
+            if not os.path.exists(LIB_PATH):
                 build_native.build(verbose=False)
+            elif os.path.exists(nvcc) and os.environ.get("OEQB_NO_REBUILD") != "1" and build_native.needs_build():
+                try:
+                    build_native.build(verbose=False)
+                except Exception as exc:  # noqa: BLE001 - a library exists: use it, but say that it is out of date
+                    import sys
+                    print(f"[oeq_b200] WARNING: {LIB_PATH} is older than its sources and rebuilding failed ({exc}); "
+                          "loading the existing library", file=sys.stderr)
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in _PROTOTYPES.items():
             fn = getattr(lib, name)

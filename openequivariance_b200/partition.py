@@ -242,8 +242,8 @@ class PartitionedConv:
             return
         p = self.plan
         n_e = e_hi - e_lo
-        rc = self.lib.oeqb_conv_forward(
-            self.desc, len(self.desc), self.key, recv_hi - recv_lo, n_e,
+        rc = self.lib.oeqb_conv_forward_rect(
+            self.desc, len(self.desc), self.key, recv_hi - recv_lo, p.n_owned + p.n_halo, n_e,
             self._p(self.x_local), self._p(Y, e_lo * self.L2 * 4), self._p(W, e_lo * self.wn * 4),
             self._p(Z, recv_lo * self.L3 * 4), self._p(rows_rel), self._p(p.cols_local, e_lo * 8),
             self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(), ctypes.c_void_p(stream.cuda_stream))
@@ -278,8 +278,8 @@ class PartitionedConv:
         dx_local = torch.empty((n_loc, self.L1), dtype=torch.float32, device=self.device)
         dY, dW = torch.empty_like(Y), torch.empty_like(W)
         main = torch.cuda.current_stream(self.device)
-        rc = self.lib.oeqb_conv_backward(
-            self.desc, len(self.desc), self.key, n_loc, p.n_local_edges, self._p(self.x_local), self._p(Y), self._p(W),
+        rc = self.lib.oeqb_conv_backward_rect(
+            self.desc, len(self.desc), self.key, p.n_owned, n_loc, p.n_local_edges, self._p(self.x_local), self._p(Y), self._p(W),
             self._p(G), self._p(dx_local), self._p(dY), self._p(dW), self._p(p.rows_local), self._p(p.cols_local),
             self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(), ctypes.c_void_p(main.cuda_stream))
         self.native.check(rc, "partitioned conv backward")

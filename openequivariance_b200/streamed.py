@@ -130,15 +130,15 @@ class StreamedConv:
             weights(c, W_c)
             torch.index_select(X, 0, p.senders, out=self.x_block[:n_s])
             Y_c = Y[p.e0:p.e1]
-            rc = self.lib.oeqb_conv_forward(
-                self.desc, len(self.desc), self.key, n_r, n_e, self._p(self.x_block), self._p(Y_c), self._p(W_c),
+            rc = self.lib.oeqb_conv_forward_rect(
+                self.desc, len(self.desc), self.key, n_r, n_s, n_e, self._p(self.x_block), self._p(Y_c), self._p(W_c),
                 self._p(Z_c), self._p(p.rows_local), self._p(p.cols_local), self._p(p.perm_local),
                 self._p(self.workspace), self.workspace.numel(), st)
             self.native.check(rc, "streamed conv forward")
             G_c = cotangent(c, Z_c)
             dY_c = dY[p.e0:p.e1] if dY is not None else torch.empty((n_e, self.L2), dtype=torch.float32, device=self.device)
-            rc = self.lib.oeqb_conv_backward(
-                self.desc, len(self.desc), self.key, n_s, n_e, self._p(self.x_block), self._p(Y_c), self._p(W_c),
+            rc = self.lib.oeqb_conv_backward_rect(
+                self.desc, len(self.desc), self.key, n_r, n_s, n_e, self._p(self.x_block), self._p(Y_c), self._p(W_c),
                 self._p(G_c), self._p(self.dx_block), self._p(dY_c), self._p(dW_c), self._p(p.rows_local),
                 self._p(p.cols_local), self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(), st)
             self.native.check(rc, "streamed conv backward")

@@ -82,3 +82,18 @@ def test_kernels_compile_for_sm100a(name, problem):
     for dt in (np.float32, np.float64):
         text = build_descriptor(with_dtype(problem, dt))
         assert native.precompile(text.encode()) >= 1
+
+
+def test_cpp_operator_library_defines_the_six_ops():
+    """csrc/torch_ops.cpp registers the libtorch_tp_jit operators from C++ (schemas of the reference's
+    extension/torch_core.hpp:636-644); the Python layer must have picked it up instead of defining them itself."""
+    import torch
+
+    import openequivariance_b200  # noqa: F401
+    from openequivariance_b200 import build_native
+    from openequivariance_b200._torch import ops
+    assert os.path.exists(build_native.TORCH_LIB) and not build_native.torch_ops_need_build()
+    assert ops.CPP_OPS
+    for name in ops._SCHEMAS:
+        op = getattr(torch.ops.libtorch_tp_jit, name)
+        assert str(op.default._schema).replace(" ", "").startswith(f"libtorch_tp_jit::{name}(Tensorjson_bytes,inthash,")

@@ -1,5 +1,7 @@
 """Argument checks of the op layer raise RuntimeError with the reference's messages
 (tests/input_validation_test.py:96-140) and the ops run on the current stream and on any visible device."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -186,3 +188,36 @@ def test_kernels_are_named_by_pass():
     assert any("forward" in n and "double_backward" not in n and "backward" not in n for n in names), names
     assert any("backward" in n and "double_backward" not in n for n in names), names
     assert any("double_backward" in n for n in names), names
+
+
+def test_python_operator_layer_still_works():
+    """The operators are normally the C++ registrations of csrc/torch_ops.cpp; the equivalent Python implementation
+    (used when that library has not been built) must keep producing the same results and the same error texts."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    code = (
+        "import torch, numpy as np, sys\n"
+        "sys.path.insert(0, 'tests')\n"
+        "import openequivariance_b200 as oeq\n"
+        "from openequivariance_b200._torch import ops\n"
+        "from helpers import tp_problem_matrix, uniform_inputs, rel_l2\n"
+        "from oracle import tp_oracle\n"
+        "assert not ops.CPP_OPS\n"
+        "p = dict(tp_problem_matrix())['uvu_m5']\n"
+        "x, y, w, g, *_ = uniform_inputs(p, 32)\n"
+        "tp = oeq.TensorProduct(p)\n"
+        "xt, yt, wt = (torch.tensor(t, device='cuda', requires_grad=True) for t in (x, y, w))\n"
+        "out = tp(xt, yt, wt); out.backward(torch.tensor(g, device='cuda'))\n"
+        "assert rel_l2(out.detach().cpu().numpy(), tp_oracle.forward(p, x, y, w)) <= 1e-5\n"
+        "assert rel_l2(xt.grad.cpu().numpy(), tp_oracle.backward(p, x, y, w, g)[0]) <= 1e-5\n"
+        "try:\n"
+        "    tp(xt.unsqueeze(1), yt, wt)\n"
+        "except RuntimeError as e:\n"
+        "    assert 'Shape mismatch' in str(e)\n"
+        "else:\n"
+        "    raise SystemExit('no error')\n"
+        "print('ok')\n")
+    env = dict(os.environ, OEQB_PYTHON_OPS="1")
+    r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
