@@ -755,11 +755,13 @@ def bench_tp(args):
         ms = statistics.median(times)
         gbs = B * bytes_per[name] / ms / 1e6
         # host cost of one op call (argument checks, descriptor lookup, marshalling, launch): time to enqueue 200 calls
+        # (only meaningful while the launch queue does not fill up: bounded to ~20 ms of device work)
         torch.cuda.synchronize(dev)
+        n_host = int(max(5, min(200, 20.0 / max(ms, 1e-3))))
         t0 = time.perf_counter()
-        for _ in range(200):
+        for _ in range(n_host):
             fn()
-        host_us = (time.perf_counter() - t0) / 200 * 1e6
+        host_us = (time.perf_counter() - t0) / n_host * 1e6
         torch.cuda.synchronize(dev)
         out[name] = {"ms": ms, "items_per_s": B / (ms * 1e-3), "algorithmic_gbs": gbs, "hbm_frac": gbs / peak,
                      "host_us_per_call": host_us}

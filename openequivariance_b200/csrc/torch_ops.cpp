@@ -17,7 +17,6 @@
 
 #include <memory>
 #include <mutex>
-#include <sstream>
 #include <string>
 #include <tuple>
 #include <unordered_map>
@@ -26,6 +25,8 @@
 #include "../../include/oeq_b200.h"
 
 namespace {
+
+[[noreturn]] void refuse(const std::string& message) { TORCH_CHECK(false, message); }
 
 struct Problem {
     std::string desc;
@@ -43,11 +44,11 @@ std::shared_ptr<Problem> problem(const at::Tensor& json_bytes, int64_t key) {
         if (it != g_problems.end()) return it->second;
     }
     at::Tensor host = json_bytes.detach().to(at::kCPU).contiguous();
-    TORCH_CHECK(host.scalar_type() == at::kByte, "json_bytes must be a uint8 tensor");
+    if (host.scalar_type() != at::kByte) refuse("json_bytes must be a uint8 tensor");
     auto p = std::make_shared<Problem>();
     p->desc.assign(reinterpret_cast<const char*>(host.data_ptr<uint8_t>()), (size_t)host.numel());
     const int rc = oeqb_query(p->desc.data(), p->desc.size(), key, &p->prop);
-    TORCH_CHECK(rc == 0, "oeqb_query failed (code ", rc, "): ", oeqb_last_error());
+    if (rc != 0) refuse("oeqb_query failed (code " + std::to_string(rc) + "): " + oeqb_last_error());
     std::lock_guard<std::mutex> lock(g_mutex);
     g_problems[key] = p;
     return p;
@@ -63,30 +64,36 @@ at::ScalarType torch_dtype(int e) {
     }
 }
 
-std::string shape_str(at::IntArrayRef s) {
-    std::ostringstream o;
-    o << "[";
-    for (size_t i = 0; i < s.size(); ++i) o << (i ? ", " : "") << s[i];
-    o << "]";
-    return o.str();
+// Messages are put together with std::string and std::to_string only: no iostream formatting in this library.
+// (A shape message formatted through std::ostringstream crashed inside the stream's integer insertion on GPU machines,
+// in processes where the CUDA driver's libraries were loaded, and only there; the cause was not found.)
+std::string shape_str(const std::vector<int64_t>& s) {
+    std::string o = "[";
+    for (size_t i = 0; i < s.size(); ++i) o += (i ? ", " : "") + std::to_string(s[i]);
+    return o + "]";
 }
 
+
+
 // Messages as in check_tensor (torch_core.hpp:109-134); -1 in `shape` accepts any extent.
-void check(const at::Tensor& t, std::initializer_list<int64_t> shape, at::ScalarType dt, const char* name) {
-    bool ok = (size_t)t.dim() == shape.size();
-    if (ok) {
-        int64_t i = 0;
-        for (int64_t s : shape) { if (s >= 0 && t.size(i) != s) ok = false; ++i; }
-    }
-    TORCH_CHECK(ok, "Shape mismatch for tensor '", name, "'. Expected: ", shape_str(std::vector<int64_t>(shape)), ". Got: ",
-                shape_str(t.sizes()));
-    TORCH_CHECK(t.is_cuda(), "Tensor '", name, "' is not on the GPU.");
-    TORCH_CHECK(t.scalar_type() == dt, "Dtype mismatch for tensor '", name, "'. Expected: ", dt, ". Got: ", t.scalar_type());
+void check(const at::Tensor& t, const std::vector<int64_t>& shape, at::ScalarType dt, const char* name) {
+    const std::vector<int64_t> got = t.sizes().vec();
+    bool ok = got.size() == shape.size();
+    for (size_t i = 0; ok && i < shape.size(); ++i)
+        if (shape[i] >= 0 && got[i] != shape[i]) ok = false;
+    if (!ok) refuse(std::string("Shape mismatch for tensor '") + name + "'. Expected: " + shape_str(shape) + ". Got: " + shape_str(got));
+#ifndef OEQB_TEST_ANY_DEVICE   // (a test build runs the argument checks on CPU tensors)
+    if (!t.is_cuda()) refuse(std::string("Tensor '") + name + "' is not on the GPU.");
+#endif
+    if (t.scalar_type() != dt)
+        refuse(std::string("Dtype mismatch for tensor '") + name + "'. Expected: " + c10::toString(dt) + ". Got: " +
+               c10::toString(t.scalar_type()));
 }
 
 int64_t first_dim(const at::Tensor& t, const char* name) {
-    TORCH_CHECK(t.dim() >= 1, "Shape mismatch for tensor '", name, "'. Expected a leading batch dimension. Got: ",
-                shape_str(t.sizes()));
+    if (t.dim() < 1)
+        refuse(std::string("Shape mismatch for tensor '") + name + "'. Expected a leading batch dimension. Got: " +
+               shape_str(t.sizes().vec()));
     return t.size(0);
 }
 
@@ -95,7 +102,9 @@ void* mptr(at::Tensor& t) { return t.numel() > 0 ? t.data_ptr() : nullptr; }
 
 void* current_stream(const at::Tensor& t) { return (void*)c10::cuda::getCurrentCUDAStream(t.device().index()).stream(); }
 
-void done(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed (code ", rc, "): ", oeqb_last_error()); }
+void done(int rc, const char* what) {
+    if (rc != 0) refuse(std::string(what) + " failed (code " + std::to_string(rc) + "): " + oeqb_last_error());
+}
 
 int64_t tp_checks(const Problem& p, const at::Tensor& x, const at::Tensor& y, const at::Tensor& W) {
     const at::ScalarType dt = torch_dtype(p.prop.irrep_dtype);
@@ -144,11 +153,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> jit_tp_double_backwar
     check(L3_grad, {B, p->prop.L3_dim}, dt, "L3_grad");
     check(L1_dgrad, {B, p->prop.L1_dim}, dt, "L1_dgrad");
     check(L2_dgrad, {B, p->prop.L2_dim}, dt, "L2_dgrad");
-    TORCH_CHECK(W_dgrad.sizes() == W.sizes(), "Shape mismatch for tensor 'W_dgrad'. Expected: ", shape_str(W.sizes()),
-                ". Got: ", shape_str(W_dgrad.sizes()));
-    TORCH_CHECK(W_dgrad.is_cuda(), "Tensor 'W_dgrad' is not on the GPU.");
-    TORCH_CHECK(W_dgrad.scalar_type() == W.scalar_type(), "Dtype mismatch for tensor 'W_dgrad'. Expected: ", W.scalar_type(),
-                ". Got: ", W_dgrad.scalar_type());
+    check(W_dgrad, W.sizes().vec(), W.scalar_type(), "W_dgrad");
     at::Tensor x = L1_in.contiguous(), y = L2_in.contiguous(), w = W.contiguous(), g = L3_grad.contiguous();
     at::Tensor x2 = L1_dgrad.contiguous(), y2 = L2_dgrad.contiguous(), w2 = W_dgrad.contiguous();
     at::Tensor dx = at::empty_like(x), dy = at::empty_like(y), dw = at::empty_like(w), dg = at::empty_like(g);
@@ -179,7 +184,7 @@ ConvSizes conv_checks(const Problem& p, const at::Tensor& x, const at::Tensor& y
 // the caller's workspace when it is large enough, else a fresh one from torch's caching allocator
 at::Tensor scratch(const Problem& p, int64_t key, int direction, ConvSizes s, const at::Tensor& workspace) {
     const int64_t need = oeqb_conv_workspace_bytes(p.desc.data(), p.desc.size(), key, direction, s.N, s.E);
-    TORCH_CHECK(need >= 0, "oeqb_conv_workspace_bytes failed (code ", -need, "): ", oeqb_last_error());
+    if (need < 0) refuse("oeqb_conv_workspace_bytes failed (code " + std::to_string(-need) + "): " + oeqb_last_error());
     if (workspace.numel() >= need) return workspace;
     return at::empty({need}, workspace.options());
 }
@@ -231,11 +236,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> jit_conv_double_backw
     check(L3_grad, {s.N, p->prop.L3_dim}, dt, "L3_grad");
     check(L1_dgrad, {s.N, p->prop.L1_dim}, dt, "L1_dgrad");
     check(L2_dgrad, {s.E, p->prop.L2_dim}, dt, "L2_dgrad");
-    TORCH_CHECK(W_dgrad.sizes() == W.sizes(), "Shape mismatch for tensor 'W_dgrad'. Expected: ", shape_str(W.sizes()),
-                ". Got: ", shape_str(W_dgrad.sizes()));
-    TORCH_CHECK(W_dgrad.is_cuda(), "Tensor 'W_dgrad' is not on the GPU.");
-    TORCH_CHECK(W_dgrad.scalar_type() == W.scalar_type(), "Dtype mismatch for tensor 'W_dgrad'. Expected: ", W.scalar_type(),
-                ". Got: ", W_dgrad.scalar_type());
+    check(W_dgrad, W.sizes().vec(), W.scalar_type(), "W_dgrad");
     at::Tensor x = L1_in.contiguous(), y = L2_in.contiguous(), w = W.contiguous(), g = L3_grad.contiguous();
     at::Tensor x2 = L1_dgrad.contiguous(), y2 = L2_dgrad.contiguous(), w2 = W_dgrad.contiguous();
     at::Tensor r = rows.contiguous(), c = cols.contiguous(), pm = transpose_perm.contiguous();
