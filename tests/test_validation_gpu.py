@@ -221,3 +221,52 @@ def test_python_operator_layer_still_works():
     env = dict(os.environ, OEQB_PYTHON_OPS="1")
     r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def _aoti_package(tmp_path):
+    exe, bufs = _tp_and_buffers()
+    ep = torch.export.export(exe, tuple(bufs), strict=False)
+    try:
+        path = torch._inductor.aoti_compile_and_package(ep, package_path=str(tmp_path / "tp.pt2"))
+    except Exception as exc:  # noqa: BLE001 - no working host compiler for inductor on this machine
+        pytest.skip(f"AOTInductor could not build a package here: {str(exc)[:200]}")
+    return exe, bufs, path
+
+
+def test_aoti_package_in_python(tmp_path):
+    """torch.export -> AOTInductor package -> load and run (the reference's tests/export_test.py:119-137)."""
+    exe, bufs, path = _aoti_package(tmp_path)
+    model = torch._inductor.aoti_load_package(path)
+    assert torch.allclose(model(*bufs), exe(*bufs), atol=1e-5)
+
+
+def test_aoti_package_from_cpp(tmp_path):
+    """The same package run by a stand-alone C++ program that gets the operators from liboeq_b200_torch.so alone (no
+    Python in the process), as the reference's extension/test/load_aoti.cpp does for its own extension."""
+    import subprocess
+    from torch.utils import cpp_extension as ce
+    from helpers import ROOT
+    from openequivariance_b200 import build_native
+    exe, bufs, path = _aoti_package(tmp_path)
+    runner = tmp_path / "run_package"
+    lib = ce.library_paths()[0]
+    cmd = [os.environ.get("CXX", "g++"), "-O1", "-std=c++17", os.path.join(ROOT, "tests", "aoti", "run_package.cpp"),
+           "-o", str(runner), f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    cmd += [f"-I{p}" for p in ce.include_paths()] + ["-I/usr/local/cuda/include", f"-L{lib}", "-ltorch", "-ltorch_cpu",
+                                                      "-ltorch_cuda", "-lc10", "-lc10_cuda", "-ldl", f"-Wl,-rpath,{lib}"]
+    build = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    if build.returncode != 0:
+        pytest.skip(f"could not compile the C++ runner here: {build.stderr[-300:]}")
+    B, L1, L2, wn = bufs[0].shape[0], bufs[0].shape[1], bufs[1].shape[1], bufs[2].shape[1]
+    run = subprocess.run([str(runner), build_native.TORCH_LIB, path, str(B), str(L1), str(L2), str(wn)],
+                         capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stdout[-1000:] + run.stderr[-2000:]
+    got = dict(line.split(" ", 1) for line in run.stdout.strip().splitlines())
+
+    def ramp(rows, cols, scale):
+        return torch.sin(torch.arange(rows * cols, dtype=torch.float32, device="cuda") * scale).reshape(rows, cols)
+
+    want = exe(ramp(B, L1, 0.37), ramp(B, L2, 0.11), ramp(B, wn, 0.23)).double().cpu()
+    assert got["shape"].split() == [str(want.shape[0]), str(want.shape[1])]
+    assert abs(float(got["sum"]) - float(want.sum())) <= 1e-4 * float(want.abs().sum())
+    assert abs(float(got["abs"]) - float(want.abs().sum())) <= 1e-5 * float(want.abs().sum())
