@@ -145,6 +145,11 @@ constexpr int FAST_REG_PRODUCER = 56;
 constexpr int FAST_REG_CONSUMER = (FAST_REG_LAUNCH + (FAST_REG_LAUNCH - FAST_REG_PRODUCER) / FAST_V) / 8 * 8;
 static_assert(FAST_V == 1 || (FAST_NT == 128 && FAST_NP == 1), "edge streams are warpgroups with one producer warp each");
 static_assert(FAST_V <= 4, "one producer warp per stream out of a single warpgroup");
+// With several streams the single producer warp of a stream is the scarce resource (it serves every edge, where two warps
+// take turns otherwise), so the folding of Y[e] into the coefficients moves to the stream's consumer threads: each folds
+// up to three of the NCY entries from a table in shared memory, then all meet at a per-stage mbarrier.
+constexpr bool FAST_CFOLD = FAST_V > 1;
+constexpr int FAST_TAB_ENTRIES = FAST_CFOLD ? NCY * FAST_CYT : 1;
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
@@ -165,13 +170,39 @@ struct __align__(16) FastShared {
     unsigned long long full[FAST_S];
     unsigned long long empty[FAST_S];
     unsigned long long drained[FAST_S];   // backward with two producers: the stage's dX row has left shared memory
+    unsigned long long folded[FAST_CFOLD ? FAST_S : 1];   // consumer-side folding: every consumer has written its coefficients
     unsigned long long zfull, zfree;
     long long range[4];              // e0, e1, n0, n1
     int abort_flag;
     int pad[3];
 };
-static_assert(FAST_V * sizeof(FastShared) <= 232448, "stages exceed shared memory");
-static_assert(FAST_KERNEL == 6 || FAST_V * sizeof(FastShared) <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
+// coefficient table for consumer-side folding, behind the streams' FastShared blocks: (coefficient, index into y) pairs
+struct FastTabEntry { float c; int j; };
+constexpr size_t FAST_SMEM_NEED = FAST_V * sizeof(FastShared) + (FAST_CFOLD ? FAST_TAB_ENTRIES * sizeof(FastTabEntry) : 0);
+static_assert(FAST_SMEM_NEED <= 232448, "stages exceed shared memory");
+static_assert(FAST_KERNEL == 6 || FAST_SMEM_NEED <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
+OEQ_DEV FastTabEntry* fast_tab(unsigned char* smem_raw) { return reinterpret_cast<FastTabEntry*>(smem_raw + FAST_V * sizeof(FastShared)); }
+// All threads of the CTA: copy the table into shared memory (before the CTA-wide barrier that follows the set-up).
+OEQ_DEV void fast_tab_fill(unsigned char* smem_raw) {
+    if (FAST_CFOLD) {
+        FastTabEntry* tab = fast_tab(smem_raw);
+        for (int q = threadIdx.x; q < FAST_TAB_ENTRIES; q += blockDim.x) { tab[q].c = FAST_CYC[q]; tab[q].j = FAST_CYJ[q]; }
+    }
+}
+// Consumer thread ltid of a stream: fold its share of the edge's coefficients, then wait until all have.
+OEQ_DEV bool fast_consumer_fold(FastShared& sh, FastStage& st, const FastTabEntry* tab, int s, unsigned par, int ltid,
+                                volatile int* abortf, int* status) {
+    if (!FAST_CFOLD) return true;
+#pragma unroll
+    for (int q = ltid; q < NCY; q += FAST_NT) {
+        float v = tab[q * FAST_CYT].c * st.y[tab[q * FAST_CYT].j];
+#pragma unroll
+        for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tab[q * FAST_CYT + m].c, st.y[tab[q * FAST_CYT + m].j], v);
+        st.cy[q] = v;
+    }
+    mbar_arrive(&sh.folded[FAST_CFOLD ? s : 0]);
+    return mbar_wait(&sh.folded[FAST_CFOLD ? s : 0], par, abortf, status, 25);
+}
 // TMA look-ahead in edges.  One stage stays in hand: in the backward pass for the dX row that is still leaving shared
 // memory (FAST_S >= FAST_D + 2); the forward pass measured fastest two edges ahead (7.07 ms against 7.23 / 7.36 ms at 3 / 4).
 constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 4) ? 2 : 1)
@@ -327,7 +358,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         if (i + FAST_D - FAST_NP < n) ldgsts_wait<FAST_D / FAST_NP - 1>(); else ldgsts_wait<0>();
         __syncwarp();
 #pragma unroll
-        for (int t = 0; t < CY_PER_LANE; ++t) {
+        for (int t = 0; t < (FAST_CFOLD ? 0 : CY_PER_LANE); ++t) {
             const int q = lane + 32 * t;
             if (q < NCY) {
                 float tc[FAST_CYT];
@@ -431,7 +462,7 @@ OEQ_DEV void weight_load(const float* w, int u, float* wv) {
 // subset of the output blocks (forward) or of the input blocks (backward) and runs only the paths that touch its
 // blocks, which keeps the per-thread row registers at the single-channel level.
 template <int KIND, int GRP>
-OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int tid) {
+OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int tid, const FastTabEntry* tab) {
     const int u = tid % FAST_GT;   // channel ch of this thread is chan(u, ch)
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
@@ -451,6 +482,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
         par ^= (s == 0);
         FastStage& st = sh.st[s];
         if (!mbar_wait(&sh.full[s], par, abortf, p.status, 21)) return;
+        if (!fast_consumer_fold(sh, st, tab, s, par, tid, abortf, p.status)) return;
         const long long row = st.row;
         const int last = st.last;
         // Paths are taken input block by input block, so that only one block of the sender row is in registers at a time.
@@ -567,12 +599,14 @@ OEQ_DEV void fast_forward_body(const FastParams& p) {
     if (tid < FAST_V) {   // thread v sets up stream v
         FastShared& sh = shs[tid];
         for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); }
+        for (int s = 0; s < (FAST_CFOLD ? FAST_S : 0); ++s) mbar_init(&sh.folded[s], FAST_NT);
         mbar_init(&sh.zfull, FAST_NT);
         mbar_init(&sh.zfree, 1);
         sh.abort_flag = 0;
         cta_range<KIND, true>(p, sh.range, tid);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    fast_tab_fill(fast_smem_raw);
     __syncthreads();
     if (tid >= FAST_V * FAST_NT) {
         fast_regs_producer();
@@ -583,12 +617,13 @@ OEQ_DEV void fast_forward_body(const FastParams& p) {
     fast_regs_consumer();
     FastShared& sh = shs[tid / FAST_NT];
     const int ltid = tid % FAST_NT;
-    if (FAST_NG == 1 || ltid < FAST_GT) fast_forward_group<KIND, 0>(p, sh, ltid); else fast_forward_group<KIND, 1>(p, sh, ltid);
+    const FastTabEntry* tab = fast_tab(fast_smem_raw);
+    if (FAST_NG == 1 || ltid < FAST_GT) fast_forward_group<KIND, 0>(p, sh, ltid, tab); else fast_forward_group<KIND, 1>(p, sh, ltid, tab);
 }
 
 // ---- backward ---------------------------------------------------------------------------------------------
 template <int KIND, int GRP>
-OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int tid) {
+OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int tid, const FastTabEntry* tab) {
     const int u = tid % FAST_GT, lane = tid & 31, warp = tid >> 5;
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
@@ -601,6 +636,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
         par ^= (s == 0);
         FastStage& st = sh.st[s];
         if (!mbar_wait(&sh.full[s], par, abortf, p.status, 22)) return;
+        if (!fast_consumer_fold(sh, st, tab, s, par, tid, abortf, p.status)) return;
         const long long row = st.row, e = st.edge;
         if (row != cur_row) {   // new receiver: its gradient row goes to registers for all of its edges
             const float* grow = p.G + row * L3_DIM;
@@ -693,10 +729,12 @@ OEQ_DEV void fast_backward_body(const FastParams& p) {
     if (tid < FAST_V) {   // thread v sets up stream v
         FastShared& sh = shs[tid];
         for (int s = 0; s < FAST_S; ++s) { mbar_init(&sh.full[s], 2); mbar_init(&sh.empty[s], FAST_NT); mbar_init(&sh.drained[s], 1); }
+        for (int s = 0; s < (FAST_CFOLD ? FAST_S : 0); ++s) mbar_init(&sh.folded[s], FAST_NT);
         sh.abort_flag = 0;
         cta_range<KIND, false>(p, sh.range, tid);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    fast_tab_fill(fast_smem_raw);
     __syncthreads();
     if (tid >= FAST_V * FAST_NT) {
         fast_regs_producer();
@@ -707,7 +745,8 @@ OEQ_DEV void fast_backward_body(const FastParams& p) {
     fast_regs_consumer();
     FastShared& sh = shs[tid / FAST_NT];
     const int ltid = tid % FAST_NT;
-    if (FAST_NG == 1 || ltid < FAST_GT) fast_backward_group<KIND, 0>(p, sh, ltid); else fast_backward_group<KIND, 1>(p, sh, ltid);
+    const FastTabEntry* tab = fast_tab(fast_smem_raw);
+    if (FAST_NG == 1 || ltid < FAST_GT) fast_backward_group<KIND, 0>(p, sh, ltid, tab); else fast_backward_group<KIND, 1>(p, sh, ltid, tab);
 }
 
 // ---- entry points (one per program: FAST_KERNEL selects which) ----------------------------------------------

@@ -47,6 +47,7 @@ bool g_no_tc = false;          // tuning aid: keep 'uvw' forward on the general 
 bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
 bool g_single_producer = false;   // tuning aid: one producer warp per CTA in the forward kernels too
 int g_validate = 1;            // index checks of convolution calls: 0 never, 1 first call per edge list, 2 every call
+bool g_streams_fwd = false;    // the forward kernels take part in `streams` too (the backward kernels always do)
 int g_streams = 1;             // edge streams per CTA on the channel-parallel path (1: two CTAs per SM; 2-4: one CTA with
                                // that many consumer sets and a register hand-over; measured slower on the benchmark graph)
 std::string g_cache_dir;
@@ -213,9 +214,13 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 // Several edge streams in one CTA per SM: consumer sets of exactly one warpgroup, three stages each
                 if (g_streams > 1 && g_streams <= 4 && nthreads == 128 && U == 128) {
                     const int V = g_streams;
-                    int SV = (int)(((232448 - 1024) / V - 256) / (stage + 24));
+                    int cyt = 1;
+                    for (auto& I : d.ins)
+                        for (auto& pr : ik_pairs(I)) cyt = std::max(cyt, (int)pr.terms.size());
+                    const size_t table = (size_t)ncy * cyt * 8;   // consumer-side folding: (coefficient, index) pairs
+                    int SV = (int)((((232448 - 1024 - table) / V) - 256) / (stage + 32));
                     if (SV > 4) SV = 4;
-                    if (SV >= 3) { d.fast_V = V; d.fast_SV = SV; d.fast_smemV = (size_t)V * ((size_t)SV * (stage + 24) + 128 + 64); }
+                    if (SV >= 3) { d.fast_V = V; d.fast_SV = SV; d.fast_smemV = (size_t)V * ((size_t)SV * (stage + 32) + 128 + 64) + table + 64; }
                 }
                 int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 24));
                 if (S3 > 6) S3 = 6;
@@ -583,7 +588,7 @@ int family_from_name(const std::string& n) {
 // Edge streams per CTA for a kernel family: the first-order kernels except the atomic forward (whose staged output
 // row leaves no room for three rings); 1 when the problem or the caller rules them out.
 int family_streams(const Desc& d, int fam, bool allow) {
-    const bool eligible = fam == FAM_FAST_FWD_TP || fam == FAM_FAST_FWD_DET || fam == FAM_FAST_BWD_TP ||
+    const bool eligible = ((fam == FAM_FAST_FWD_TP || fam == FAM_FAST_FWD_DET) && g_streams_fwd) || fam == FAM_FAST_BWD_TP ||
                           fam == FAM_FAST_BWD_DET || fam == FAM_FAST_BWD_ATOMIC;
     return (allow && eligible && d.fast && d.fast_V > 1) ? d.fast_V : 1;
 }
@@ -1151,6 +1156,7 @@ int oeqb_set_option(const char* name, const char* value) {
     else if (n == "single_group") g_single_group = atoi(value) != 0;
     else if (n == "single_producer") g_single_producer = atoi(value) != 0;
     else if (n == "streams") g_streams = atoi(value);
+    else if (n == "streams_forward") g_streams_fwd = atoi(value) != 0;
     else if (n == "validate") g_validate = atoi(value);
     else if (n == "no_tc") g_no_tc = atoi(value) != 0;
     else return fail(OEQB_EINVAL, "unknown option '%s'", name);
