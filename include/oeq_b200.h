@@ -126,6 +126,22 @@ OEQB_API int oeqb_conv_backward_rect(const void* desc, size_t desc_len, int64_t 
                             const void* rows, const void* cols, const void* transpose_perm,
                             void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The deterministic backward pass in two steps, for callers that need some rows of dX before the others (no counterpart in
+ * the reference): oeqb_conv_backward_edges runs the per-edge pass (dY, dW, and the per-edge dX rows into the workspace);
+ * oeqb_conv_backward_rows then sums the workspace rows of the senders [row_begin, row_end) into dX, and may be called
+ * several times with disjoint ranges, in any order, on the same stream or on streams ordered after the edge pass.  The
+ * partitioned driver reduces the rows it sends back to other GPUs first and overlaps their transfer with the rest.
+ * Together the calls give exactly oeqb_conv_backward_rect's result.  Only for deterministic descriptors that oeqb_query
+ * reports as fast_path = 1 (others: OEQB_EUNSUPPORTED, use oeqb_conv_backward_rect); workspace as for that call. */
+OEQB_API int oeqb_conv_backward_edges(const void* desc, size_t desc_len, int64_t key, int64_t n_receivers, int64_t n_nodes,
+                             int64_t n_edges, const void* X, const void* Y, const void* W, const void* G,
+                             void* dY, void* dW,
+                             const void* rows, const void* cols, const void* transpose_perm,
+                             void* workspace, int64_t workspace_bytes, void* stream);
+OEQB_API int oeqb_conv_backward_rows(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                            int64_t row_begin, int64_t row_end, const void* transpose_perm,
+                            void* workspace, int64_t workspace_bytes, void* dX, void* stream);
+
 /* Allocation-free variant of oeqb_conv_backward for deterministic convolutions on the channel-parallel kernels.
  * It has no counterpart in the reference.
  *

@@ -787,10 +787,11 @@ extern "C" __global__ void oeq_fixup_backward_offsets(const IDX* cols, const IDX
     for (long long c = prev + 1; c <= cur; ++c) colptr[c] = k;
 }
 // dX[c] = sum over the sender's edges, in sender-major list order, of the per-edge rows in scratch
+// (senders [c_begin, c_end): a partitioned caller reduces the rows it has to send away first)
 extern "C" __global__ void __launch_bounds__(256) oeq_fixup_backward_reduce(const float* scratch, const IDX* perm, const long long* colptr,
-                                                                     long long N, float* dX) {
+                                                                     long long c_begin, long long c_end, float* dX) {
     constexpr int NQ = L1_DIM / 4;
-    for (long long c = blockIdx.x; c < N; c += gridDim.x) {
+    for (long long c = c_begin + blockIdx.x; c < c_end; c += gridDim.x) {
         const long long k0 = colptr[c], k1 = colptr[c + 1];
         for (int q = threadIdx.x; q < NQ; q += 256) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -1012,23 +1012,36 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
 
-// dX[c] = sum of the per-edge rows in scratch over the sender's edges, in sender-major list order
-int fast_scatter(Entry* e, const void* scratch, const void* cols, const void* perm, long long N, long long E, void* colptr,
-                 void* dX, cudaStream_t st) {
+// dX[c] = sum of the per-edge rows in scratch over the sender's edges, in sender-major list order.  Two steps: the sender
+// offsets (once), then the row sums for a range of senders [c_begin, c_end).
+int fast_scatter_offsets(Entry* e, const void* cols, const void* perm, long long N, long long E, void* colptr, cudaStream_t st) {
     int rc;
     Program* prog;
     if ((rc = get_program(e, FAM_FAST_SCATTER, &prog))) return rc;
-    cudaKernel_t k1, k2;
+    cudaKernel_t k1;
     if ((rc = get_kernel(prog, "oeq_fixup_backward_offsets", 0, &k1))) return rc;
+    void* args[] = {(void*)&cols, (void*)&perm, &E, &N, &colptr};
+    return launch(k1, (unsigned)((E + 1 + 255) / 256), 256, 0, args, st);
+}
+
+int fast_scatter_rows(Entry* e, const void* scratch, const void* perm, const void* colptr, long long c_begin, long long c_end,
+                      void* dX, cudaStream_t st) {
+    if (c_end <= c_begin) return OEQB_OK;
+    int rc;
+    Program* prog;
+    if ((rc = get_program(e, FAM_FAST_SCATTER, &prog))) return rc;
+    cudaKernel_t k2;
     if ((rc = get_kernel(prog, "oeq_fixup_backward_reduce", 0, &k2))) return rc;
-    {
-        void* args[] = {(void*)&cols, (void*)&perm, &E, &N, &colptr};
-        if ((rc = launch(k1, (unsigned)((E + 1 + 255) / 256), 256, 0, args, st))) return rc;
-    }
     long long grid = (long long)sm_count() * 8;
-    if (grid > N) grid = N;
-    void* args[] = {(void*)&scratch, (void*)&perm, &colptr, &N, &dX};
+    if (grid > c_end - c_begin) grid = c_end - c_begin;
+    void* args[] = {(void*)&scratch, (void*)&perm, (void*)&colptr, &c_begin, &c_end, &dX};
     return launch(k2, (unsigned)grid, 256, 0, args, st);
+}
+
+int fast_scatter(Entry* e, const void* scratch, const void* cols, const void* perm, long long N, long long E, void* colptr,
+                 void* dX, cudaStream_t st) {
+    if (int rc = fast_scatter_offsets(e, cols, perm, N, E, colptr, st)) return rc;
+    return fast_scatter_rows(e, scratch, perm, colptr, 0, N, dX, st);
 }
 
 // ------------------------------------------------------------------- scratch that nobody has to allocate
@@ -1333,6 +1346,11 @@ static int conv_check(const Desc& d, int64_t n_nodes, int64_t n_edges, const voi
     return OEQB_OK;
 }
 
+static int conv_backward_impl(const void* desc, size_t desc_len, int64_t key, int64_t n_receivers, int64_t n_nodes,
+                              int64_t n_edges, const void* X, const void* Y, const void* W, const void* G, void* dX,
+                              void* dY, void* dW, const void* rows, const void* cols, const void* transpose_perm,
+                              void* workspace, int64_t workspace_bytes, void* stream, bool defer_rows);
+
 int oeqb_conv_forward(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
                       const void* X, const void* Y, const void* W, void* Z, const void* rows, const void* cols,
                       const void* transpose_perm, void* workspace, int64_t workspace_bytes, void* stream) {
@@ -1399,6 +1417,45 @@ int oeqb_conv_backward_rect(const void* desc, size_t desc_len, int64_t key, int6
                             int64_t n_edges, const void* X, const void* Y, const void* W, const void* G, void* dX,
                             void* dY, void* dW, const void* rows, const void* cols, const void* transpose_perm,
                             void* workspace, int64_t workspace_bytes, void* stream) {
+    return conv_backward_impl(desc, desc_len, key, n_receivers, n_nodes, n_edges, X, Y, W, G, dX, dY, dW, rows, cols,
+                              transpose_perm, workspace, workspace_bytes, stream, /*defer_rows=*/false);
+}
+
+int oeqb_conv_backward_edges(const void* desc, size_t desc_len, int64_t key, int64_t n_receivers, int64_t n_nodes,
+                             int64_t n_edges, const void* X, const void* Y, const void* W, const void* G, void* dY,
+                             void* dW, const void* rows, const void* cols, const void* transpose_perm, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+    // dX is not touched by this step; a non-null placeholder satisfies the common argument checks
+    return conv_backward_impl(desc, desc_len, key, n_receivers, n_nodes, n_edges, X, Y, W, G, workspace, dY, dW, rows, cols,
+                              transpose_perm, workspace, workspace_bytes, stream, /*defer_rows=*/true);
+}
+
+int oeqb_conv_backward_rows(const void* desc, size_t desc_len, int64_t key, int64_t n_nodes, int64_t n_edges,
+                            int64_t row_begin, int64_t row_end, const void* transpose_perm, void* workspace,
+                            int64_t workspace_bytes, void* dX, void* stream) {
+    if (row_begin < 0 || row_end > n_nodes || row_begin > row_end)
+        return fail(OEQB_EINVAL, "oeqb_conv_backward_rows: bad row range [%lld, %lld) of %lld", (long long)row_begin,
+                    (long long)row_end, (long long)n_nodes);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    const Desc& d = e->d;
+    if (!(d.conv && d.det && use_fast(d)))
+        return fail(OEQB_EUNSUPPORTED, "oeqb_conv_backward_rows: only after oeqb_conv_backward_edges (deterministic "
+                                       "convolutions on the channel-parallel kernels)");
+    const size_t scratch_bytes = round_up((size_t)n_edges * d.dim[0] * d.elt());
+    const size_t need = scratch_bytes + round_up((size_t)(n_nodes + 1) * 8);
+    if (!workspace || workspace_bytes < (int64_t)need || !dX || !transpose_perm || !aligned16({workspace, dX}))
+        return fail(OEQB_EINVAL, "oeqb_conv_backward_rows: needs the workspace of the matching oeqb_conv_backward_edges call "
+                                 "(%zu bytes), dX and transpose_perm", need);
+    return fast_scatter_rows(e, workspace, transpose_perm, (char*)workspace + scratch_bytes, row_begin, row_end, dX,
+                             (cudaStream_t)stream);
+}
+
+static int conv_backward_impl(const void* desc, size_t desc_len, int64_t key, int64_t n_receivers, int64_t n_nodes,
+                              int64_t n_edges, const void* X, const void* Y, const void* W, const void* G, void* dX,
+                              void* dY, void* dW, const void* rows, const void* cols, const void* transpose_perm,
+                              void* workspace, int64_t workspace_bytes, void* stream, bool defer_rows) {
     if (n_receivers < 0) return fail(OEQB_EINVAL, "oeqb_conv_backward_rect: negative size");
     std::lock_guard<std::mutex> lock(g_mutex);
     Entry* e;
@@ -1424,8 +1481,12 @@ int oeqb_conv_backward_rect(const void* desc, size_t desc_len, int64_t key, int6
         void* colptr = (char*)workspace + scratch_bytes;
         FastParams f{X, Y, W, G, nullptr, dX, dY, dW, workspace, rows, cols, n_nodes, n_edges, nullptr};
         if (int rc = fast_launch(e, 4, f, st)) return rc;
+        if (defer_rows) return fast_scatter_offsets(e, cols, transpose_perm, n_nodes, n_edges, colptr, st);
         return fast_scatter(e, workspace, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
     }
+    if (defer_rows)
+        return fail(OEQB_EUNSUPPORTED, "oeqb_conv_backward_edges: this problem (or these buffers) is not served by the "
+                                       "deterministic channel-parallel kernels; call oeqb_conv_backward");
     if (!d.det && fast) {
         CUDA_TRY(cudaMemsetAsync(dX, 0, n_nodes * d.dim[0] * d.elt(), st));
         FastParams f{X, Y, W, G, nullptr, dX, dY, dW, nullptr, rows, cols, n_nodes, n_edges, nullptr};

@@ -36,6 +36,8 @@ _PROTOTYPES = {
     "oeqb_conv_forward_rect": (c_int, _DESC + [c_int64, c_int64, c_int64] + [_P] * 8 + [c_int64, _P]),
     "oeqb_conv_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11 + [c_int64, _P]),
     "oeqb_conv_backward_rect": (c_int, _DESC + [c_int64, c_int64, c_int64] + [_P] * 11 + [c_int64, _P]),
+    "oeqb_conv_backward_edges": (c_int, _DESC + [c_int64, c_int64, c_int64] + [_P] * 10 + [c_int64, _P]),
+    "oeqb_conv_backward_rows": (c_int, _DESC + [c_int64, c_int64, c_int64, c_int64, _P, _P, c_int64, _P, _P]),
     "oeqb_conv_double_backward": (c_int, _DESC + [c_int64, c_int64] + [_P] * 15 + [c_int64, _P]),
     "oeqb_conv_backward_noalloc": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11),
     "oeqb_noalloc_status": (c_int, []),

@@ -231,6 +231,9 @@ class PartitionedConv:
         need = self.lib.oeqb_conv_workspace_bytes(self.desc, len(self.desc), self.key, 1, p.n_owned + p.n_halo, p.n_local_edges)
         self.workspace = torch.empty(max(int(need), 1), dtype=torch.uint8, device=device)
         self._keep = []
+        # the two-step backward (halo rows of dX first, their transfer overlapped with the owned rows) needs the
+        # channel-parallel deterministic kernels; other problems take the single call
+        self.split_backward = native.query(self.desc, self.key).fast_path == 1 and exchange is None and give_back is None
 
     @staticmethod
     def _p(t, byte_offset=0):
@@ -278,10 +281,32 @@ class PartitionedConv:
         dx_local = torch.empty((n_loc, self.L1), dtype=torch.float32, device=self.device)
         dY, dW = torch.empty_like(Y), torch.empty_like(W)
         main = torch.cuda.current_stream(self.device)
+        st = ctypes.c_void_p(main.cuda_stream)
+        if self.split_backward and p.world > 1 and p.n_local_edges > 0 and p.n_halo > 0:
+            # per-edge pass, then the halo rows of dX (the last n_halo local rows); they travel to their owners on the side
+            # stream while the owned rows are summed; the owners add what arrived at the end, in rank order
+            rc = self.lib.oeqb_conv_backward_edges(
+                self.desc, len(self.desc), self.key, p.n_owned, n_loc, p.n_local_edges, self._p(self.x_local), self._p(Y),
+                self._p(W), self._p(G), self._p(dY), self._p(dW), self._p(p.rows_local), self._p(p.cols_local),
+                self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(), st)
+            self.native.check(rc, "partitioned conv backward (edges)")
+            rc = self.lib.oeqb_conv_backward_rows(self.desc, len(self.desc), self.key, n_loc, p.n_local_edges, p.n_owned, n_loc,
+                                                  self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(),
+                                                  self._p(dx_local), st)
+            self.native.check(rc, "partitioned conv backward (halo rows)")
+            self.comm_stream.wait_stream(main)
+            with torch.cuda.stream(self.comm_stream):
+                received = send_halo_gradients(p, dx_local, self.group)
+            rc = self.lib.oeqb_conv_backward_rows(self.desc, len(self.desc), self.key, n_loc, p.n_local_edges, 0, p.n_owned,
+                                                  self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(),
+                                                  self._p(dx_local), st)
+            self.native.check(rc, "partitioned conv backward (owned rows)")
+            main.wait_stream(self.comm_stream)
+            return add_halo_gradients(p, dx_local, received), dY, dW
         rc = self.lib.oeqb_conv_backward_rect(
             self.desc, len(self.desc), self.key, p.n_owned, n_loc, p.n_local_edges, self._p(self.x_local), self._p(Y), self._p(W),
             self._p(G), self._p(dx_local), self._p(dY), self._p(dW), self._p(p.rows_local), self._p(p.cols_local),
-            self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(), ctypes.c_void_p(main.cuda_stream))
+            self._p(p.perm_local), self._p(self.workspace), self.workspace.numel(), st)
         self.native.check(rc, "partitioned conv backward")
         dX = self._give_back(p, dx_local)
         return dX, dY, dW

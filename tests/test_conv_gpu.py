@@ -174,3 +174,41 @@ def test_int32_indices_through_the_c_abi(graph):
         outs.append(Z.cpu())
     assert torch.equal(outs[0], outs[1])
     assert rel_l2(outs[1].numpy(), tp_oracle.forward(p, x, y, w, graph=(graph.rows, graph.cols))) <= 1e-5
+
+
+def test_two_step_backward_equals_the_single_call(graph):
+    """oeqb_conv_backward_edges + oeqb_conv_backward_rows (two row ranges, the later rows first, as the partitioned driver
+    calls them) against oeqb_conv_backward: identical bits for dX, dY and dW."""
+    import ctypes
+    from openequivariance_b200 import native
+    from openequivariance_b200.core.descriptor import build_descriptor, descriptor_hash
+    p = MATRIX["mace_medium"]
+    E, N = graph.nnz, graph.node_count
+    x, y, w, g, *_ = uniform_inputs(p, E, n_rows=N)
+    lib = native.load()
+    text = build_descriptor(p, conv=True, deterministic=True)
+    desc, key = text.encode(), descriptor_hash(text)
+    X, Y, W, G = (torch.tensor(a, device="cuda") for a in (x, y, w, g))
+    rows, cols, perm = (torch.tensor(a, device="cuda") for a in (graph.rows, graph.cols, graph.transpose_perm))
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    need = lib.oeqb_conv_workspace_bytes(desc, len(desc), key, 1, N, E)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    ref = [torch.full_like(t, float("nan")) for t in (X, Y, W)]
+    native.check(lib.oeqb_conv_backward(desc, len(desc), key, N, E, ptr(X), ptr(Y), ptr(W), ptr(G), ptr(ref[0]), ptr(ref[1]),
+                                        ptr(ref[2]), ptr(rows), ptr(cols), ptr(perm), ptr(ws), need, st), "single call")
+    got = [torch.full_like(t, float("nan")) for t in (X, Y, W)]
+    ws2 = torch.empty(need, dtype=torch.uint8, device="cuda")
+    native.check(lib.oeqb_conv_backward_edges(desc, len(desc), key, N, N, E, ptr(X), ptr(Y), ptr(W), ptr(G), ptr(got[1]),
+                                              ptr(got[2]), ptr(rows), ptr(cols), ptr(perm), ptr(ws2), need, st), "edges")
+    split = N - 11
+    native.check(lib.oeqb_conv_backward_rows(desc, len(desc), key, N, E, split, N, ptr(perm), ptr(ws2), need, ptr(got[0]), st), "rows")
+    native.check(lib.oeqb_conv_backward_rows(desc, len(desc), key, N, E, 0, split, ptr(perm), ptr(ws2), need, ptr(got[0]), st), "rows")
+    torch.cuda.synchronize()
+    for a, b, what in zip(got, ref, ("dX", "dY", "dW")):
+        assert torch.equal(a, b), what
+    # a problem without those kernels is refused
+    other = MATRIX["uvw_m4"]
+    text = build_descriptor(other, conv=True, deterministic=True)
+    rc = lib.oeqb_conv_backward_rows(text.encode(), len(text), descriptor_hash(text), N, E, 0, N, ptr(perm), ptr(ws2), need, ptr(got[0]), st)
+    assert rc == 5
