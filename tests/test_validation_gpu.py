@@ -223,13 +223,50 @@ def test_python_operator_layer_still_works():
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+_AOTI_PROBE = r"""
+import os, sys, torch
+class M(torch.nn.Module):
+    def forward(self, x):
+        return x * 2 + 1
+x = torch.randn(8, 4, device="cuda")
+ep = torch.export.export(M(), (x,), strict=False)
+path = torch._inductor.aoti_compile_and_package(ep, package_path=sys.argv[1])
+m = torch._inductor.aoti_load_package(path)
+assert torch.allclose(m(x), x * 2 + 1)
+print("aoti ok")
+"""
+_AOTI_STATE = {}
+
+
+def _gomp_fix(tmp_path):
+    """inductor links its wrapper with -fopenmp; a compiler installed outside the system prefix does not find a
+    libgomp.spec by itself.  Point it at torch's own libgomp through a spec file in a scratch directory."""
+    fix = tmp_path / "gomp"
+    fix.mkdir(exist_ok=True)
+    (fix / "libgomp.spec").write_text("*link_gomp: -lgomp %{static: -ldl }\n")
+    lib = os.path.join(os.path.dirname(torch.__file__), "lib", "libgomp.so.1")
+    if os.path.exists(lib) and not (fix / "libgomp.so").exists():
+        os.symlink(lib, fix / "libgomp.so")
+    return str(fix) + os.pathsep + os.environ.get("LIBRARY_PATH", "")
+
+
 def _aoti_package(tmp_path):
+    import subprocess
+    import sys
+    os.environ["LIBRARY_PATH"] = _gomp_fix(tmp_path)
+    if "ok" not in _AOTI_STATE:
+        # AOTInductor itself has to work on this machine: a package of a model without any custom operator, built and
+        # loaded in a child process (a broken tool chain crashes the loader instead of raising)
+        r = subprocess.run([sys.executable, "-c", _AOTI_PROBE, str(tmp_path / "probe.pt2")], capture_output=True, text=True,
+                           timeout=900)
+        _AOTI_STATE["ok"] = r.returncode == 0 and "aoti ok" in r.stdout
+        _AOTI_STATE["why"] = f"exit code {r.returncode}: {(r.stderr or r.stdout)[-200:]}"
+    if not _AOTI_STATE["ok"]:
+        pytest.skip("AOTInductor cannot build and load even a package without custom operators on this machine "
+                    f"({_AOTI_STATE['why']})")
     exe, bufs = _tp_and_buffers()
     ep = torch.export.export(exe, tuple(bufs), strict=False)
-    try:
-        path = torch._inductor.aoti_compile_and_package(ep, package_path=str(tmp_path / "tp.pt2"))
-    except Exception as exc:  # noqa: BLE001 - no working host compiler for inductor on this machine
-        pytest.skip(f"AOTInductor could not build a package here: {str(exc)[:200]}")
+    path = torch._inductor.aoti_compile_and_package(ep, package_path=str(tmp_path / "tp.pt2"))
     return exe, bufs, path
 
 
