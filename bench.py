@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-atomic", action="store_true", help="skip the atomic_variant object")
+    ap.add_argument("--no-double-backward", action="store_true", help="skip the double_backward object")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle spot check of the benchmarked step's outputs")
     ap.add_argument("--workload", default="conv",
                     choices=["conv", "conv_streamed", "tp_uvu", "tp_uvw", "tp_uvw64", "tp_readme"],
@@ -353,6 +354,8 @@ def bench_single(args, n_nodes, deterministic, dev):
         result["parity"] = parity_of_step(problem, conv, step, X, Y, W, G, rows, cols, n_nodes)
     if deterministic and not args.no_atomic:
         result["atomic_variant"] = bench_atomic_variant(args, problem, X, Y, W, G, rows, cols, gen, dev, n_nodes, E)
+    if not args.no_double_backward:
+        result["double_backward"] = bench_double_backward(problem, conv, X, Y, W, G, rows, cols, ws, p_arg, dev, E)
     if not args.no_e2e:
         result["e2e"] = bench_e2e(args, conv, problem, X, Y, W, G, rows, cols, perm if deterministic else None, dev, E)
     if not args.no_cpu_baseline:
@@ -364,6 +367,28 @@ def bench_single(args, n_nodes, deterministic, dev):
                                   "sample": f"{n_s} edges (receiver-contiguous slab of the same synthetic graph), "
                                             "torch-CPU fp32 einsum oracle, fwd+bwd; e3nn unavailable on this box"}
     return result
+
+
+def bench_double_backward(problem, conv, X, Y, W, G, rows, cols, ws, p_arg, dev, E):
+    """Second-order pass of the same convolution (the gradient of a gradient penalty): one ``jit_conv_double_backward`` call,
+    which returns dX, dY, dW and dG for the cotangents (X2, Y2, W2) of the first-order gradients."""
+    import torch
+    L1, L2, L3, wn = problem.irreps_in1.dim, problem.irreps_in2.dim, problem.irreps_out.dim, problem.weight_numel
+    gen = torch.Generator(device=dev).manual_seed(23)
+    X2 = torch.randn(X.shape, device=dev, generator=gen)
+    Y2 = torch.randn(Y.shape, device=dev, generator=gen)
+    W2 = torch.randn(W.shape, device=dev, generator=gen)
+    ops = torch.ops.libtorch_tp_jit
+
+    def step():
+        return ops.jit_conv_double_backward(conv.kernel, conv.hash, X, Y, W, G, X2, Y2, W2, rows, cols, ws, p_arg)
+
+    ms = timed_region(step, 3, 2, dev)
+    n = X.shape[0]
+    nbytes = 4 * (3 * n * L1 + 3 * E * (L2 + wn) + 2 * n * L3) + 24 * E      # every distinct input read once, every output written once
+    del X2, Y2, W2
+    return {"ms_per_step": ms, "edges_per_s": E / (ms * 1e-3), "steps": 3, "algorithmic_bytes": nbytes,
+            "gbs": nbytes / ms / 1e6}
 
 
 def bench_atomic_variant(args, problem, X, Y, W, G, rows, cols, gen, dev, n_nodes, E):

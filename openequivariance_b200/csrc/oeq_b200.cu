@@ -667,7 +667,9 @@ void write_file_atomic(const std::string& path, const std::string& data) {
 }
 
 // Compiles `src` for sm_100a; returns the cubin (from the disk cache when present).
-int compile_cubin(const std::string& src, const char* label, std::string& cubin) {
+// *from_cache (optional) receives the cache file's path when the cubin was read from it, "" when it was compiled now.
+int compile_cubin(const std::string& src, const char* label, std::string& cubin, std::string* from_cache = nullptr) {
+    if (from_cache) from_cache->clear();
     static const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo", "-default-device",
                                  "--extra-device-vectorization"};
     const int nopts = sizeof(opts) / sizeof(opts[0]);
@@ -681,6 +683,7 @@ int compile_cubin(const std::string& src, const char* label, std::string& cubin)
     const std::string path = cache_dir() + name;
     if (read_file(path, cubin)) {
         if (g_log) fprintf(stderr, "[oeq_b200] %s: cubin cache hit %s\n", label, path.c_str());
+        if (from_cache) *from_cache = path;
         return OEQB_OK;
     }
     nvrtcProgram prog;
@@ -716,6 +719,9 @@ struct Program {
 
 struct Entry {
     Desc d;
+    uint64_t desc_hash = 0;     // of the descriptor text this entry was built from: a key reused for another problem is refused
+    size_t desc_len = 0;
+    const void* seen_ptr = nullptr;   // last caller buffer whose contents were compared (callers pass the same buffer again)
     std::string header;
     std::unique_ptr<Program> prog[FAM_COUNT];
     std::unique_ptr<Program> prog_single[FAM_COUNT];   // the same families built with one edge stream per CTA
@@ -727,9 +733,22 @@ std::map<int64_t, std::unique_ptr<Entry>> g_entries;
 // Caller holds g_mutex.
 int get_entry(const void* desc, size_t len, int64_t key, Entry** out) {
     auto it = g_entries.find(key);
-    if (it != g_entries.end()) { *out = it->second.get(); return OEQB_OK; }
+    if (it != g_entries.end()) {
+        Entry* have = it->second.get();
+        if (desc && len > 0 && !(desc == have->seen_ptr && len == have->desc_len)) {
+            if (len != have->desc_len || fnv1a(std::string((const char*)desc, len)) != have->desc_hash)
+                return fail(OEQB_EINVAL, "key %lld was first used with a different descriptor: keys must identify one problem",
+                            (long long)key);
+            have->seen_ptr = desc;
+        }
+        *out = have;
+        return OEQB_OK;
+    }
     if (!desc || len == 0) return fail(OEQB_EINVAL, "descriptor is empty");
     auto e = std::make_unique<Entry>();
+    e->desc_hash = fnv1a(std::string((const char*)desc, len));
+    e->desc_len = len;
+    e->seen_ptr = desc;
     std::string why;
     if (!parse_desc((const char*)desc, len, e->d, why)) return fail(OEQB_EPARSE, "descriptor: %s", why.c_str());
     e->header = emit_header(e->d);
@@ -744,9 +763,19 @@ int get_program(Entry* e, int fam, Program** out, bool allow_streams = true) {
     if (slot) { *out = slot.get(); return OEQB_OK; }
     auto p = std::make_unique<Program>();
     const std::string src = family_source(e->d, e->header, fam, allow_streams);
-    int rc = compile_cubin(src, family_name(fam), p->cubin);
+    std::string cache_path;
+    int rc = compile_cubin(src, family_name(fam), p->cubin, &cache_path);
     if (rc) return rc;
     cudaError_t ce = cudaLibraryLoadData(&p->lib, p->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    if (ce != cudaSuccess && !cache_path.empty()) {
+        // a truncated or foreign file in the cache: drop it and compile afresh, once
+        cudaGetLastError();
+        remove(cache_path.c_str());
+        if (g_log) fprintf(stderr, "[oeq_b200] %s: cached cubin %s did not load (%s); recompiling\n", family_name(fam),
+                           cache_path.c_str(), cudaGetErrorString(ce));
+        if ((rc = compile_cubin(src, family_name(fam), p->cubin, nullptr))) return rc;
+        ce = cudaLibraryLoadData(&p->lib, p->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    }
     if (ce != cudaSuccess) return fail(OEQB_ECOMPILE, "cudaLibraryLoadData(%s): %s", family_name(fam), cudaGetErrorString(ce));
     *out = p.get();
     slot = std::move(p);

@@ -23,6 +23,10 @@ is not installed here and cannot be, so this file restates its published algorit
 Gradients of every order come from torch autograd on these einsums, which is how the reference's
 harness obtains e3nn's (``_torch/NPDoubleBackwardMixin.py:17-137``).
 
+The Wigner-3j tensors come from the product's ``openequivariance_b200.core.wigner.wigner_3j`` (the oracle does not carry a
+second construction); that function is pinned entry by entry against the reference's generator (item (1) below), so what this file
+adds, and what item (2) pins, is the contraction, the normalisation and the weight layout.
+
 Pinning status: PINNED.  (1) The Wigner-3j tensors, path weights, instruction tables and e3nn->kernel weight
 permutations are pinned entry-by-entry against the reference's own generator (tests/golden/wigner_3j.npz,
 problems.json, coord_graph.json; made by tests/golden/make_golden.py).  (2) The contraction itself -- forward and

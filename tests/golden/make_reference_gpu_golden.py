@@ -94,6 +94,46 @@ def run_conv(store):
         store[f"conv/{mode}/dw"] = conv.reorder_weights_to_e3nn(wt.grad.cpu().numpy(), True)
 
 
+def second_order_cases():
+    """The benchmark signatures themselves (MACE-like channelwise 'uvu', NequIP-like fully connected shared-weight 'uvw') and a
+    smaller channelwise problem, each with forward, backward and double backward."""
+    from openequivariance.benchmark.problems import ChannelwiseTPP, FullyConnectedTPProblem
+    feats = "128x0e+128x1o+128x2e+128x3o"
+    ir = "32x0e+32x0o+32x1e+32x1o+32x2e+32x2o"
+    return [("mace_like", ChannelwiseTPP(feats, "1x0e+1x1o+1x2e+1x3o", feats), 2),
+            ("nequip_like", FullyConnectedTPProblem(ir, "1x0e+1x1o+1x2e", ir, shared_weights=True), 3),
+            ("ctpp_32", ChannelwiseTPP("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"), 4)]
+
+
+def run_second_order(name, problem, batch, store):
+    """z, (dx, dy, dw) for the cotangent g, and the gradients of <dx,x2> + <dy,y2> + <dw,w2> w.r.t. (x, y, w, g): what the
+    reference's double-backward kernels return.  Weights and weight gradients are stored in e3nn order."""
+    import openequivariance as oeq
+    rng = np.random.default_rng(abs(hash(name)) % 1000 + 31)
+    shared = problem.shared_weights
+    wshape = (problem.weight_numel,) if shared else (batch, problem.weight_numel)
+    draw = lambda *shape: rng.uniform(-1.0, 1.0, size=shape).astype(np.float32)  # noqa: E731
+    x, x2 = draw(batch, problem.irreps_in1.dim), draw(batch, problem.irreps_in1.dim)
+    y, y2 = draw(batch, problem.irreps_in2.dim), draw(batch, problem.irreps_in2.dim)
+    w, w2 = draw(*wshape), draw(*wshape)
+    g = draw(batch, problem.irreps_out.dim)
+    tp = oeq.TensorProduct(problem)
+    t = lambda a: torch.tensor(a, device="cuda", requires_grad=True)  # noqa: E731
+    xt, yt, gt = t(x), t(y), t(g)
+    wt = t(tp.reorder_weights_from_e3nn(w, not shared))
+    w2t = torch.tensor(tp.reorder_weights_from_e3nn(w2, not shared), device="cuda")
+    z = tp(xt, yt, wt)
+    dx, dy, dw = torch.autograd.grad(z, [xt, yt, wt], gt, create_graph=True)
+    scalar = (dx * torch.tensor(x2, device="cuda")).sum() + (dy * torch.tensor(y2, device="cuda")).sum() + (dw * w2t).sum()
+    ddx, ddy, ddw, ddg = torch.autograd.grad(scalar, [xt, yt, wt, gt])
+    torch.cuda.synchronize()
+    back = lambda a: tp.reorder_weights_to_e3nn(a.detach().cpu().numpy(), not shared)  # noqa: E731
+    for key, val in (("x", x), ("y", y), ("w", w), ("g", g), ("x2", x2), ("y2", y2), ("w2", w2), ("z", z.detach().cpu().numpy()),
+                     ("dx", dx.detach().cpu().numpy()), ("dy", dy.detach().cpu().numpy()), ("dw", back(dw)),
+                     ("ddx", ddx.cpu().numpy()), ("ddy", ddy.cpu().numpy()), ("ddw", back(ddw)), ("ddg", ddg.cpu().numpy())):
+        store[f"tp2/{name}/{key}"] = val
+
+
 def bench(n_nodes, steps):
     """Reference kernels on the benchmark workload (graph and inputs built with this repository's seeded generators)."""
     import openequivariance as oeq
@@ -200,6 +240,7 @@ def main():
     ap.add_argument("--out", default="out/reference_gpu.npz")
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--bench-tp", action="store_true", help="time the reference's batched tensor-product kernels only")
+    ap.add_argument("--second-order", default="", help="also write the second-order fixtures (benchmark signatures) to this file")
     ap.add_argument("--nodes", type=int, default=50000)
     ap.add_argument("--steps", type=int, default=5)
     args = ap.parse_args()
@@ -218,6 +259,12 @@ def main():
     os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
     np.savez_compressed(args.out, **{k.replace("/", "__"): v for k, v in store.items()})
     print("fixtures:", len(store), "arrays ->", args.out)
+    if args.second_order:
+        store2 = {}
+        for name, problem, batch in second_order_cases():
+            run_second_order(name, problem, batch, store2)
+        np.savez_compressed(args.second_order, **{k.replace("/", "__"): v for k, v in store2.items()})
+        print("second-order fixtures:", len(store2), "arrays ->", args.second_order)
     if args.bench:
         t0 = time.time()
         print(json.dumps({"reference_on_gpu": bench(args.nodes, args.steps), "wall_s": round(time.time() - t0, 1)}))

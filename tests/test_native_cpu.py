@@ -97,3 +97,13 @@ def test_cpp_operator_library_defines_the_six_ops():
     for name in ops._SCHEMAS:
         op = getattr(torch.ops.libtorch_tp_jit, name)
         assert str(op.default._schema).replace(" ", "").startswith(f"libtorch_tp_jit::{name}(Tensorjson_bytes,inthash,")
+
+
+def test_a_key_reused_for_another_problem_is_refused():
+    a = build_descriptor(P.readme_problem())
+    b = build_descriptor(P.mace_like_problem())
+    key = 9_100_000_001
+    native.query(a.encode(), key)
+    native.query(a.encode(), key)                       # same problem again: fine
+    with pytest.raises(RuntimeError, match="different descriptor"):
+        native.query(b.encode(), key)

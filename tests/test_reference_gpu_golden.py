@@ -99,3 +99,48 @@ def test_kernels_match_reference_kernels_conv(mode):
     conv.backward_cpu(x, dx, y, dy, w, dw, g, graph)
     for mine, key in ((dx, "dx"), (dy, "dy"), (dw, "dw")):
         assert rel_l2(mine, _get(f"conv/{mode}", key)) <= TOL * 2
+
+
+# ---- second order, on the benchmark signatures themselves ------------------------------------------------------------
+# tests/golden/reference_gpu_second_order.npz (made by make_reference_gpu_golden.py --second-order): forward, backward and
+# double backward of the MACE-like and the NequIP-like problem (and a smaller channelwise one) as the unmodified reference's
+# kernels computed them on a B200.
+
+GOLD2 = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_gpu_second_order.npz"))
+TP2_CASES = {
+    "mace_like": lambda: P.mace_like_problem(),
+    "nequip_like": lambda: P.nequip_like_problem(),
+    "ctpp_32": lambda: P.ChannelwiseTPP("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),
+}
+# second-order results of fp32 kernels on inputs in [-1, 1): sums of thousands of terms with cancellation
+TOL2 = 1e-5
+
+
+def _get2(name, key):
+    return GOLD2[f"tp2__{name}__{key}"]
+
+
+@pytest.mark.parametrize("name", list(TP2_CASES))
+def test_oracle_matches_reference_kernels_second_order(name):
+    p = TP2_CASES[name]()
+    x, y, w, g, x2, y2, w2 = (_get2(name, k) for k in ("x", "y", "w", "g", "x2", "y2", "w2"))
+    assert rel_l2(tp_oracle.forward(p, x, y, w), _get2(name, "z")) <= TOL2
+    for mine, key in zip(tp_oracle.backward(p, x, y, w, g), ("dx", "dy", "dw")):
+        assert rel_l2(mine, _get2(name, key)) <= TOL2, key
+    for mine, key in zip(tp_oracle.double_backward(p, x, y, w, g, x2, y2, w2), ("ddx", "ddy", "ddw", "ddg")):
+        assert rel_l2(mine, _get2(name, key)) <= TOL2, key
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(TP2_CASES))
+def test_kernels_match_reference_kernels_second_order(name):
+    import openequivariance_b200 as oeq
+    p = TP2_CASES[name]()
+    tp = oeq.TensorProduct(p)
+    shared = p.shared_weights
+    x, y, w, g, x2, y2, w2 = (_get2(name, k) for k in ("x", "y", "w", "g", "x2", "y2", "w2"))
+    wk, w2k = tp.reorder_weights_from_e3nn(w, not shared), tp.reorder_weights_from_e3nn(w2, not shared)
+    got = tp.double_backward_cpu(x, y, g, wk, w2k, x2, y2)           # kernel-order weights in and out
+    got = (got[0], got[1], tp.reorder_weights_to_e3nn(got[2], not shared), got[3])
+    for mine, key in zip(got, ("ddx", "ddy", "ddw", "ddg")):
+        assert rel_l2(mine, _get2(name, key)) <= TOL2 * 2, key      # two fp32 implementations against each other
