@@ -112,8 +112,8 @@ TP2_CASES = {
     "nequip_like": lambda: P.nequip_like_problem(),
     "ctpp_32": lambda: P.ChannelwiseTPP("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),
 }
-# second-order results of fp32 kernels on inputs in [-1, 1): sums of thousands of terms with cancellation
-TOL2 = 1e-5
+# fp32 results of the reference's kernels against the fp64 oracle (measured: at most 1.7e-7 over all cases and orders)
+TOL2 = 1e-6
 
 
 def _get2(name, key):
