@@ -1,5 +1,5 @@
 // Channel-parallel, TMA-pipelined kernels for 'uvu' problems whose second operand has multiplicity 1 everywhere
-// and whose first operand uses one common multiplicity FU (the MACE-style channelwise product), fp32.
+// and whose first operand uses one common multiplicity FU (the MACE-style channelwise product), fp32 or fp64 (T).
 //
 // Work decomposition
 //   * one consumer thread per channel u (FU threads) handles every path of its channel, so all of an edge's
@@ -29,14 +29,14 @@
 #define FAST_ATOMIC 2   // convolution, any edge order, atomic / bulk-reduce scatter
 
 struct FastParams {
-    const float* X; const float* Y; const float* W; const float* G;
-    float* Z; float* dX; float* dY; float* dW; float* scratch;
+    const T* X; const T* Y; const T* W; const T* G;
+    T* Z; T* dX; T* dY; T* dW; T* scratch;
     const IDX* rows; const IDX* cols;
     long long N; long long E;
     int* status;
     int accum;          // forward kernels: add to the output rows instead of overwriting them
     int pad;
-    const float* X2; const float* Y2; const float* W2;   // second-order kernels: the cotangents of (dX, dY, dW)
+    const T* X2; const T* Y2; const T* W2;   // second-order kernels: the cotangents of (dX, dY, dW)
     const IDX* eorder;  // convolutions over an unsorted edge list: position -> edge id, grouped by receiver (or null:
                         // position = edge id).  rows / cols / Y / W / dY / dW are indexed by edge id.
 };
@@ -107,8 +107,12 @@ OEQ_DEV void tma_store_hint(void* dst, const void* src_smem, unsigned bytes, uns
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(dst), "r"(smem_u32(src_smem)), "r"(bytes), "l"(pol) : "memory");
 }
 OEQ_DEV void tma_reduce_add(void* dst, const void* src_smem, unsigned bytes) {
-    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
-                 "r"(bytes) : "memory");
+    if (sizeof(T) == 8)
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
+                     "r"(bytes) : "memory");
+    else
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
+                     "r"(bytes) : "memory");
 }
 OEQ_DEV void l2_prefetch(const void* src, unsigned bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
@@ -117,8 +121,9 @@ OEQ_DEV void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memo
 template <int N> OEQ_DEV void tma_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 template <int N> OEQ_DEV void tma_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 OEQ_DEV void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-OEQ_DEV void ldgsts4(void* dst_smem, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+OEQ_DEV void ldgsts4(void* dst_smem, const void* src) {   // one element of T
+    if (sizeof(T) == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
 OEQ_DEV void ldgsts_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> OEQ_DEV void ldgsts_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -153,20 +158,20 @@ constexpr int FAST_TAB_ENTRIES = FAST_CFOLD ? NCY * FAST_CYT : 1;
 constexpr int FAST_NYP = (L2_DIM <= 1) ? 1 : (L2_DIM <= 2) ? 2 : (L2_DIM <= 4) ? 4 : (L2_DIM <= 8) ? 8 : (L2_DIM <= 16) ? 16 : 32;
 constexpr int FAST_YPAD = (L2_DIM + 3) & ~3;
 struct __align__(16) FastStage {
-    float x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
-    float w[WN];
-    float cy[NCY];                   // folded coefficients of this edge: cy[q] = sum_j C[i_q][j][k_q] * y[j], one per (i, k) pair
-    float y[FAST_YPAD];
-    float cy2[FAST_DBL ? NCY : 4];   // second-order kernels: coefficients folded with Y2
-    float y2[FAST_DBL ? FAST_YPAD : 4];
-    float dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
+    T x[L1_DIM];                 // sender row; the backward pass overwrites it in place with the edge's dX row
+    T w[WN];
+    T cy[NCY];                   // folded coefficients of this edge: cy[q] = sum_j C[i_q][j][k_q] * y[j], one per (i, k) pair
+    T y[FAST_YPAD];
+    T cy2[FAST_DBL ? NCY : 4];   // second-order kernels: coefficients folded with Y2
+    T y2[FAST_DBL ? FAST_YPAD : 4];
+    T dyp[FAST_NCW][FAST_NYP];   // per-warp partial sums of dY
     long long edge, row, col;
     int first, last, pad0, pad1;
 };
 constexpr int FAST_ZBUF = (FAST_KERNEL == 2) ? L3_DIM : 4;   // atomic forward stages a receiver row for a bulk reduce
 struct __align__(16) FastShared {
     FastStage st[FAST_S];
-    float zbuf[FAST_ZBUF];
+    T zbuf[FAST_ZBUF];
     unsigned long long full[FAST_S];
     unsigned long long empty[FAST_S];
     unsigned long long drained[FAST_S];   // backward with two producers: the stage's dX row has left shared memory
@@ -177,7 +182,7 @@ struct __align__(16) FastShared {
     int pad[3];
 };
 // coefficient table for consumer-side folding, behind the streams' FastShared blocks: (coefficient, index into y) pairs
-struct FastTabEntry { float c; int j; };
+struct FastTabEntry { T c; int j; };
 constexpr size_t FAST_SMEM_NEED = FAST_V * sizeof(FastShared) + (FAST_CFOLD ? FAST_TAB_ENTRIES * sizeof(FastTabEntry) : 0);
 static_assert(FAST_SMEM_NEED <= 232448, "stages exceed shared memory");
 static_assert(FAST_KERNEL == 6 || FAST_SMEM_NEED <= FAST_SMEM_BYTES, "the host sized the dynamic shared memory too small");
@@ -195,9 +200,9 @@ OEQ_DEV bool fast_consumer_fold(FastShared& sh, FastStage& st, const FastTabEntr
     if (!FAST_CFOLD) return true;
 #pragma unroll
     for (int q = ltid; q < NCY; q += FAST_NT) {
-        float v = tab[q * FAST_CYT].c * st.y[tab[q * FAST_CYT].j];
+        T v = tab[q * FAST_CYT].c * st.y[tab[q * FAST_CYT].j];
 #pragma unroll
-        for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tab[q * FAST_CYT + m].c, st.y[tab[q * FAST_CYT + m].j], v);
+        for (int m = 1; m < FAST_CYT; ++m) v = oeq_fma(tab[q * FAST_CYT + m].c, st.y[tab[q * FAST_CYT + m].j], v);
         st.cy[q] = v;
     }
     mbar_arrive(&sh.folded[FAST_CFOLD ? s : 0]);
@@ -215,15 +220,15 @@ constexpr int FAST_D = (FAST_KERNEL <= 2) ? ((FAST_S >= 4) ? 2 : 1)
 // values a lane still carries, starting with the most distant partner, so 16 values cost 8 + 4 + 2 + 1 shuffles plus one
 // for the last lane bit; the order of the additions is fixed, hence reproducible.
 template <int N>
-OEQ_DEV void warp_reduce_transpose(float (&v)[N], int lane) {
+OEQ_DEV void warp_reduce_transpose(T (&v)[N], int lane) {
     int d = 16;
 #pragma unroll
     for (int h = N / 2; h >= 1; h >>= 1, d >>= 1) {
         const bool up = (lane & d) != 0;
 #pragma unroll
         for (int t = 0; t < h; ++t) {
-            const float send = up ? v[t] : v[t + h];
-            const float keep = up ? v[t + h] : v[t];
+            const T send = up ? v[t] : v[t + h];
+            const T keep = up ? v[t + h] : v[t];
             v[t] = keep + __shfl_xor_sync(0xffffffffu, send, d);
         }
     }
@@ -261,7 +266,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
     // memory, where it stays in the L1, every time)
     constexpr int CY_PER_LANE = (NCY + 31) / 32;
     constexpr bool TAB_IN_REGS = FAST_V == 1;
-    float tab_c[TAB_IN_REGS ? CY_PER_LANE : 1][FAST_CYT];
+    T tab_c[TAB_IN_REGS ? CY_PER_LANE : 1][FAST_CYT];
     int tab_j[TAB_IN_REGS ? CY_PER_LANE : 1][FAST_CYT];
     if (TAB_IN_REGS) {
 #pragma unroll
@@ -269,7 +274,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
             const int q = lane + 32 * t;
 #pragma unroll
             for (int m = 0; m < FAST_CYT; ++m) {
-                tab_c[TAB_IN_REGS ? t : 0][m] = (q < NCY) ? FAST_CYC[q * FAST_CYT + m] : 0.f;
+                tab_c[TAB_IN_REGS ? t : 0][m] = (q < NCY) ? FAST_CYC[q * FAST_CYT + m] : T(0);
                 tab_j[TAB_IN_REGS ? t : 0][m] = (q < NCY) ? FAST_CYJ[q * FAST_CYT + m] : 0;
             }
         }
@@ -326,22 +331,22 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         if (lane == 0) {
             if (BWD && KIND != FAST_TP && row != prefetched_row) {
                 // a receiver the consumers will reach in a few edges: bring its gradient row into the L2 now
-                l2_prefetch(p.G + row * L3_DIM, (unsigned)(L3_DIM * sizeof(float)));
+                l2_prefetch(p.G + row * L3_DIM, (unsigned)(L3_DIM * sizeof(T)));
                 prefetched_row = row;
             }
             st.edge = e; st.row = row; st.col = col;
             st.first = (ia == 0) || (KIND == FAST_TP);   // consumers also compare rows; see fast_backward
             st.last = (ia == n - 1) || (row != nxt) || (KIND == FAST_TP);
-            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN) * sizeof(float)));
+            mbar_arrive_expect_tx(&sh.full[s], (unsigned)((L1_DIM + WN) * sizeof(T)));
             // weight rows are read once: they should leave the L2 before the sender rows, which neighbouring receivers reuse
-            if (KIND == FAST_TP) tma_load_hint(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s], pol_stream);
-            else tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)), &sh.full[s]);
-            tma_load_hint(st.w, p.W + e * WN, (unsigned)(WN * sizeof(float)), &sh.full[s], pol_stream);
+            if (KIND == FAST_TP) tma_load_hint(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(T)), &sh.full[s], pol_stream);
+            else tma_load(st.x, p.X + col * L1_DIM, (unsigned)(L1_DIM * sizeof(T)), &sh.full[s]);
+            tma_load_hint(st.w, p.W + e * WN, (unsigned)(WN * sizeof(T)), &sh.full[s], pol_stream);
             // second-order kernels: the rows of X2 and W2 are read by the consumers straight from global memory (staging
             // them too would leave room for two stages only); bring them into the L2 ahead of the consumers
             if (FAST_DBL) {
-                l2_prefetch(p.W2 + e * WN, (unsigned)(WN * sizeof(float)));
-                l2_prefetch(p.X2 + col * L1_DIM, (unsigned)(L1_DIM * sizeof(float)));
+                l2_prefetch(p.W2 + e * WN, (unsigned)(WN * sizeof(T)));
+                l2_prefetch(p.X2 + col * L1_DIM, (unsigned)(L1_DIM * sizeof(T)));
             }
         }
         for (int j = lane; j < L2_DIM; j += 32) ldgsts4(&st.y[j], p.Y + e * L2_DIM + j);
@@ -361,21 +366,21 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         for (int t = 0; t < (FAST_CFOLD ? 0 : CY_PER_LANE); ++t) {
             const int q = lane + 32 * t;
             if (q < NCY) {
-                float tc[FAST_CYT];
+                T tc[FAST_CYT];
                 int tj[FAST_CYT];
 #pragma unroll
                 for (int m = 0; m < FAST_CYT; ++m) {
                     tc[m] = TAB_IN_REGS ? tab_c[TAB_IN_REGS ? t : 0][m] : __ldg(&FAST_CYC[q * FAST_CYT + m]);
                     tj[m] = TAB_IN_REGS ? tab_j[TAB_IN_REGS ? t : 0][m] : __ldg(&FAST_CYJ[q * FAST_CYT + m]);
                 }
-                float v = tc[0] * st.y[tj[0]];
+                T v = tc[0] * st.y[tj[0]];
 #pragma unroll
-                for (int m = 1; m < FAST_CYT; ++m) v = fmaf(tc[m], st.y[tj[m]], v);
+                for (int m = 1; m < FAST_CYT; ++m) v = oeq_fma(tc[m], st.y[tj[m]], v);
                 st.cy[q] = v;
                 if (FAST_DBL) {
-                    float v2 = tc[0] * st.y2[tj[0]];
+                    T v2 = tc[0] * st.y2[tj[0]];
 #pragma unroll
-                    for (int m = 1; m < FAST_CYT; ++m) v2 = fmaf(tc[m], st.y2[tj[m]], v2);
+                    for (int m = 1; m < FAST_CYT; ++m) v2 = oeq_fma(tc[m], st.y2[tj[m]], v2);
                     st.cy2[FAST_DBL ? q : 0] = v2;
                 }
             }
@@ -390,17 +395,17 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
         FastStage& st = sh.st[s];
         if (!mbar_wait(&sh.empty[s], par, abortf, p.status, 12)) return false;
         if (lane < L2_DIM) {
-            float tot = 0.f;
+            T tot = T(0);
 #pragma unroll
             for (int w = 0; w < FAST_NCW; ++w) tot += st.dyp[w][lane];
-            float* dst = p.dY + st.edge * L2_DIM + lane;
+            T* dst = p.dY + st.edge * L2_DIM + lane;
             *dst = tot;
         }
         if (lane == 0) {
-            float* row = (KIND == FAST_TP) ? p.dX + st.edge * L1_DIM : (KIND == FAST_DET) ? p.scratch + st.edge * L1_DIM
+            T* row = (KIND == FAST_TP) ? p.dX + st.edge * L1_DIM : (KIND == FAST_DET) ? p.scratch + st.edge * L1_DIM
                                                                                         : p.dX + st.col * L1_DIM;
-            if (KIND == FAST_ATOMIC) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(float)));
-            else tma_store_hint(row, st.x, (unsigned)(L1_DIM * sizeof(float)), pol_stream);
+            if (KIND == FAST_ATOMIC) tma_reduce_add(row, st.x, (unsigned)(L1_DIM * sizeof(T)));
+            else tma_store_hint(row, st.x, (unsigned)(L1_DIM * sizeof(T)), pol_stream);
         }
         tma_commit();
         if (FAST_NP == 2) {   // tell whichever producer reuses the stage that the row has been read out
@@ -430,7 +435,7 @@ OEQ_DEV void fast_producer(const FastParams& p, FastShared& sh, int lane, const 
 // neighbouring channels and moving them with 8-byte accesses was measured: no faster.)
 OEQ_DEV int chan(int u, int ch) { return u + ch * FAST_GT; }
 template <class BLK>
-OEQ_DEV void block_load(const float* row, int u, float* v) {
+OEQ_DEV void block_load(const T* row, int u, T* v) {
 #pragma unroll
     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
@@ -439,18 +444,18 @@ OEQ_DEV void block_load(const float* row, int u, float* v) {
 // the reverse; ADD: add to what the row holds; STREAM: global row that is not read again soon (evict-first stores).
 // a(ch, i) yields the value of channel ch, component i.
 template <class BLK, bool ADD, bool STREAM, class F>
-OEQ_DEV void block_store(float* row, int u, F&& a) {
+OEQ_DEV void block_store(T* row, int u, F&& a) {
 #pragma unroll
     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
         for (int i = 0; i < BLK::D; ++i) {
-            float* dst = row + feat_idx<BLK::OFF, BLK::MUL, BLK::D>(chan(u, ch), i);
-            const float t = ADD ? *dst + a(ch, i) : a(ch, i);
+            T* dst = row + feat_idx<BLK::OFF, BLK::MUL, BLK::D>(chan(u, ch), i);
+            const T t = ADD ? *dst + a(ch, i) : a(ch, i);
             if (STREAM) __stcs(dst, t); else *dst = t;
         }
 }
 template <int WOFF>
-OEQ_DEV void weight_load(const float* w, int u, float* wv) {
+OEQ_DEV void weight_load(const T* w, int u, T* wv) {
 #pragma unroll
     for (int ch = 0; ch < FAST_CH; ++ch) wv[ch] = w[WOFF + chan(u, ch)];
 }
@@ -466,14 +471,14 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
     const int u = tid % FAST_GT;   // channel ch of this thread is chan(u, ch)
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
-    float acc[FAST_CH * FAST_GPC];
+    T acc[FAST_CH * FAST_GPC];
 #pragma unroll
-    for (int k = 0; k < FAST_CH * FAST_GPC; ++k) acc[k] = 0.f;
+    for (int k = 0; k < FAST_CH * FAST_GPC; ++k) acc[k] = T(0);
     long long next_row = sh.range[2];
     long long nseg = 0;                                // receiver rows this CTA has handed to the bulk reduce
     auto zero_rows = [&](long long a, long long b) {   // receivers without edges
         for (long long r = a; r < b; ++r)
-            for (int q = tid; q < L3_DIM; q += FAST_NT) p.Z[r * L3_DIM + q] = 0.f;
+            for (int q = tid; q < L3_DIM; q += FAST_NT) p.Z[r * L3_DIM + q] = T(0);
     };
     int s = -1;          // stage of edge i and the parity of its use: the ring is walked with counters, not divisions
     unsigned par = 1;
@@ -486,34 +491,34 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
         const long long row = st.row;
         const int last = st.last;
         // Paths are taken input block by input block, so that only one block of the sender row is in registers at a time.
-        const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
+        const T4* cy4 = reinterpret_cast<const T4*>(st.cy);
         static_for<0, NB1>([&](auto bc) {
             constexpr int B = decltype(bc)::value;
             using B1 = Blk1<B>;
             if constexpr ((GRP == 0 ? FP_FWD_NEEDS_X0[B] : FP_FWD_NEEDS_X1[B]) != 0) {
-                float xb[FAST_CH * B1::D];
+                T xb[FAST_CH * B1::D];
                 block_load<B1>(st.x, u, xb);
 #if FAST_FWD3
-                float x2b[FAST_CH * B1::D];
+                T x2b[FAST_CH * B1::D];
                 {
-                    const float* x2row = p.X2 + st.col * L1_DIM;
+                    const T* x2row = p.X2 + st.col * L1_DIM;
 #pragma unroll
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                         for (int i1 = 0; i1 < B1::D; ++i1)
                             x2b[ch * B1::D + i1] = __ldg(x2row + feat_idx<B1::OFF, B1::MUL, B1::D>(chan(u, ch), i1));
                 }
-                const float4* cy4b = reinterpret_cast<const float4*>(st.cy2);
-                const float* w2row = p.W2 + st.edge * WN;
+                const T4* cy4b = reinterpret_cast<const T4*>(st.cy2);
+                const T* w2row = p.W2 + st.edge * WN;
 #endif
                 static_for<0, NINS>([&](auto ic) {
                     constexpr int I = decltype(ic)::value;
                     using F = FIns<I>;
                     if constexpr (F::A == B && FP_INS_GF[I] == GRP) {
-                        float wv[FAST_CH];
+                        T wv[FAST_CH];
                         weight_load<F::WOFF>(st.w, u, wv);
 #if FAST_FWD3
-                        float w2v[FAST_CH];
+                        T w2v[FAST_CH];
 #pragma unroll
                         for (int ch = 0; ch < FAST_CH; ++ch) w2v[ch] = __ldg(w2row + F::WOFF + chan(u, ch));
                         F::fwd3(xb, x2b, cy4, cy4b, wv, w2v, acc + F::GO);
@@ -538,14 +543,14 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
 #pragma unroll
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
-                        for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = 0.f;
+                        for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = T(0);
                 }
             });
             fence_async_smem();
             mbar_arrive(&sh.zfull);
             if (tid == 0) {
                 if (!mbar_wait(&sh.zfull, (unsigned)(nseg & 1), abortf, p.status, 24)) return;
-                tma_reduce_add(p.Z + row * L3_DIM, sh.zbuf, (unsigned)(L3_DIM * sizeof(float)));
+                tma_reduce_add(p.Z + row * L3_DIM, sh.zbuf, (unsigned)(L3_DIM * sizeof(T)));
                 tma_commit();
                 tma_wait_read<0>();
                 mbar_arrive(&sh.zfree);
@@ -553,7 +558,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
             ++nseg;
         } else if (last) {
             if (KIND == FAST_DET && !p.accum) { zero_rows(next_row, row); next_row = row + 1; }
-            float* zrow = p.Z + row * L3_DIM;
+            T* zrow = p.Z + row * L3_DIM;
             static_for<0, NB3>([&](auto oc) {
                 constexpr int O = decltype(oc)::value;
                 using B3 = Blk3<O>;
@@ -573,7 +578,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
 #pragma unroll
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
-                        for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = 0.f;
+                        for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = T(0);
                 }
             });
         }
@@ -627,7 +632,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
     const int u = tid % FAST_GT, lane = tid & 31, warp = tid >> 5;
     const long long n = sh.range[1] - sh.range[0];
     volatile int* abortf = &sh.abort_flag;
-    float g[FAST_CH * FAST_GPC];
+    T g[FAST_CH * FAST_GPC];
     long long cur_row = -1;
     int s = -1;
     unsigned par = 1;
@@ -639,7 +644,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
         if (!fast_consumer_fold(sh, st, tab, s, par, tid, abortf, p.status)) return;
         const long long row = st.row, e = st.edge;
         if (row != cur_row) {   // new receiver: its gradient row goes to registers for all of its edges
-            const float* grow = p.G + row * L3_DIM;
+            const T* grow = p.G + row * L3_DIM;
             static_for<0, NB3>([&](auto oc) {
                 constexpr int O = decltype(oc)::value;
                 using B3 = Blk3<O>;
@@ -653,16 +658,16 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
             });
             cur_row = row;
         }
-        float dyr[FAST_NYP];
+        T dyr[FAST_NYP];
 #pragma unroll
-        for (int j = 0; j < FAST_NYP; ++j) dyr[j] = 0.f;
-        const float4* cy4 = reinterpret_cast<const float4*>(st.cy);
-        float* dwrow = p.dW + e * WN;
+        for (int j = 0; j < FAST_NYP; ++j) dyr[j] = T(0);
+        const T4* cy4 = reinterpret_cast<const T4*>(st.cy);
+        T* dwrow = p.dW + e * WN;
         // second-order backward: this thread's entries of the W2 row, all requested now and used path by path
-        float wdxv[FAST_DBL ? FAST_CH * NINS : 1];
-        const float4* cy4b = reinterpret_cast<const float4*>(st.cy2);
+        T wdxv[FAST_DBL ? FAST_CH * NINS : 1];
+        const T4* cy4b = reinterpret_cast<const T4*>(st.cy2);
         if (FAST_DBL) {
-            const float* wdxrow = p.W2 + e * WN;
+            const T* wdxrow = p.W2 + e * WN;
             static_for<0, NINS>([&](auto ic) {
                 constexpr int I = decltype(ic)::value;
                 if constexpr (FP_INS_GB[I] == GRP) {
@@ -677,14 +682,14 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
             constexpr int B = decltype(bc)::value;
             using B1 = Blk1<B>;
             if constexpr (FP_X_OWNER[B] == GRP) {
-                float xb[FAST_CH * B1::D], dxb[FAST_CH * B1::D];
+                T xb[FAST_CH * B1::D], dxb[FAST_CH * B1::D];
                 block_load<B1>(st.x, u, xb);
 #pragma unroll
-                for (int q = 0; q < FAST_CH * B1::D; ++q) dxb[q] = 0.f;
+                for (int q = 0; q < FAST_CH * B1::D; ++q) dxb[q] = T(0);
 #if FAST_DBL
-                float x2b[FAST_CH * B1::D];
+                T x2b[FAST_CH * B1::D];
                 {
-                    const float* x2row = p.X2 + st.col * L1_DIM;
+                    const T* x2row = p.X2 + st.col * L1_DIM;
 #pragma unroll
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
@@ -696,7 +701,7 @@ OEQ_DEV void fast_backward_group(const FastParams& p, FastShared& sh, const int 
                     constexpr int I = decltype(ic)::value;
                     using F = FIns<I>;
                     if constexpr (F::A == B && FP_INS_GB[I] == GRP) {
-                        float wv[FAST_CH], wx[FAST_CH], dw[FAST_CH];
+                        T wv[FAST_CH], wx[FAST_CH], dw[FAST_CH];
 #pragma unroll
                         for (int ch = 0; ch < FAST_CH; ++ch) {
                             wv[ch] = st.w[F::WOFF + chan(u, ch)];
@@ -788,30 +793,31 @@ extern "C" __global__ void oeq_fixup_backward_offsets(const IDX* cols, const IDX
 }
 // dX[c] = sum over the sender's edges, in sender-major list order, of the per-edge rows in scratch
 // (senders [c_begin, c_end): a partitioned caller reduces the rows it has to send away first)
-extern "C" __global__ void __launch_bounds__(256) oeq_fixup_backward_reduce(const float* scratch, const IDX* perm, const long long* colptr,
-                                                                     long long c_begin, long long c_end, float* dX) {
-    constexpr int NQ = L1_DIM / 4;
+extern "C" __global__ void __launch_bounds__(256) oeq_fixup_backward_reduce(const T* scratch, const IDX* perm, const long long* colptr,
+                                                                     long long c_begin, long long c_end, T* dX) {
+    constexpr int VE = 16 / sizeof(T);          // elements per 16-byte piece
+    constexpr int NQ = L1_DIM / VE;
+    struct __align__(16) Piece { T v[VE]; };
+    auto load = [&](long long e, int q) { return __ldcs(reinterpret_cast<const float4*>(scratch + e * L1_DIM) + q); };
     for (long long c = c_begin + blockIdx.x; c < c_end; c += gridDim.x) {
         const long long k0 = colptr[c], k1 = colptr[c + 1];
         for (int q = threadIdx.x; q < NQ; q += 256) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            Piece acc;
+#pragma unroll
+            for (int t = 0; t < VE; ++t) acc.v[t] = T(0);
+            auto add = [&](const float4& raw) {
+                const Piece& pc = reinterpret_cast<const Piece&>(raw);
+#pragma unroll
+                for (int t = 0; t < VE; ++t) acc.v[t] += pc.v[t];
+            };
             long long k = k0;
             for (; k + 4 <= k1; k += 4) {
                 const long long ea = perm[k], eb = perm[k + 1], ec = perm[k + 2], ed = perm[k + 3];
-                const float4 a = __ldcs(reinterpret_cast<const float4*>(scratch + ea * L1_DIM) + q);
-                const float4 b = __ldcs(reinterpret_cast<const float4*>(scratch + eb * L1_DIM) + q);
-                const float4 cc = __ldcs(reinterpret_cast<const float4*>(scratch + ec * L1_DIM) + q);
-                const float4 d = __ldcs(reinterpret_cast<const float4*>(scratch + ed * L1_DIM) + q);
-                acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-                acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
-                acc.x += cc.x; acc.y += cc.y; acc.z += cc.z; acc.w += cc.w;
-                acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+                const float4 a = load(ea, q), b = load(eb, q), cc = load(ec, q), d = load(ed, q);
+                add(a); add(b); add(cc); add(d);
             }
-            for (; k < k1; ++k) {
-                const float4 a = __ldcs(reinterpret_cast<const float4*>(scratch + (long long)perm[k] * L1_DIM) + q);
-                acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-            }
-            reinterpret_cast<float4*>(dX + c * L1_DIM)[q] = acc;
+            for (; k < k1; ++k) add(load((long long)perm[k], q));
+            reinterpret_cast<Piece*>(dX + c * L1_DIM)[q] = acc;
         }
     }
 }

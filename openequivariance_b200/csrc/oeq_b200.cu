@@ -100,6 +100,7 @@ struct Desc {
     int fast_ncy = 0;    // folded-coefficient slots per edge (each instruction padded to a multiple of 4)
     int fast_ng = 1;     // thread groups sharing an edge
     int fast_ch = 1;     // channels carried by one consumer thread
+    int fast_bwd_ng = 1; // thread groups of the backward kernels (2 in the fp64 configuration)
     size_t fast_smem = 0;
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
@@ -171,48 +172,54 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     if (d.layout == 1 && d.uvw) return bad("ir_mul layout with uvw");
     if (d.dim[0] * 1LL > (1LL << 24) || d.dim[2] > (1LL << 24) || d.wn > (1LL << 30)) return bad("problem too large");
 
-    // Fast path: fp32, either layout, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
+    // Fast path: fp32 or fp64, either layout, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
     // that is a multiple of 32, l <= 4 everywhere, no Kahan, rows small enough to live in registers.
+    // fp64 takes the "wide" configuration: one channel per thread in two block-owning thread groups (forward and
+    // backward), so that half a gradient row of doubles fits a thread's registers, and one CTA per SM for the doubled stages.
     d.fast = false;
-    if (d.dtype == 1 && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
+    if ((d.dtype == 1 || d.dtype == 2) && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
+        const bool wide = d.dtype == 2;
         bool ok = true;
         int U = d.L[0][0].mul;
         for (auto& b : d.L[0]) ok = ok && b.mul == U && b.l <= 4;
         for (auto& b : d.L[1]) ok = ok && b.mul == 1 && b.l <= 4;
         for (auto& b : d.L[2]) ok = ok && b.mul == U && b.l <= 4;
-        ok = ok && U >= 32 && U % 32 == 0 && U <= 256 && d.dim[1] <= 32;
+        ok = ok && U >= 32 && U % 32 == 0 && U <= (wide ? 128 : 256) && d.dim[1] <= 32;
         ok = ok && d.dim[0] / U <= 32 && d.dim[2] / U <= 112;
         if (ok) {
+            const size_t elt = d.elt();
             int ncy = 0;
             for (auto& I : d.ins) ncy += ((int)ik_pairs(I).size() + 3) & ~3;
             const int nyp = d.dim[1] <= 1 ? 1 : d.dim[1] <= 2 ? 2 : d.dim[1] <= 4 ? 4 : d.dim[1] <= 8 ? 8 : d.dim[1] <= 16 ? 16 : 32;
             // Two channels per thread halve the shared-memory traffic of the coefficient loads; the row registers
             // that doubles are won back by dealing the blocks to two thread groups.
-            const int ch = (!g_single_group && U % 64 == 0 && d.ins.size() >= 2) ? 2 : 1;
-            const int ng = ch == 2 ? 2 : 1;
-            const int nthreads = ng * U / ch;
-            const size_t stage = ((4 * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + (nthreads / 32) * nyp) + 72) + 15) & ~(size_t)15;
-            int ctas = 256 / U;
+            const int ch = (!wide && !g_single_group && U % 64 == 0 && d.ins.size() >= 2) ? 2 : 1;
+            const int ng = (ch == 2 || (wide && d.ins.size() >= 2 && d.L[0].size() >= 2 && d.L[2].size() >= 2)) ? 2 : 1;
+            const int bwd_ng = wide ? ng : 1;
+            const int nthreads = std::max(ng * U / ch, bwd_ng * U);
+            const size_t stage = ((elt * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + 8 + (nthreads / 32) * nyp) + 40) + 15) & ~(size_t)15;
+            int ctas = wide ? 1 : 256 / U;
             ctas = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas);
             while (ctas > 1 && ctas * (nthreads + 32) * (ch == 2 ? 168 : 128) > 65536) --ctas;   // registers per thread
             int S = 0;
             for (; ctas >= 1; ctas /= 2) {
                 const size_t budget = 232448 / ctas - 1024 - 256;
-                S = (int)(budget / (stage + 24));
+                S = (int)(budget / (stage + 32));
                 if (S > 6) S = 6;
                 if (S >= 3) break;
             }
-            if (S >= 3 && ctas >= 1) {
+            if (S >= 3 && ctas >= 1 && nthreads + 64 <= 1024) {
                 d.fast = true;
                 d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
-                d.fast_smem = (size_t)S * (stage + 24) + 128;
-                const size_t stage4 = stage + 4 * (size_t)(ncy + ((d.dim[1] + 3) & ~3));
-                int S4 = (int)((232448 / ctas - 1024 - 256) / (stage4 + 24));
+                d.fast_bwd_ng = bwd_ng;
+                d.fast_smem = (size_t)S * (stage + 32) + 160;
+                const size_t stage4 = stage + elt * (size_t)(ncy + ((d.dim[1] + 3) & ~3));
+                int S4 = wide ? 0 : (int)((232448 / ctas - 1024 - 256) / (stage4 + 32));
                 if (S4 > 6) S4 = 6;
                 d.fast_S4 = S4;    // < 3: second-order passes run on the general kernels
-                d.fast_smem4 = (size_t)S4 * (stage4 + 24) + 128;
+                d.fast_smem4 = (size_t)S4 * (stage4 + 32) + 160;
                 // Several edge streams in one CTA per SM: consumer sets of exactly one warpgroup, three stages each
-                if (g_streams > 1 && g_streams <= 4 && nthreads == 128 && U == 128) {
+                if (!wide && g_streams > 1 && g_streams <= 4 && nthreads == 128 && U == 128) {
                     const int V = g_streams;
                     int cyt = 1;
                     for (auto& I : d.ins)
@@ -222,10 +229,10 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                     if (SV > 4) SV = 4;
                     if (SV >= 3) { d.fast_V = V; d.fast_SV = SV; d.fast_smemV = (size_t)V * ((size_t)SV * (stage + 32) + 128 + 64) + table + 64; }
                 }
-                int S3 = (int)((232448 / ctas - 1024 - 256 - 4 * (size_t)d.dim[2]) / (stage + 24));
+                int S3 = wide ? 0 : (int)((232448 / ctas - 1024 - 256 - elt * (size_t)d.dim[2]) / (stage + 32));
                 if (S3 > 6) S3 = 6;
                 d.fast_S3 = S3;    // < 2: atomic forward falls back to the general kernel
-                d.fast_smem3 = (size_t)(S3 > 0 ? S3 : 0) * (stage + 24) + 4 * (size_t)d.dim[2] + 160;
+                d.fast_smem3 = (size_t)(S3 > 0 ? S3 : 0) * (stage + 32) + elt * (size_t)d.dim[2] + 192;
             }
         }
     }
@@ -322,6 +329,10 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
+    // element type T comes from the problem header; T4 = four of them (16 or 32 bytes), oeq_fma = fused multiply-add on T
+    s << "template <class R> struct OeqVec4;\ntemplate <> struct OeqVec4<float> { typedef float4 type; };\n"
+         "template <> struct OeqVec4<double> { typedef double4 type; };\ntypedef OeqVec4<T>::type T4;\n"
+         "OEQ_DEV T oeq_fma(T a, T b, T c) { return fma(a, b, c); }\n";
     s << "#define FAST_DBL " << (dbl ? 1 : 0) << "\n";
     s << "constexpr int FAST_V = " << streams << ";\n";
     s << "constexpr int FAST_NP = " << (streams > 1 ? 1 : fast_producers(stages)) << ";\n";
@@ -344,13 +355,13 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
         for (int q = 0; q < pad; ++q)
             for (int t = 0; t < cyt; ++t) {
                 const bool real = q < np && t < (int)pairs[n][q].terms.size();
-                cyc << (real ? hexf(pairs[n][q].terms[t].c) : std::string("0.0")) << "f, ";
+                cyc << "T(" << (real ? hexf(pairs[n][q].terms[t].c) : std::string("0.0")) << "), ";
                 cyj << (real ? d.L[1][d.ins[n].b].off + pairs[n][q].terms[t].j : 0) << ", ";
             }
         off += pad;
     }
     s << "constexpr int FAST_CYT = " << cyt << ";\n";
-    s << "__device__ const float FAST_CYC[NCY * FAST_CYT] = {" << cyc.str() << "};\n";
+    s << "__device__ const T FAST_CYC[NCY * FAST_CYT] = {" << cyc.str() << "};\n";
     s << "__device__ const int FAST_CYJ[NCY * FAST_CYT] = {" << cyj.str() << "};\n";
     s << "template <int I> struct FIns;\n";
     const char comp[4] = {'x', 'y', 'z', 'w'};
@@ -364,49 +375,49 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
         s << "  static constexpr int A = " << I.a << ", XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
           << ", CY4 = " << cyoff[n] / 4 << ", WOFF = " << I.woff << ", D1 = " << D1 << ", D3 = " << D3 << ";\n";
         // ---- forward: FAST_CH channels per thread share the coefficient loads
-        s << "  static OEQ_DEV void fwd(const float* x, const float4* cy, const float* w, float* acc) {\n";
-        for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
+        s << "  static OEQ_DEV void fwd(const T* x, const T4* cy, const T* w, T* acc) {\n";
+        for (int q = 0; q < nq; ++q) s << "    const T4 c" << q << " = cy[CY4 + " << q << "];\n";
         s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-        s << "      const float* xc = x + ch * D1; float* ac = acc + ch * FAST_GPC; const float wc = w[ch];\n";
+        s << "      const T* xc = x + ch * D1; T* ac = acc + ch * FAST_GPC; const T wc = w[ch];\n";
         if (D1 <= D3) {
-            for (int i = 0; i < D1; ++i) s << "      const float xs" << i << " = wc * xc[" << i << "];\n";
+            for (int i = 0; i < D1; ++i) s << "      const T xs" << i << " = wc * xc[" << i << "];\n";
             for (int z = 0; z < np; ++z)
-                s << "      ac[" << P[z].k << "] = fmaf(" << C(z) << ", xs" << P[z].i << ", ac[" << P[z].k << "]);\n";
+                s << "      ac[" << P[z].k << "] = oeq_fma(" << C(z) << ", xs" << P[z].i << ", ac[" << P[z].k << "]);\n";
         } else {
-            for (int k = 0; k < D3; ++k) s << "      float t" << k << " = 0.f;\n";
+            for (int k = 0; k < D3; ++k) s << "      T t" << k << " = T(0);\n";
             for (int z = 0; z < np; ++z)
-                s << "      t" << P[z].k << " = fmaf(" << C(z) << ", xc[" << P[z].i << "], t" << P[z].k << ");\n";
-            for (int k = 0; k < D3; ++k) s << "      ac[" << k << "] = fmaf(wc, t" << k << ", ac[" << k << "]);\n";
+                s << "      t" << P[z].k << " = oeq_fma(" << C(z) << ", xc[" << P[z].i << "], t" << P[z].k << ");\n";
+            for (int k = 0; k < D3; ++k) s << "      ac[" << k << "] = oeq_fma(wc, t" << k << ", ac[" << k << "]);\n";
         }
         s << "    }\n  }\n";
         // ---- fused second-order forward: acc += cy(y) . (w x2 + w2 x) + cy(y2) . (w x)
         if (dbl) {
-            s << "  static OEQ_DEV void fwd3(const float* x, const float* x2, const float4* cy, const float4* cyb, const float* w, const float* w2, float* acc) {\n";
-            for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "]; const float4 b" << q << " = cyb[CY4 + " << q << "];\n";
+            s << "  static OEQ_DEV void fwd3(const T* x, const T* x2, const T4* cy, const T4* cyb, const T* w, const T* w2, T* acc) {\n";
+            for (int q = 0; q < nq; ++q) s << "    const T4 c" << q << " = cy[CY4 + " << q << "]; const T4 b" << q << " = cyb[CY4 + " << q << "];\n";
             s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-            s << "      const float* xc = x + ch * D1; const float* yc = x2 + ch * D1; float* ac = acc + ch * FAST_GPC; const float wc = w[ch]; const float vc = w2[ch];\n";
+            s << "      const T* xc = x + ch * D1; const T* yc = x2 + ch * D1; T* ac = acc + ch * FAST_GPC; const T wc = w[ch]; const T vc = w2[ch];\n";
             for (int i = 0; i < D1; ++i)
-                s << "      const float xa" << i << " = fmaf(vc, xc[" << i << "], wc * yc[" << i << "]); const float xb" << i << " = wc * xc[" << i << "];\n";
+                s << "      const T xa" << i << " = oeq_fma(vc, xc[" << i << "], wc * yc[" << i << "]); const T xb" << i << " = wc * xc[" << i << "];\n";
             auto Bc = [&](int z) { std::ostringstream t; t << "b" << (z / 4) << "." << comp[z % 4]; return t.str(); };
             for (int z = 0; z < np; ++z)
-                s << "      ac[" << P[z].k << "] = fmaf(" << C(z) << ", xa" << P[z].i << ", fmaf(" << Bc(z) << ", xb" << P[z].i << ", ac[" << P[z].k << "]));\n";
+                s << "      ac[" << P[z].k << "] = oeq_fma(" << C(z) << ", xa" << P[z].i << ", oeq_fma(" << Bc(z) << ", xb" << P[z].i << ", ac[" << P[z].k << "]));\n";
             s << "    }\n  }\n";
         }
         // ---- backward
         const bool scale_g = D3 <= D1;
         const int nqv = scale_g ? D3 : D1;
-        s << "  static OEQ_DEV void bwd(const float* x, const float* g, const float4* cy, const float* w, const float* wdx, float* dx, float* dy, float* dw) {\n";
-        for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "];\n";
-        s << "    float qv[FAST_CH][" << nqv << "];\n";
+        s << "  static OEQ_DEV void bwd(const T* x, const T* g, const T4* cy, const T* w, const T* wdx, T* dx, T* dy, T* dw) {\n";
+        for (int q = 0; q < nq; ++q) s << "    const T4 c" << q << " = cy[CY4 + " << q << "];\n";
+        s << "    T qv[FAST_CH][" << nqv << "];\n";
         s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-        s << "      const float* xc = x + ch * D1; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * D1; const float wc = w[ch]; const float wx = wdx[ch];\n";
-        for (int i = 0; i < D1; ++i) s << "      float s" << i << " = 0.f;\n";
+        s << "      const T* xc = x + ch * D1; const T* gc = g + ch * FAST_GPC; T* dxc = dx + ch * D1; const T wc = w[ch]; const T wx = wdx[ch];\n";
+        for (int i = 0; i < D1; ++i) s << "      T s" << i << " = T(0);\n";
         for (int z = 0; z < np; ++z)
-            s << "      s" << P[z].i << " = fmaf(" << C(z) << ", gc[" << P[z].k << "], s" << P[z].i << ");\n";
-        s << "      float dwv = 0.f;\n";
+            s << "      s" << P[z].i << " = oeq_fma(" << C(z) << ", gc[" << P[z].k << "], s" << P[z].i << ");\n";
+        s << "      T dwv = T(0);\n";
         for (int i = 0; i < D1; ++i) {
-            s << "      dwv = fmaf(xc[" << i << "], s" << i << ", dwv);\n";
-            s << "      dxc[" << i << "] = fmaf(wx, s" << i << ", dxc[" << i << "]);\n";
+            s << "      dwv = oeq_fma(xc[" << i << "], s" << i << ", dwv);\n";
+            s << "      dxc[" << i << "] = oeq_fma(wx, s" << i << ", dxc[" << i << "]);\n";
         }
         s << "      dw[ch] = dwv;\n";
         for (int t = 0; t < nqv; ++t) s << "      qv[ch][" << t << "] = wc * " << (scale_g ? "gc" : "xc") << "[" << t << "];\n";
@@ -416,12 +427,12 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
         std::stable_sort(byik.begin(), byik.end(), [](const Nz& a, const Nz& b) { return a.i != b.i ? a.i < b.i : a.k < b.k; });
         for (size_t z = 0; z < byik.size();) {
             size_t m = z;
-            s << "    { float pr = 0.f;\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = fmaf(";
+            s << "    { T pr = T(0);\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = oeq_fma(";
             if (scale_g) s << "x[ch * D1 + " << byik[z].i << "], qv[ch][" << byik[z].k << "]";
             else s << "qv[ch][" << byik[z].i << "], g[ch * FAST_GPC + " << byik[z].k << "]";
             s << ", pr);\n     ";
             while (m < byik.size() && byik[m].i == byik[z].i && byik[m].k == byik[z].k) {
-                s << " dy[" << byik[m].j << "] = fmaf(" << hexf(byik[m].c) << "f, pr, dy[" << byik[m].j << "]);";
+                s << " dy[" << byik[m].j << "] = oeq_fma(T(" << hexf(byik[m].c) << "), pr, dy[" << byik[m].j << "]);";
                 ++m;
             }
             s << " }\n";
@@ -431,29 +442,29 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
         // ---- fused second-order backward: s = cy(y).g and t = cy(y2).g;  dx += w2 s + w t;  dW = x2.s + x.t;
         //      dy[j] += C (w x2 + w2 x)[i] g[k]
         if (dbl) {
-            s << "  static OEQ_DEV void bwd3(const float* x, const float* x2, const float* g, const float4* cy, const float4* cyb, const float* w, const float* w2, float* dx, float* dy, float* dw) {\n";
-            for (int q = 0; q < nq; ++q) s << "    const float4 c" << q << " = cy[CY4 + " << q << "]; const float4 b" << q << " = cyb[CY4 + " << q << "];\n";
+            s << "  static OEQ_DEV void bwd3(const T* x, const T* x2, const T* g, const T4* cy, const T4* cyb, const T* w, const T* w2, T* dx, T* dy, T* dw) {\n";
+            for (int q = 0; q < nq; ++q) s << "    const T4 c" << q << " = cy[CY4 + " << q << "]; const T4 b" << q << " = cyb[CY4 + " << q << "];\n";
             auto Bc = [&](int z) { std::ostringstream t; t << "b" << (z / 4) << "." << comp[z % 4]; return t.str(); };
-            s << "    float qv[FAST_CH][" << D1 << "];\n";
+            s << "    T qv[FAST_CH][" << D1 << "];\n";
             s << "#pragma unroll\n    for (int ch = 0; ch < FAST_CH; ++ch) {\n";
-            s << "      const float* xc = x + ch * D1; const float* yc = x2 + ch * D1; const float* gc = g + ch * FAST_GPC; float* dxc = dx + ch * D1; const float wc = w[ch]; const float vc = w2[ch];\n";
-            for (int i = 0; i < D1; ++i) s << "      float s" << i << " = 0.f, t" << i << " = 0.f;\n";
+            s << "      const T* xc = x + ch * D1; const T* yc = x2 + ch * D1; const T* gc = g + ch * FAST_GPC; T* dxc = dx + ch * D1; const T wc = w[ch]; const T vc = w2[ch];\n";
+            for (int i = 0; i < D1; ++i) s << "      T s" << i << " = T(0), t" << i << " = T(0);\n";
             for (int z = 0; z < np; ++z)
-                s << "      s" << P[z].i << " = fmaf(" << C(z) << ", gc[" << P[z].k << "], s" << P[z].i << "); t" << P[z].i << " = fmaf("
+                s << "      s" << P[z].i << " = oeq_fma(" << C(z) << ", gc[" << P[z].k << "], s" << P[z].i << "); t" << P[z].i << " = oeq_fma("
                   << Bc(z) << ", gc[" << P[z].k << "], t" << P[z].i << ");\n";
-            s << "      float dwv = 0.f;\n";
+            s << "      T dwv = T(0);\n";
             for (int i = 0; i < D1; ++i) {
-                s << "      dwv = fmaf(yc[" << i << "], s" << i << ", fmaf(xc[" << i << "], t" << i << ", dwv));\n";
-                s << "      dxc[" << i << "] = fmaf(vc, s" << i << ", fmaf(wc, t" << i << ", dxc[" << i << "]));\n";
-                s << "      qv[ch][" << i << "] = fmaf(vc, xc[" << i << "], wc * yc[" << i << "]);\n";
+                s << "      dwv = oeq_fma(yc[" << i << "], s" << i << ", oeq_fma(xc[" << i << "], t" << i << ", dwv));\n";
+                s << "      dxc[" << i << "] = oeq_fma(vc, s" << i << ", oeq_fma(wc, t" << i << ", dxc[" << i << "]));\n";
+                s << "      qv[ch][" << i << "] = oeq_fma(vc, xc[" << i << "], wc * yc[" << i << "]);\n";
             }
             s << "      dw[ch] = dwv;\n    }\n";
             for (size_t z = 0; z < byik.size();) {
                 size_t m = z;
-                s << "    { float pr = 0.f;\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = fmaf(qv[ch][" << byik[z].i
+                s << "    { T pr = T(0);\n#pragma unroll\n      for (int ch = 0; ch < FAST_CH; ++ch) pr = oeq_fma(qv[ch][" << byik[z].i
                   << "], g[ch * FAST_GPC + " << byik[z].k << "], pr);\n     ";
                 while (m < byik.size() && byik[m].i == byik[z].i && byik[m].k == byik[z].k) {
-                    s << " dy[" << byik[m].j << "] = fmaf(" << hexf(byik[m].c) << "f, pr, dy[" << byik[m].j << "]);";
+                    s << " dy[" << byik[m].j << "] = oeq_fma(T(" << hexf(byik[m].c) << "), pr, dy[" << byik[m].j << "]);";
                     ++m;
                 }
                 s << " }\n";
@@ -612,7 +623,7 @@ std::string family_source(const Desc& d, const std::string& header, int fam, boo
         const int V = family_streams(d, fam, allow_streams);
         const int stages = V > 1 ? d.fast_SV : dbl ? d.fast_S4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
         const size_t smem = V > 1 ? d.fast_smemV : dbl ? d.fast_smem4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : 1, dbl, stages, smem, V);
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : d.fast_bwd_ng, dbl, stages, smem, V);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(fwd3 ? fam - FAM_FAST_FWD3_TP : dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
@@ -1036,7 +1047,7 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
     const long long work = p.E > 0 ? p.E : 1;
     if (grid > work) grid = work;
     void* args[] = {&p};
-    const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)d.fast_U;
+    const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)(d.fast_bwd_ng * d.fast_U);
     const int producers = fast_producers(dbl ? d.fast_S4 : (kernel == 2 ? d.fast_S3 : d.fast_S));
     return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
