@@ -20,9 +20,12 @@
 #pragma once
 #if OEQ_TC
 
+// TC_MODE (with the tables): 0 forward, 1 gradient of x, 2 gradient of y, 3 gradient of the weights.
 struct TcParams {
     const float* x; const float* y; const float* W; float* z;
+    const float* g;     // mode 2 only: the output cotangent (x is then the first input, z the gradient of y)
     long long batch;
+    int accum;          // add to what z holds instead of overwriting it
     int* status;
 };
 
@@ -89,7 +92,10 @@ OEQ_DEV void tc_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta
 // A / B chunk geometry: 32 K-columns = 8 core matrices of 128 bytes per 8-row group
 constexpr unsigned TC_LBO = 128, TC_SBO = 1024;
 constexpr int TC_A_FLOATS = 128 * 32, TC_B_FLOATS = 32 * 32;
-constexpr int TC_XSTRIDE = 32 * TC_MAXD1 + 4;   // padded row of the staged input block (conflict-free column reads)
+// padded row of the staged input block: conflict-free for the column reads of the Clebsch-Gordan stage (modes 0, 1) or
+// for one thread per row (mode 2)
+constexpr int TC_XSTRIDE = 32 * TC_MAXD1 + (TC_MODE == 2 ? 1 : 4);
+constexpr int TC_DYS = L2_DIM | 1;              // mode 2: row of a thread's partial sums of dy
 constexpr int TC_YSTRIDE = (L2_DIM + 3) & ~3;
 
 struct __align__(128) TcShared {
@@ -97,6 +103,7 @@ struct __align__(128) TcShared {
     float b[2][2][TC_B_FLOATS];
     float xs[128 * TC_XSTRIDE];       // input block a(p) of the 128 items of the tile
     float ys[128 * TC_YSTRIDE];       // harmonics of the 128 items
+    float dys[TC_MODE == 2 ? 256 * TC_DYS : 4];   // mode 2: per-thread partial sums of dy (two threads per item)
     unsigned long long mma_done[2];   // a buffer may be rewritten
     unsigned long long acc_done[2];   // accumulators of an output block are complete
     unsigned tmem_base;
@@ -111,7 +118,7 @@ OEQ_DEV int tc_elem(int row, int kcol) { return (row >> 3) * (TC_SBO / 4) + (kco
 // floats of the z row.  All components are pulled out of tensor memory first (column 32 k + c holds channel c of
 // component k), then written as 16-byte stores, so every 32-byte sector of z is written whole.
 template <int D3>
-OEQ_DEV void tc_epilogue(unsigned tbase, float* zdst, bool live) {
+OEQ_DEV void tc_epilogue(unsigned tbase, float* zdst, bool live, bool accum) {
     float v[16 * D3];   // v[c * D3 + k]
 #pragma unroll
     for (int k = 0; k < D3; ++k) {
@@ -127,14 +134,25 @@ OEQ_DEV void tc_epilogue(unsigned tbase, float* zdst, bool live) {
     }
     if (live) {
         float4* dst = reinterpret_cast<float4*>(zdst);   // 64 * D3 bytes from a 16-byte boundary
+        if (accum) {
+#pragma unroll
+            for (int q = 0; q < 4 * D3; ++q) {
+                const float4 old = dst[q];
+                v[4 * q] += old.x; v[4 * q + 1] += old.y; v[4 * q + 2] += old.z; v[4 * q + 3] += old.w;
+            }
+        }
 #pragma unroll
         for (int q = 0; q < 4 * D3; ++q) __stcs(dst + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
     }
 }
 
+#if TC_MODE != 3
 // The loops over paths, output components and Clebsch-Gordan terms are run-time loops over the TC_* tables of the
 // problem header (not unrolled): the whole kernel is a few KB of code and stays in the instruction cache.
-extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const TcParams p) {
+// The same kernel computes the gradient of the first input when it is compiled with the transposed tables (TC_WT = 1:
+// x is then the output cotangent, z the gradient, and the weight block is applied transposed); TC_KERNEL_NAME,
+// TC_IN_DIM and TC_OUT_DIM (row lengths of x and z) come with the tables.
+extern "C" __global__ void __launch_bounds__(256, 1) TC_KERNEL_NAME(const TcParams p) {
     extern __shared__ __align__(128) unsigned char tc_smem_raw[];
     TcShared& sh = *reinterpret_cast<TcShared*>(tc_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -166,9 +184,13 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
     for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
         const long long item0 = tile * 128;
         __syncthreads();   // previous tile's readers of xs / ys are done
-        for (int r = warp; r < 128; r += 8)          // one warp per row: no index division
-            for (int j = lane; j < L2_DIM; j += 32)
-                sh.ys[r * TC_YSTRIDE + j] = (item0 + r < p.batch) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
+        if (TC_MODE != 2) {
+            for (int r = warp; r < 128; r += 8)          // one warp per row: no index division
+                for (int j = lane; j < L2_DIM; j += 32)
+                    sh.ys[r * TC_YSTRIDE + j] = (item0 + r < p.batch) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
+        } else {
+            for (int j = 0; j < TC_DYS; ++j) sh.dys[tid * TC_DYS + j] = 0.f;   // read and written by this thread only
+        }
         for (int q = 0; q < NINS && !dead; ++q) {
             const int d1 = TC_D1[q], d3 = TC_D3[q], xoff = TC_XOFF[q], zoff = TC_ZOFF[q], woff = TC_WOFF[q];
             const int first = TC_FIRST[q], last = TC_LAST[q];
@@ -182,7 +204,7 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
 #pragma unroll
                 for (int rr = 0; rr < 16; ++rr) {
                     const long long b = item0 + warp + 8 * rr;
-                    v[rr] = (b < p.batch) ? __ldg(p.x + b * L1_DIM + xoff + c) : 0.f;
+                    v[rr] = (b < p.batch) ? __ldg(p.x + b * TC_IN_DIM + xoff + c) : 0.f;
                 }
 #pragma unroll
                 for (int rr = 0; rr < 16; ++rr) sh.xs[(warp + 8 * rr) * TC_XSTRIDE + c] = v[rr];
@@ -199,31 +221,45 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
                 float acc0[8], acc1[8];
 #pragma unroll
                 for (int uu = 0; uu < 8; ++uu) { acc0[uu] = 0.f; acc1[uu] = 0.f; }
-                const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
-                for (int t = t0; t < t1; ++t) {
-                    const int ti = TC_TI[t], tj = TC_TJ[t];
-                    const float c = TC_TC[t];
-                    const float cy0 = c * yrow0[tj], cy1 = c * yrow1[tj];
-                    const float* px0 = xrow0 + ti;
-                    const float* px1 = xrow1 + ti;
+                if (TC_MODE != 2) {
+                    const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
+                    for (int t = t0; t < t1; ++t) {
+                        const int ti = TC_TI[t], tj = TC_TJ[t];
+                        const float c = TC_TC[t];
+                        const float cy0 = c * yrow0[tj], cy1 = c * yrow1[tj];
+                        const float* px0 = xrow0 + ti;
+                        const float* px1 = xrow1 + ti;
+#pragma unroll
+                        for (int uu = 0; uu < 8; ++uu) {
+                            acc0[uu] = fmaf(cy0, px0[uu * ustride], acc0[uu]);
+                            acc1[uu] = fmaf(cy1, px1[uu * ustride], acc1[uu]);
+                        }
+                    }
+                } else {
+                    // mode 2: the A operand is component k of the cotangent's block itself, A[b][w] = g[b, o][w, k]
+                    const long long b0 = item0 + brow, b1 = b0 + 8;
+                    const float* g0 = p.g + (b0 < p.batch ? b0 : 0) * L3_DIM + zoff + ucol * d3 + k;
+                    const float* g1 = p.g + (b1 < p.batch ? b1 : 0) * L3_DIM + zoff + ucol * d3 + k;
 #pragma unroll
                     for (int uu = 0; uu < 8; ++uu) {
-                        acc0[uu] = fmaf(cy0, px0[uu * ustride], acc0[uu]);
-                        acc1[uu] = fmaf(cy1, px1[uu * ustride], acc1[uu]);
+                        acc0[uu] = (b0 < p.batch) ? __ldg(g0 + uu * 4 * d3) : 0.f;
+                        acc1[uu] = (b1 < p.batch) ? __ldg(g1 + uu * 4 * d3) : 0.f;
                     }
                 }
                 // the A buffer was last read by the MMAs of step - 2 (a commit covers every MMA issued before it)
                 if (step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 31)) dead = true;
                 if (!dead) {
-                    if (k == 0) {   // weight block of the path: B[w, u] = W_p[u, w]; its buffer was last read two paths ago
+                    if (k == 0) {   // weight block of the path: B[n, kk] = W_p[kk, n] (forward: n = w, kk = u) or
+                                    // W_p[n, kk] (gradient: n = u, kk = w); its buffer was last read two paths ago
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
                             const int e = tid + 256 * r;          // e = u * 32 + w
                             const int u = e >> 5, w = e & 31;
                             const float v = __ldg(p.W + woff + e);
                             const float hi = tc_tf32(v);
-                            sh.b[npath & 1u][0][tc_elem(w, u)] = hi;
-                            sh.b[npath & 1u][1][tc_elem(w, u)] = tc_tf32(v - hi);
+                            const int off = TC_WT ? tc_elem(u, w) : tc_elem(w, u);
+                            sh.b[npath & 1u][0][off] = hi;
+                            sh.b[npath & 1u][1][off] = tc_tf32(v - hi);
                         }
                     }
 #pragma unroll
@@ -267,12 +303,36 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
                     const int qd = warp & 3, half = warp >> 2;          // TMEM lane quarter, column half
                     const long long b = item0 + qd * 32 + lane;
                     const unsigned tbase = tmem + ((unsigned)(qd * 32) << 16) + (nblock & 1u) * 256u + 16u * half;
-                    float* zdst = p.z + (b < p.batch ? b : 0) * L3_DIM + zoff + 16 * half * d3;
-                    const bool live = b < p.batch;
-                    if (d3 == 1) tc_epilogue<1>(tbase, zdst, live);
-                    else if (d3 == 3) tc_epilogue<3>(tbase, zdst, live);
-                    else if (d3 == 5) tc_epilogue<5>(tbase, zdst, live);
-                    else tc_epilogue<7>(tbase, zdst, live);
+                    if (TC_MODE != 2) {
+                        float* zdst = p.z + (b < p.batch ? b : 0) * TC_OUT_DIM + zoff + 16 * half * d3;
+                        const bool live = b < p.batch;
+                        if (d3 == 1) tc_epilogue<1>(tbase, zdst, live, p.accum != 0);
+                        else if (d3 == 3) tc_epilogue<3>(tbase, zdst, live, p.accum != 0);
+                        else if (d3 == 5) tc_epilogue<5>(tbase, zdst, live, p.accum != 0);
+                        else tc_epilogue<7>(tbase, zdst, live, p.accum != 0);
+                    } else {
+                        // mode 2: the accumulators are g'[b][u, k] = sum_w W_p[u, w] g[b, o][w, k]; this thread folds its item's
+                        // 16 channels into dy[b][j] += c * sum_u x[b][u, i] g'[b][u, k], term by term
+                        float* dyp = sh.dys + tid * TC_DYS;
+                        const float* xb = sh.xs + (qd * 32 + lane) * TC_XSTRIDE + 16 * half * d1;
+                        for (int k = 0; k < d3; ++k) {
+                            unsigned r[16];
+                            asm volatile(
+                                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                                : "r"(tbase + 32u * (unsigned)k) : "memory");
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
+                            for (int t = t0; t < t1; ++t) {
+                                const float* px = xb + TC_TI[t];
+                                float dot = 0.f;
+#pragma unroll
+                                for (int u = 0; u < 16; ++u) dot = fmaf(px[u * d1], __uint_as_float(r[u]), dot);
+                                dyp[TC_TJ[t]] = fmaf(TC_TC[t], dot, dyp[TC_TJ[t]]);
+                            }
+                        }
+                    }
                     tc_fence_before();
                 }
                 ++nblock;
@@ -281,10 +341,197 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_forward(const Tc
             }
             ++npath;
         }
+        if (TC_MODE == 2) {
+            // dy of the tile: threads t and t + 128 hold the two channel halves of item t (warps 0-3 / 4-7 above)
+            __syncthreads();
+            const long long b = item0 + tid;
+            if (tid < 128 && b < p.batch && !dead)
+                for (int j = 0; j < L2_DIM; ++j) {
+                    const float v = sh.dys[tid * TC_DYS + j] + sh.dys[(tid + 128) * TC_DYS + j];
+                    p.z[b * L2_DIM + j] = p.accum ? p.z[b * L2_DIM + j] + v : v;
+                }
+        }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
+#endif  // TC_MODE != 3
+
+#if TC_MODE == 3
+// ---- gradient of the shared weights ---------------------------------------------------------------------------
+//   dW_p[u, w] = sum_b sum_k T_p[b][u, k] * g[b, o][w, k],     T_p as in the forward (Clebsch-Gordan stage, CUDA cores)
+// A GEMM whose reduction runs over the batch.  Up to four paths into the same output block o are stacked on M (they share
+// the B operand): per step (group of paths, component k, tile of 128 items)
+//   D[(slot, u), w] += A[(slot, u), b] * B[w, b],   A = T (128 x 128), B = component k of the cotangent block (32 x 128),
+// both K-major with the items on K (16 tcgen05.mma of K = 8, three split terms each).  The accumulators of every group
+// stay in tensor memory (32 columns per group) over all tiles of the CTA; at the end the CTA stores them as one row of
+// a partials matrix that a second kernel sums in row order (bitwise reproducible).
+// Thread roles (256 threads): warp w computes T for slot w % 4 and the 64 items of half w / 4.  A lane covers channels
+// lane / 4 + 8 uu (uu < 4) and items lane % 4 + 4 bb (bb < 16): one load or store of the warp then touches 8 channels of
+// 4 items, which is 4 short runs in global memory and 32 different banks of the canonical layout.
+struct TcDwParams {
+    const float* x; const float* y; const float* g; float* part;
+    long long batch;
+    int* status;
+};
+constexpr unsigned TCW_LBO = 128, TCW_SBO = 4096;   // 128 K-columns: 32 core matrices of 128 bytes per 8-row group
+constexpr int TCW_A_FLOATS = 128 * 128, TCW_B_FLOATS = 32 * 128;
+constexpr int TCW_YS = L2_DIM | 1;
+struct __align__(128) TcDwShared {
+    float a[2][TCW_A_FLOATS];         // [hi, lo]
+    float b[2][TCW_B_FLOATS];
+    float ys[128 * TCW_YS];           // harmonics of the tile's items
+    unsigned long long mma_done;
+    unsigned tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(TcDwShared) > 116 * 1024 && sizeof(TcDwShared) <= 232448, "one CTA per SM is assumed (it owns all of TMEM)");
+static_assert(TCW_NGRP * 32 <= 512, "one 32-column accumulator per group of paths");
+OEQ_DEV int tcw_elem(int row, int kcol) { return (row >> 3) * (TCW_SBO / 4) + (kcol >> 2) * (TCW_LBO / 4) + (row & 7) * 4 + (kcol & 3); }
+
+extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(const TcDwParams p) {
+    extern __shared__ __align__(128) unsigned char tc_smem_raw[];
+    TcDwShared& sh = *reinterpret_cast<TcDwShared*>(tc_smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    volatile int* abortf = &sh.abort_flag;
+    if (tid == 0) {
+        tc_mbar_init(&sh.mma_done, 1);
+        sh.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(tc_smem_u32(&sh.tmem_base)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = sh.tmem_base;
+
+    const int slot = warp & 3, ihalf = warp >> 2, r8 = lane >> 2, b4 = lane & 3;
+    unsigned nstep = 0;    // steps issued so far
+    const long long ntiles = (p.batch + 127) / 128;
+    bool dead = false;
+
+    for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
+        const long long item0 = tile * 128;
+        __syncthreads();   // the previous tile's readers of ys are done
+        for (int r = warp; r < 128; r += 8)
+            for (int j = lane; j < L2_DIM; j += 32)
+                sh.ys[r * TCW_YS + j] = (item0 + r < p.batch) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
+        __syncthreads();
+        // rows of this thread's items; items past the end of the batch read row 0 and are multiplied by y = 0
+        const int ib = 64 * ihalf + b4;                  // first of this thread's 16 items of the A operand
+        const long long nlive = p.batch - item0;         // items of the tile that exist
+        const bool first_tile = tile == blockIdx.x;
+        for (int grp = 0; grp < TCW_NGRP && !dead; ++grp) {
+            const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp];
+            for (int k = 0; k < d3 && !dead; ++k) {
+                // Clebsch-Gordan stage: acc[uu][bb] = T[item ib + 4 bb][channel r8 + 8 uu] of this warp's slot
+                float acc[4][16];
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu)
+#pragma unroll
+                    for (int bb = 0; bb < 16; ++bb) acc[uu][bb] = 0.f;
+                {
+                    const int q = grp * 4 + slot;
+                    const int d1 = TCW_D1[q];
+                    const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
+                    for (int t = t0; t < t1; ++t) {
+                        const float c = TCW_TC[t];
+                        const int tj = TCW_TJ[t];
+                        const float* px = p.x + TCW_XOFF[q] + r8 * d1 + TCW_TI[t];
+#pragma unroll
+                        for (int bb = 0; bb < 16; ++bb) {
+                            const int bi = ib + 4 * bb;
+                            const float cy = c * sh.ys[bi * TCW_YS + tj];
+                            const float* pb = px + (bi < nlive ? item0 + bi : 0) * L1_DIM;
+#pragma unroll
+                            for (int uu = 0; uu < 4; ++uu) acc[uu][bb] = fmaf(cy, __ldg(pb + 8 * uu * d1), acc[uu][bb]);
+                        }
+                    }
+                }
+                // this thread's 16 entries of B: rows w = r8 + 8 ww (ww < 4), items 16 * warp + b4 + 4 bb (bb < 4)
+                float gv[4][4];
+#pragma unroll
+                for (int bb = 0; bb < 4; ++bb) {
+                    const int bi = 16 * warp + b4 + 4 * bb;
+                    const float* pg = p.g + (bi < nlive ? item0 + bi : 0) * L3_DIM + zoff + r8 * d3 + k;
+#pragma unroll
+                    for (int ww = 0; ww < 4; ++ww) gv[ww][bb] = (bi < nlive) ? __ldg(pg + 8 * ww * d3) : 0.f;
+                }
+                // the operand buffers were last read by the MMAs of the previous step
+                if (nstep >= 1 && !tc_mbar_wait(&sh.mma_done, (nstep - 1) & 1u, abortf, p.status, 33)) dead = true;
+                if (!dead) {
+#pragma unroll
+                    for (int uu = 0; uu < 4; ++uu)
+#pragma unroll
+                        for (int bb = 0; bb < 16; ++bb) {
+                            const int off = tcw_elem(slot * 32 + r8 + 8 * uu, ib + 4 * bb);
+                            const float v = acc[uu][bb], hi = tc_tf32(v);
+                            sh.a[0][off] = hi;
+                            sh.a[1][off] = tc_tf32(v - hi);
+                        }
+#pragma unroll
+                    for (int ww = 0; ww < 4; ++ww)
+#pragma unroll
+                        for (int bb = 0; bb < 4; ++bb) {
+                            const int off = tcw_elem(r8 + 8 * ww, 16 * warp + b4 + 4 * bb);
+                            const float hi = tc_tf32(gv[ww][bb]);
+                            sh.b[0][off] = hi;
+                            sh.b[1][off] = tc_tf32(gv[ww][bb] - hi);
+                        }
+                    tc_fence_async_smem();
+                }
+                tc_fence_before();
+                __syncthreads();
+                tc_fence_after();
+                if (sh.abort_flag) dead = true;
+                if (!dead && tid == 0) {
+                    const unsigned dcol = tmem + 32u * (unsigned)grp;
+#pragma unroll 4
+                    for (int ks = 0; ks < 16; ++ks) {
+                        const unsigned long long ah = tc_desc(&sh.a[0][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
+                        const unsigned long long al = tc_desc(&sh.a[1][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
+                        const unsigned long long bh = tc_desc(&sh.b[0][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
+                        const unsigned long long blo = tc_desc(&sh.b[1][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
+                        tc_mma(dcol, ah, bh, (first_tile && k == 0 && ks == 0) ? 0u : 1u);
+                        tc_mma(dcol, al, bh, 1u);
+                        tc_mma(dcol, ah, blo, 1u);
+                    }
+                    tc_commit(&sh.mma_done);
+                }
+                ++nstep;
+            }
+        }
+    }
+    // the CTA's sums: row blockIdx.x of the partials matrix.  TMEM lane = (slot, u), column = 32 * group + w.
+    if (!dead && nstep >= 1 && !tc_mbar_wait(&sh.mma_done, (nstep - 1) & 1u, abortf, p.status, 34)) dead = true;
+    if (!dead && nstep >= 1) {
+        tc_fence_after();
+        const int half = warp >> 2;
+        float* prow = p.part + (long long)blockIdx.x * WN;
+        for (int grp = 0; grp < TCW_NGRP; ++grp) {
+            if (slot >= TCW_NS[grp]) continue;   // uniform in the warp
+            unsigned r[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)grp + 16u * half) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float4* dst = reinterpret_cast<float4*>(prow + TCW_WOFF[grp * 4 + slot] + lane * 32 + 16 * half);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                dst[c] = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),
+                                     __uint_as_float(r[4 * c + 3]));
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+#endif  // TC_MODE == 3
 
 #endif  // OEQ_TC

@@ -44,6 +44,7 @@ std::atomic<long long> g_launches{0};
 bool g_log = false;
 bool g_force_generic = false;
 bool g_no_tc = false;          // tuning aid: keep 'uvw' forward on the general kernel
+int g_tc_backward = 7;         // 'uvw' backward outputs taken from the tensor-core kernels: 1 dx, 2 dy, 4 dW (bit mask)
 bool g_single_group = false;   // tuning aid: one thread group per edge on the channel-parallel path
 bool g_single_producer = false;   // tuning aid: one producer warp per CTA in the forward kernels too
 int g_validate = 1;            // index checks of convolution calls: 0 never, 1 first call per edge list, 2 every call
@@ -103,6 +104,7 @@ struct Desc {
     int fast_bwd_ng = 1; // thread groups of the backward kernels (2 in the fp64 configuration)
     size_t fast_smem = 0;
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
+    bool tc_bwd = false;     // ... and the tensor-core backward kernels (every input block is read by some path)
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
     int fast_S4 = 0;         // stages of the second-order kernels (their stage carries a second coefficient table)
@@ -238,6 +240,7 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     }
     // Tensor-core path for 'uvw': shared fp32 weights, every in1 / out multiplicity 32, in2 multiplicity 1, l <= 3.
     d.tc = false;
+    d.tc_bwd = false;
     if (d.dtype == 1 && d.layout == 0 && d.uvw && d.shared && !d.L[0].empty()) {
         bool ok = d.dim[1] <= 16;
         for (auto& b : d.L[0]) ok = ok && b.mul == 32 && b.l <= 3;
@@ -245,9 +248,17 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         for (auto& b : d.L[2]) ok = ok && b.mul == 32 && b.l <= 3;
         // every output block must be written by at least one path (the kernel stores only blocks it accumulates)
         std::vector<int> hit(d.L[2].size(), 0);
-        for (auto& I : d.ins) hit[I.o] = 1;
+        for (auto& I : d.ins) hit[I.o] += 1;
         for (int h : hit) ok = ok && h;
         d.tc = ok;
+        // the backward kernels likewise store only the input blocks that some path reads
+        std::vector<int> read(d.L[0].size(), 0);
+        for (auto& I : d.ins) read[I.a] = 1;
+        d.tc_bwd = ok;
+        for (int h : read) d.tc_bwd = d.tc_bwd && h;
+        int groups = 0;   // the weight-gradient kernel keeps one 32-column accumulator per group of four paths into a block
+        for (int h : hit) groups += (h + 3) / 4;
+        d.tc_bwd = d.tc_bwd && groups <= 16;
     }
     return true;
 }
@@ -512,36 +523,50 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
     return s.str();
 }
 
-// Per-path tables for the tensor-core 'uvw' forward (kernels/uvw_tc.cuh): paths ordered by output block, and for each
-// path and output component k the Clebsch-Gordan sum that produces one element of the A operand.
-std::string emit_tc(const Desc& d) {
+// Per-path tables for the tensor-core 'uvw' kernels (kernels/uvw_tc.cuh): paths ordered by the block they
+// accumulate into, and for each path and component of that block the Clebsch-Gordan sum that produces one element of
+// the A operand.
+//   mode 0, forward:   z[b, o][w, k] = sum_p sum_u W_p[u, w] * (sum_{i,j} C[i,j,k] x[b, a][u, i] y[b][j])
+//   mode 1, dx:       dx[b, a][u, i] = sum_p sum_w W_p[u, w] * (sum_{k,j} C[i,j,k] g[b, o][w, k] y[b][j])
+// The second is the first with the roles of the input and output blocks exchanged and the weight block transposed, so
+// the same kernel serves both from two sets of tables.
+std::string emit_tc_dw(const Desc& d);
+std::string emit_tc(const Desc& d, int mode = 0) {
     std::ostringstream s;
     if (!d.tc) { s << "#define OEQ_TC 0\n"; return s.str(); }
+    if (mode == 3) return emit_tc_dw(d);
     s << "#define OEQ_TC 1\n";
+    const bool dx = mode == 1, dy = mode == 2;
+    s << "#define TC_MODE " << mode << "\n";
+    s << "#define TC_WT " << (mode != 0 ? 1 : 0) << "\n";
+    s << "#define TC_KERNEL_NAME " << (dx ? "oeq_uvw_tc_backward_dx" : dy ? "oeq_uvw_tc_backward_dy" : "oeq_uvw_tc_forward") << "\n";
+    s << "constexpr int TC_IN_DIM = " << (dx ? d.dim[2] : d.dim[0]) << ", TC_OUT_DIM = " << (dx ? d.dim[0] : d.dim[2]) << ";\n";
+    // mode 2 (dy) accumulates nowhere across paths: every path is its own group; the paths are ordered by the input
+    // block they stage
+    auto dst = [&](int q) { return dx ? d.ins[q].a : dy ? q : d.ins[q].o; };   // block the path accumulates into
+    auto src = [&](int q) { return dx ? d.ins[q].o : d.ins[q].a; };           // block the path stages
     std::vector<int> order(d.ins.size());
     for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
-    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return d.ins[a].o < d.ins[b].o; });
-    // Inside an output block the order of the paths is free.  Paths that read the same input block are put next to each
-    // other, and a group starts with the input block the previous group ended with where it can: the kernel keeps the
-    // staged input block when the next path reads the same one.
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return dy ? src(a) < src(b) : dst(a) < dst(b); });
+    // Inside a destination block the order of the paths is free.  Paths that read the same block are put next to each
+    // other, and a group starts with the block the previous group ended with where it can: the kernel keeps the
+    // staged block when the next path reads the same one.
     for (size_t g0 = 0; g0 < order.size();) {
         size_t g1 = g0;
-        while (g1 < order.size() && d.ins[order[g1]].o == d.ins[order[g0]].o) ++g1;
-        std::stable_sort(order.begin() + g0, order.begin() + g1, [&](int a, int b) { return d.ins[a].a < d.ins[b].a; });
+        while (g1 < order.size() && dst(order[g1]) == dst(order[g0])) ++g1;
+        std::stable_sort(order.begin() + g0, order.begin() + g1, [&](int a, int b) { return src(a) < src(b); });
         if (g0 > 0) {
-            const int prev = d.ins[order[g0 - 1]].a;
-            std::stable_partition(order.begin() + g0, order.begin() + g1, [&](int q) { return d.ins[q].a == prev; });
+            const int prev = src(order[g0 - 1]);
+            std::stable_partition(order.begin() + g0, order.begin() + g1, [&](int q) { return src(q) == prev; });
         }
-        // end the group with the input block that the next group can start with (the most frequent one is a good guess:
-        // leave the sorted order otherwise)
         g0 = g1;
     }
     std::vector<int> first(d.ins.size(), 0), last(d.ins.size(), 0);
     for (size_t q = 0; q < order.size(); ++q) {
-        if (q == 0 || d.ins[order[q - 1]].o != d.ins[order[q]].o) first[order[q]] = 1;
-        if (q + 1 == order.size() || d.ins[order[q + 1]].o != d.ins[order[q]].o) last[order[q]] = 1;
+        if (q == 0 || dst(order[q - 1]) != dst(order[q])) first[order[q]] = 1;
+        if (q + 1 == order.size() || dst(order[q + 1]) != dst(order[q])) last[order[q]] = 1;
     }
-    // run-time tables, one entry per path in schedule order (paths sorted by output block)
+    // run-time tables, one entry per path in schedule order
     auto ilist = [&](const char* name, const std::vector<long long>& v) {
         s << "__device__ const int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
         for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
@@ -554,14 +579,15 @@ std::string emit_tc(const Desc& d) {
     for (size_t q = 0; q < order.size(); ++q) {
         const Instr& I = d.ins[order[q]];
         const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
-        vd1.push_back(A.d()); vd3.push_back(O.d()); vx.push_back(A.off); vz.push_back(O.off); vw.push_back(I.woff);
+        const Block &S = dx ? O : A, &D = dx ? A : O;   // block read, block accumulated into
+        vd1.push_back(S.d()); vd3.push_back(D.d()); vx.push_back(S.off); vz.push_back(D.off); vw.push_back(I.woff);
         vf.push_back(first[order[q]]); vl.push_back(last[order[q]]);
-        if (A.d() > maxd1) maxd1 = A.d();
+        if (S.d() > maxd1) maxd1 = S.d();
         for (int k = 0; k < 8; ++k) {
             kbeg.push_back((long long)ti.size());
-            if (k < O.d())
+            if (k < D.d())
                 for (auto& z : I.nz)
-                    if (z.k == k) { ti.push_back(z.i); tj.push_back(B.off + z.j); tcf.push_back(z.c); }
+                    if ((dx ? z.i : z.k) == k) { ti.push_back(dx ? z.k : z.i); tj.push_back(B.off + z.j); tcf.push_back(z.c); }
         }
     }
     kbeg.push_back((long long)ti.size());
@@ -569,6 +595,58 @@ std::string emit_tc(const Desc& d) {
     ilist("TC_D1", vd1); ilist("TC_D3", vd3); ilist("TC_XOFF", vx); ilist("TC_ZOFF", vz); ilist("TC_WOFF", vw);
     ilist("TC_FIRST", vf); ilist("TC_LAST", vl); ilist("TC_KBEG", kbeg); ilist("TC_TI", ti); ilist("TC_TJ", tj);
     s << "__device__ const float TC_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
+    for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
+    if (tcf.empty()) s << "0";
+    s << "};\n";
+    return s.str();
+}
+
+// Tables for the tensor-core weight-gradient kernel: the paths of an output block in groups of up to four slots.
+std::string emit_tc_dw(const Desc& d) {
+    std::ostringstream s;
+    s << "#define OEQ_TC 1\n#define TC_MODE 3\n#define TC_WT 0\n#define TC_KERNEL_NAME oeq_uvw_tc_unused\n";
+    s << "constexpr int TC_IN_DIM = " << d.dim[0] << ", TC_OUT_DIM = " << d.dim[2] << ";\n";
+    std::vector<std::vector<int>> groups;
+    for (size_t o = 0; o < d.L[2].size(); ++o) {
+        std::vector<int> cur;
+        for (size_t q = 0; q < d.ins.size(); ++q)
+            if (d.ins[q].o == (int)o) {
+                cur.push_back((int)q);
+                if (cur.size() == 4) { groups.push_back(cur); cur.clear(); }
+            }
+        if (!cur.empty()) groups.push_back(cur);
+    }
+    auto ilist = [&](const char* name, const std::vector<long long>& v) {
+        s << "__device__ const int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
+        for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
+        if (v.empty()) s << "0";
+        s << "};\n";
+    };
+    std::vector<long long> ns, gd3, gz, sd1, sx, sw, kbeg, ti, tj;
+    std::vector<double> tcf;
+    int maxd1 = 1;
+    for (auto& grp : groups) {
+        const Block& O = d.L[2][d.ins[grp[0]].o];
+        ns.push_back((long long)grp.size()); gd3.push_back(O.d()); gz.push_back(O.off);
+        for (int slot = 0; slot < 4; ++slot) {
+            const bool used = slot < (int)grp.size();
+            const Instr* I = used ? &d.ins[grp[slot]] : nullptr;
+            sd1.push_back(used ? d.L[0][I->a].d() : 1); sx.push_back(used ? d.L[0][I->a].off : 0); sw.push_back(used ? I->woff : 0);
+            if (used) maxd1 = std::max(maxd1, d.L[0][I->a].d());
+            for (int k = 0; k < 8; ++k) {
+                kbeg.push_back((long long)ti.size());
+                if (used && k < O.d())
+                    for (auto& z : I->nz)
+                        if (z.k == k) { ti.push_back(z.i); tj.push_back(d.L[1][I->b].off + z.j); tcf.push_back(z.c); }
+            }
+        }
+    }
+    kbeg.push_back((long long)ti.size());
+    s << "constexpr int TC_MAXD1 = " << maxd1 << ";\n";
+    s << "constexpr int TCW_NGRP = " << groups.size() << ";\n";
+    ilist("TCW_NS", ns); ilist("TCW_D3", gd3); ilist("TCW_ZOFF", gz); ilist("TCW_D1", sd1); ilist("TCW_XOFF", sx);
+    ilist("TCW_WOFF", sw); ilist("TCW_KBEG", kbeg); ilist("TCW_TI", ti); ilist("TCW_TJ", tj);
+    s << "__device__ const float TCW_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
     for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
     if (tcf.empty()) s << "0";
     s << "};\n";
@@ -583,11 +661,13 @@ enum Family {
     FAM_FAST_BWD2_TP, FAM_FAST_BWD2_DET, FAM_FAST_BWD2_ATOMIC,   // second-order variants of the backward kernels
     FAM_UVW_TC,                                                  // tcgen05 'uvw' forward
     FAM_FAST_FWD3_TP, FAM_FAST_FWD3_DET,                         // fused second-order forward (three terms in one pass)
+    FAM_UVW_TC_DX, FAM_UVW_TC_DY, FAM_UVW_TC_DW,                 // tcgen05 'uvw' backward: gradients of x, y and the weights
     FAM_COUNT
 };
 const char* const kFamilyNames[FAM_COUNT] = {"generic", "fast_fwd_tp", "fast_fwd_det", "fast_fwd_atomic", "fast_bwd_tp",
                                              "fast_bwd_det", "fast_bwd_atomic", "fast_scatter", "fast_bwd2_tp",
-                                             "fast_bwd2_det", "fast_bwd2_atomic", "uvw_tc", "fast_fwd3_tp", "fast_fwd3_det"};
+                                             "fast_bwd2_det", "fast_bwd2_atomic", "uvw_tc", "fast_fwd3_tp", "fast_fwd3_det",
+                                             "uvw_tc_dx", "uvw_tc_dy", "uvw_tc_dw"};
 const char* family_name(int f) { return (f >= 0 && f < FAM_COUNT) ? kFamilyNames[f] : "?"; }
 int family_from_name(const std::string& n) {
     for (int f = 0; f < FAM_COUNT; ++f)
@@ -609,8 +689,8 @@ std::string family_source(const Desc& d, const std::string& header, int fam, boo
     if (fam == FAM_GENERIC) {
         src += K_COMMON;
         src += K_GENERIC;
-    } else if (fam == FAM_UVW_TC) {
-        src += emit_tc(d);
+    } else if (fam == FAM_UVW_TC || (fam >= FAM_UVW_TC_DX && fam <= FAM_UVW_TC_DW)) {
+        src += emit_tc(d, fam == FAM_UVW_TC ? 0 : fam - FAM_UVW_TC_DX + 1);
         src += K_COMMON;
         src += K_UVW_TC;
     } else {
@@ -869,6 +949,8 @@ int generic_forward(Entry* e, FwdParams p, cudaStream_t st) {
     return launch(k, generic_grid(p.n_units), 128, 0, args, st);
 }
 
+int keep_pool_memory();
+
 int generic_backward(Entry* e, BwdParams p, cudaStream_t st) {
     if (p.n_units <= 0) return OEQB_OK;
     Program* prog;
@@ -888,20 +970,7 @@ int generic_backward(Entry* e, BwdParams p, cudaStream_t st) {
         int chunk = 32;
         long long chunks = (p.n_edges + chunk - 1) / chunk;
         void* part = nullptr;
-        {
-            // keep freed scratch in the device's stream-ordered pool: by default the pool gives memory back to the
-            // driver at every synchronisation and the next call pays for mapping it again
-            static bool pool_kept[64] = {false};
-            int dev = 0;
-            CUDA_TRY(cudaGetDevice(&dev));
-            if (dev >= 0 && dev < 64 && !pool_kept[dev]) {
-                cudaMemPool_t pool;
-                CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, dev));
-                uint64_t keep = UINT64_MAX;
-                CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-                pool_kept[dev] = true;
-            }
-        }
+        if ((rc = keep_pool_memory())) return rc;
         CUDA_TRY(cudaMallocAsync(&part, (size_t)chunks * d.wn * d.elt(), st));
         p.dW_part = part;
         void* args[] = {&p, &chunk};
@@ -1109,28 +1178,103 @@ int noalloc_scratch(void** out) {
 // ------------------------------------------------------------------------------------ tensor-core 'uvw'
 struct TcParams {
     const void* x; const void* y; const void* W; void* z;
+    const void* g;
+    long long batch;
+    int accum;
+    int* status;
+};
+struct TcDwParams {
+    const void* x; const void* y; const void* g; void* part;
     long long batch;
     int* status;
 };
-// sizeof(TcShared) in kernels/uvw_tc.cuh, rounded up: operand buffers + staged input block + harmonics
-size_t tc_smem_bytes(const Desc& d) {
+// sizeof(TcShared) in kernels/uvw_tc.cuh, rounded up: operand buffers + staged block + harmonics (+ the dy partials);
+// mode as in emit_tc
+size_t tc_smem_bytes(const Desc& d, int mode) {
     int maxd1 = 1;
-    for (auto& I : d.ins) maxd1 = std::max(maxd1, d.L[0][I.a].d());
-    return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 128 * (32 * maxd1 + 4) + 128 * (((int)d.dim[1] + 3) & ~3)) + 512;
+    for (auto& I : d.ins) maxd1 = std::max(maxd1, mode == 1 ? d.L[2][I.o].d() : d.L[0][I.a].d());
+    const size_t dys = mode == 2 ? 256 * (size_t)(d.dim[1] | 1) : 4;
+    return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 128 * (32 * maxd1 + 4) + 128 * (((int)d.dim[1] + 3) & ~3) + dys) + 512;
 }
 
-int tc_forward(Entry* e, TcParams p, cudaStream_t st) {
+// mode 0: z from (x, y, W); mode 1: the gradient of x from (g, y, W), passed in the places of x and z; mode 2: the
+// gradient of y (in the place of z) from (x, W, g)
+int tc_forward(Entry* e, TcParams p, cudaStream_t st, int mode = 0) {
+    static const char* names[3] = {"oeq_uvw_tc_forward", "oeq_uvw_tc_backward_dx", "oeq_uvw_tc_backward_dy"};
     int rc;
     if ((rc = status_word(&p.status))) return rc;
     Program* prog;
-    if ((rc = get_program(e, FAM_UVW_TC, &prog))) return rc;
+    if ((rc = get_program(e, mode == 0 ? FAM_UVW_TC : FAM_UVW_TC_DX + (mode - 1), &prog))) return rc;
     cudaKernel_t k;
-    const size_t smem = tc_smem_bytes(e->d);
-    if ((rc = get_kernel(prog, "oeq_uvw_tc_forward", smem, &k))) return rc;
+    const size_t smem = tc_smem_bytes(e->d, mode);
+    if ((rc = get_kernel(prog, names[mode], smem, &k))) return rc;
     long long tiles = (p.batch + 127) / 128, grid = sm_count();
     if (grid > tiles) grid = tiles;
     void* args[] = {&p};
     return launch(k, (unsigned)grid, 256, smem, args, st);
+}
+
+// Keep freed stream-ordered scratch in the device's pool: by default the pool gives memory back to the driver at every
+// synchronisation and the next call pays for mapping it again.
+int keep_pool_memory() {
+    static bool pool_kept[64] = {false};
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !pool_kept[dev]) {
+        cudaMemPool_t pool;
+        CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, dev));
+        uint64_t keep = UINT64_MAX;
+        CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        pool_kept[dev] = true;
+    }
+    return OEQB_OK;
+}
+
+// dW = sum over the batch, on the tensor cores: every CTA writes the sums of its tiles as one row of a partials matrix,
+// oeq_generic_dw_reduce adds the rows in order.
+int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* dW, long long batch, int accum, cudaStream_t st) {
+    int rc;
+    const Desc& d = e->d;
+    TcDwParams p{x, y, g, nullptr, batch, nullptr};
+    if ((rc = status_word(&p.status))) return rc;
+    Program *prog, *gen;
+    if ((rc = get_program(e, FAM_UVW_TC_DW, &prog))) return rc;
+    if ((rc = get_program(e, FAM_GENERIC, &gen))) return rc;
+    cudaKernel_t k, kr;
+    const size_t smem = 4 * (size_t)(2 * 128 * 128 + 2 * 32 * 128 + 128 * (d.dim[1] | 1)) + 256;
+    if ((rc = get_kernel(prog, "oeq_uvw_tc_backward_dw", smem, &k))) return rc;
+    if ((rc = get_kernel(gen, "oeq_generic_dw_reduce", 0, &kr))) return rc;
+    long long tiles = (batch + 127) / 128, grid = sm_count();
+    if (grid > tiles) grid = tiles;
+    if ((rc = keep_pool_memory())) return rc;
+    void* part = nullptr;
+    CUDA_TRY(cudaMallocAsync(&part, (size_t)grid * d.wn * sizeof(float), st));
+    p.part = part;
+    void* args[] = {&p};
+    rc = launch(k, (unsigned)grid, 256, smem, args, st);
+    if (!rc) {
+        void* rargs[] = {&part, &grid, &dW, &accum};
+        rc = launch(kr, (unsigned)((d.wn + 31) / 32), 256, 0, rargs, st);
+    }
+    cudaFreeAsync(part, st);
+    return rc;
+}
+
+// 'uvw' backward on the tensor cores; mask selects the outputs (1 dx, 2 dy, 4 dW).  dx is contracted with y_dx, dW with
+// y_dw (they differ in the second-order pass); accum adds to the outputs.
+int tc_backward(Entry* e, int mask, const void* x, const void* y_dx, const void* y_dw, const void* W, const void* g, void* dx,
+                void* dy, void* dW, long long batch, int accum, cudaStream_t st) {
+    if (mask & 1) {   // dx: the forward kernel on the transposed tables, with g in the place of x
+        TcParams t{g, y_dx, W, dx, nullptr, batch, accum, nullptr};
+        if (int rc = tc_forward(e, t, st, 1)) return rc;
+    }
+    if (mask & 2) {   // dy: g' = g W^T on the tensor cores, folded with x per item
+        TcParams t{x, nullptr, W, dy, g, batch, accum, nullptr};
+        if (int rc = tc_forward(e, t, st, 2)) return rc;
+    }
+    if (mask & 4)     // dW: reduction over the batch on the tensor cores, fixed-order sum of the CTAs' rows
+        if (int rc = tc_backward_dw(e, x, y_dw, g, dW, batch, accum, st)) return rc;
+    return OEQB_OK;
 }
 
 // A problem that the specialised kernels serve took a slower route: counted (oeqb_slow_path_count) and, with the log
@@ -1212,6 +1356,7 @@ int oeqb_set_option(const char* name, const char* value) {
     else if (n == "streams_forward") g_streams_fwd = atoi(value) != 0;
     else if (n == "validate") g_validate = atoi(value);
     else if (n == "no_tc") g_no_tc = atoi(value) != 0;
+    else if (n == "tc_backward") g_tc_backward = atoi(value) & 7;
     else return fail(OEQB_EINVAL, "unknown option '%s'", name);
     return OEQB_OK;
 }
@@ -1259,6 +1404,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     int done = 0;
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
         if (fam == FAM_UVW_TC) { if (!d.tc) continue; }
+        if (fam >= FAM_UVW_TC_DX && fam <= FAM_UVW_TC_DW) { if (!d.tc_bwd) continue; }
         else if (fam != FAM_GENERIC && !d.fast) continue;
         if (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC && d.fast_S4 < 3) continue;
         if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;
@@ -1289,7 +1435,7 @@ int oeqb_tp_forward(const void* desc, size_t desc_len, int64_t key, int64_t batc
         return fast_launch(e, 0, f, (cudaStream_t)stream);
     }
     if (e->d.tc && !g_force_generic && !g_no_tc) {
-        TcParams t{x, y, W, z, batch, nullptr};
+        TcParams t{x, y, W, z, nullptr, batch, 0, nullptr};
         return tc_forward(e, t, (cudaStream_t)stream);
     }
     FwdParams p{x, y, W, z, nullptr, nullptr, batch, batch, UNIT_ITEM, OUT_STORE};
@@ -1311,9 +1457,13 @@ int oeqb_tp_backward(const void* desc, size_t desc_len, int64_t key, int64_t bat
         FastParams f{x, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
         return fast_launch(e, 3, f, st);
     }
-    CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
-    BwdParams p{x, y, y, W, g, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, UNIT_ITEM, 0};
-    return generic_backward(e, p, st);
+    const int tcb = (d.tc_bwd && !g_force_generic && !g_no_tc && aligned16({dx, g})) ? g_tc_backward : 0;
+    if (tcb != 7) {
+        CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
+        BwdParams p{x, y, y, W, g, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, UNIT_ITEM, 0};
+        if (int rc = generic_backward(e, p, st)) return rc;
+    }
+    return tc_backward(e, tcb, x, y, y, W, g, dx, dy, dW, batch, 0, st);
 }
 
 int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int64_t batch, const void* x,
@@ -1347,6 +1497,17 @@ int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int6
         FastParams b{x, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
         b.X2 = x2; b.Y2 = y2; b.W2 = W2;   // both second-order backward terms in one pass
         return fast_launch(e, 3, b, st, nullptr, true);
+    }
+    if (d.tc_bwd && !g_force_generic && !g_no_tc && g_tc_backward == 7 && aligned16({dx, dg, g})) {
+        // the same five passes on the tensor-core kernels (the second and later ones add to their outputs)
+        TcParams t{x2, y, W, dg, nullptr, batch, 0, nullptr};
+        if ((rc = tc_forward(e, t, st, 0))) return rc;
+        t.x = x; t.y = y2; t.accum = 1;
+        if ((rc = tc_forward(e, t, st, 0))) return rc;
+        t.y = y; t.W = W2;
+        if ((rc = tc_forward(e, t, st, 0))) return rc;
+        if ((rc = tc_backward(e, 7, x2, y2, y, W, g, dx, dy, dW, batch, 0, st))) return rc;
+        return tc_backward(e, 7, x, y, y2, W2, g, dx, dy, dW, batch, 1, st);
     }
     CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
     // dg = F(x2, y, W) + F(x, y2, W) + F(x, y, W2): the product is linear in each argument
