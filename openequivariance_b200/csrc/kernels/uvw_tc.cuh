@@ -55,6 +55,15 @@ OEQ_DEV bool tc_mbar_wait(unsigned long long* bar, unsigned parity, volatile int
         }
     }
 }
+// Asynchronous copies global -> shared (16 or 4 bytes; nothing is read and zeros are written when !live): a staging
+// loop issues all of its copies back to back and waits once, so their latencies overlap.
+OEQ_DEV void tc_cp16(void* dst_smem, const void* src, bool live) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(tc_smem_u32(dst_smem)), "l"(src), "r"(live ? 16u : 0u) : "memory");
+}
+OEQ_DEV void tc_cp4(void* dst_smem, const void* src, bool live) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(tc_smem_u32(dst_smem)), "l"(src), "r"(live ? 4u : 0u) : "memory");
+}
+OEQ_DEV void tc_cp_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 OEQ_DEV float tc_tf32(float v) {   // round to tf32 (10-bit mantissa), result is a valid fp32 bit pattern
     unsigned r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
@@ -97,13 +106,18 @@ constexpr int TC_A_FLOATS = 128 * 32, TC_B_FLOATS = 32 * 32;
 constexpr int TC_XSTRIDE = 32 * TC_MAXD1 + (TC_MODE == 2 ? 1 : 4);
 constexpr int TC_DYS = L2_DIM | 1;              // mode 2: row of a thread's partial sums of dy
 constexpr int TC_YSTRIDE = (L2_DIM + 3) & ~3;
+constexpr int TC_CW = 16;                       // compute warps
+constexpr int TC_CT = 32 * TC_CW;               // compute threads
+constexpr int TC_THREADS = TC_CT + 32;          // ... and the warp that issues the MMAs
+constexpr int TC_EC = 128 / TC_CW;              // channels (accumulator columns) of one thread in an epilogue
 
 struct __align__(128) TcShared {
     float a[2][2][TC_A_FLOATS];       // [buffer][hi, lo]
     float b[2][2][TC_B_FLOATS];
     float xs[128 * TC_XSTRIDE];       // input block a(p) of the 128 items of the tile
     float ys[128 * TC_YSTRIDE];       // harmonics of the 128 items
-    float dys[TC_MODE == 2 ? 256 * TC_DYS : 4];   // mode 2: per-thread partial sums of dy (two threads per item)
+    float dys[TC_MODE == 2 ? TC_CT * TC_DYS : 4];   // mode 2: per-thread partial sums of dy (TC_CW / 4 threads per item)
+    unsigned long long a_full[2];     // the operands of a step are in place (every compute thread arrives)
     unsigned long long mma_done[2];   // a buffer may be rewritten
     unsigned long long acc_done[2];   // accumulators of an output block are complete
     unsigned tmem_base;
@@ -113,51 +127,65 @@ static_assert(sizeof(TcShared) > 116 * 1024 && sizeof(TcShared) <= 232448, "one 
 
 // offset (in floats) of element (row, kcol) in a chunk
 OEQ_DEV int tc_elem(int row, int kcol) { return (row >> 3) * (TC_SBO / 4) + (kcol >> 2) * (TC_LBO / 4) + (row & 7) * 4 + (kcol & 3); }
+OEQ_DEV void tc_mbar_arrive(unsigned long long* bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+OEQ_DEV void tc_compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(TC_CT) : "memory"); }   // the compute warps only
+// eight consecutive accumulator columns of this thread's TMEM lane
+OEQ_DEV void tc_ld8(unsigned taddr, unsigned (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 
-// Epilogue of one output block for one thread: its item's 16 output channels x D3 components are 16 * D3 consecutive
+// Epilogue of one output block for one thread: its item's TC_EC output channels x D3 components are TC_EC * D3 consecutive
 // floats of the z row.  All components are pulled out of tensor memory first (column 32 k + c holds channel c of
 // component k), then written as 16-byte stores, so every 32-byte sector of z is written whole.
 template <int D3>
 OEQ_DEV void tc_epilogue(unsigned tbase, float* zdst, bool live, bool accum) {
-    float v[16 * D3];   // v[c * D3 + k]
+    float v[TC_EC * D3];   // v[c * D3 + k]
 #pragma unroll
     for (int k = 0; k < D3; ++k) {
-        unsigned r[16];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-            : "r"(tbase + 32u * (unsigned)k) : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        unsigned r[8];
+        tc_ld8(tbase + 32u * (unsigned)k, r);
 #pragma unroll
-        for (int c = 0; c < 16; ++c) v[c * D3 + k] = __uint_as_float(r[c]);
+        for (int c = 0; c < TC_EC; ++c) v[c * D3 + k] = __uint_as_float(r[c]);
     }
     if (live) {
-        float4* dst = reinterpret_cast<float4*>(zdst);   // 64 * D3 bytes from a 16-byte boundary
+        float4* dst = reinterpret_cast<float4*>(zdst);   // 32 * D3 bytes from a 16-byte boundary
         if (accum) {
 #pragma unroll
-            for (int q = 0; q < 4 * D3; ++q) {
+            for (int q = 0; q < 2 * D3; ++q) {
                 const float4 old = dst[q];
                 v[4 * q] += old.x; v[4 * q + 1] += old.y; v[4 * q + 2] += old.z; v[4 * q + 3] += old.w;
             }
         }
 #pragma unroll
-        for (int q = 0; q < 4 * D3; ++q) __stcs(dst + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+        for (int q = 0; q < 2 * D3; ++q) __stcs(dst + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
     }
 }
+static_assert(TC_EC == 8, "the epilogues read eight accumulator columns per thread");
 
 #if TC_MODE != 3
 // The loops over paths, output components and Clebsch-Gordan terms are run-time loops over the TC_* tables of the
 // problem header (not unrolled): the whole kernel is a few KB of code and stays in the instruction cache.
 // The same kernel computes the gradient of the first input when it is compiled with the transposed tables (TC_WT = 1:
-// x is then the output cotangent, z the gradient, and the weight block is applied transposed); TC_KERNEL_NAME,
-// TC_IN_DIM and TC_OUT_DIM (row lengths of x and z) come with the tables.
-extern "C" __global__ void __launch_bounds__(256, 1) TC_KERNEL_NAME(const TcParams p) {
+// x is then the output cotangent, z the gradient, and the weight block is applied transposed), and the gradient of the
+// second input (mode 2); TC_KERNEL_NAME, TC_IN_DIM and TC_OUT_DIM (row lengths of x and z) come with the tables.
+//
+// Sixteen compute warps and one warp that issues the MMAs.  The compute warps never meet the issuing warp at a CTA-wide
+// barrier: a step's operands are handed over through the a_full mbarrier (every compute thread arrives after its
+// stores), buffers come back through mma_done, finished accumulators through acc_done (tcgen05.commit).  The compute
+// warps meet among themselves (named barrier) only where the staged input block changes hands.  A thread that gave up
+// keeps walking the loops and joining those barriers without doing work, so nobody waits for it.
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const TcParams p) {
     extern __shared__ __align__(128) unsigned char tc_smem_raw[];
     TcShared& sh = *reinterpret_cast<TcShared*>(tc_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     volatile int* abortf = &sh.abort_flag;
     if (tid == 0) {
+        tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
         tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
         tc_mbar_init(&sh.acc_done[0], 1); tc_mbar_init(&sh.acc_done[1], 1);
         sh.abort_flag = 0;
@@ -171,185 +199,181 @@ extern "C" __global__ void __launch_bounds__(256, 1) TC_KERNEL_NAME(const TcPara
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
-
-    // this thread's 16 elements of every A chunk: items brow, brow + 8 and channels ucol + 4 * uu, uu < 8
-    const int brow = warp * 16 + (lane >> 2);
-    const int ucol = lane & 3;
-    unsigned step = 0;     // chunk steps issued so far: A buffer = step & 1
+    const long long ntiles = (p.batch + 127) / 128;
+    unsigned step = 0;     // chunk steps so far: operand buffer = step & 1
     unsigned npath = 0;    // paths started so far: weight buffer = npath & 1
     unsigned nblock = 0;   // output blocks finished so far: accumulator half = nblock & 1
-    const long long ntiles = (p.batch + 127) / 128;
     bool dead = false;
 
-    for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
-        const long long item0 = tile * 128;
-        __syncthreads();   // previous tile's readers of xs / ys are done
-        if (TC_MODE != 2) {
-            for (int r = warp; r < 128; r += 8)          // one warp per row: no index division
-                for (int j = lane; j < L2_DIM; j += 32)
-                    sh.ys[r * TC_YSTRIDE + j] = (item0 + r < p.batch) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
-        } else {
-            for (int j = 0; j < TC_DYS; ++j) sh.dys[tid * TC_DYS + j] = 0.f;   // read and written by this thread only
-        }
-        for (int q = 0; q < NINS && !dead; ++q) {
-            const int d1 = TC_D1[q], d3 = TC_D3[q], xoff = TC_XOFF[q], zoff = TC_ZOFF[q], woff = TC_WOFF[q];
-            const int first = TC_FIRST[q], last = TC_LAST[q];
-            // stage the path's input block: rows of 32 * d1 contiguous floats, coalesced; the block stays when the previous
-            // path of this tile read the same one
-            const bool restage = q == 0 || TC_XOFF[q - 1] != xoff;
-            __syncthreads();   // readers of the previous path's block are done
-            const int rowlen = restage ? 32 * d1 : 0;
-            for (int c = lane; c < rowlen; c += 32) {   // warp w copies rows w, w + 8, ...: 16 independent loads in flight
-                float v[16];
-#pragma unroll
-                for (int rr = 0; rr < 16; ++rr) {
-                    const long long b = item0 + warp + 8 * rr;
-                    v[rr] = (b < p.batch) ? __ldg(p.x + b * TC_IN_DIM + xoff + c) : 0.f;
-                }
-#pragma unroll
-                for (int rr = 0; rr < 16; ++rr) sh.xs[(warp + 8 * rr) * TC_XSTRIDE + c] = v[rr];
-            }
-            __syncthreads();
-            const float* xrow0 = sh.xs + brow * TC_XSTRIDE + ucol * d1;
-            const float* xrow1 = xrow0 + 8 * TC_XSTRIDE;
-            const int ustride = 4 * d1;                 // distance between this thread's consecutive channels
-            const float* yrow0 = sh.ys + brow * TC_YSTRIDE;
-            const float* yrow1 = yrow0 + 8 * TC_YSTRIDE;
-            for (int k = 0; k < d3 && !dead; ++k) {
-                const unsigned buf = step & 1u;
-                // Clebsch-Gordan stage for output component k: 16 elements per thread, term by term
-                float acc0[8], acc1[8];
-#pragma unroll
-                for (int uu = 0; uu < 8; ++uu) { acc0[uu] = 0.f; acc1[uu] = 0.f; }
-                if (TC_MODE != 2) {
-                    const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
-                    for (int t = t0; t < t1; ++t) {
-                        const int ti = TC_TI[t], tj = TC_TJ[t];
-                        const float c = TC_TC[t];
-                        const float cy0 = c * yrow0[tj], cy1 = c * yrow1[tj];
-                        const float* px0 = xrow0 + ti;
-                        const float* px1 = xrow1 + ti;
-#pragma unroll
-                        for (int uu = 0; uu < 8; ++uu) {
-                            acc0[uu] = fmaf(cy0, px0[uu * ustride], acc0[uu]);
-                            acc1[uu] = fmaf(cy1, px1[uu * ustride], acc1[uu]);
-                        }
-                    }
-                } else {
-                    // mode 2: the A operand is component k of the cotangent's block itself, A[b][w] = g[b, o][w, k]
-                    const long long b0 = item0 + brow, b1 = b0 + 8;
-                    const float* g0 = p.g + (b0 < p.batch ? b0 : 0) * L3_DIM + zoff + ucol * d3 + k;
-                    const float* g1 = p.g + (b1 < p.batch ? b1 : 0) * L3_DIM + zoff + ucol * d3 + k;
-#pragma unroll
-                    for (int uu = 0; uu < 8; ++uu) {
-                        acc0[uu] = (b0 < p.batch) ? __ldg(g0 + uu * 4 * d3) : 0.f;
-                        acc1[uu] = (b1 < p.batch) ? __ldg(g1 + uu * 4 * d3) : 0.f;
-                    }
-                }
-                // the A buffer was last read by the MMAs of step - 2 (a commit covers every MMA issued before it)
-                if (step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 31)) dead = true;
-                if (!dead) {
-                    if (k == 0) {   // weight block of the path: B[n, kk] = W_p[kk, n] (forward: n = w, kk = u) or
-                                    // W_p[n, kk] (gradient: n = u, kk = w); its buffer was last read two paths ago
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            const int e = tid + 256 * r;          // e = u * 32 + w
-                            const int u = e >> 5, w = e & 31;
-                            const float v = __ldg(p.W + woff + e);
-                            const float hi = tc_tf32(v);
-                            const int off = TC_WT ? tc_elem(u, w) : tc_elem(w, u);
-                            sh.b[npath & 1u][0][off] = hi;
-                            sh.b[npath & 1u][1][off] = tc_tf32(v - hi);
-                        }
-                    }
-#pragma unroll
-                    for (int uu = 0; uu < 8; ++uu) {
-                        const int off0 = tc_elem(brow, ucol + 4 * uu), off1 = tc_elem(brow + 8, ucol + 4 * uu);
-                        const float h0 = tc_tf32(acc0[uu]), h1 = tc_tf32(acc1[uu]);
-                        sh.a[buf][0][off0] = h0;
-                        sh.a[buf][1][off0] = tc_tf32(acc0[uu] - h0);
-                        sh.a[buf][0][off1] = h1;
-                        sh.a[buf][1][off1] = tc_tf32(acc1[uu] - h1);
-                    }
-                    tc_fence_async_smem();
-                }
-                tc_fence_before();
-                __syncthreads();
-                tc_fence_after();
-                if (sh.abort_flag) dead = true;
-                if (!dead && tid == 0) {
-                    const unsigned bbuf = npath & 1u;
-                    const unsigned dcol = tmem + (nblock & 1u) * 256u + 32u * (unsigned)k;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const unsigned long long ah = tc_desc(&sh.a[buf][0][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                        const unsigned long long al = tc_desc(&sh.a[buf][1][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                        const unsigned long long bh = tc_desc(&sh.b[bbuf][0][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                        const unsigned long long bl = tc_desc(&sh.b[bbuf][1][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                        tc_mma(dcol, ah, bh, (first && ks == 0) ? 0u : 1u);
-                        tc_mma(dcol, al, bh, 1u);
-                        tc_mma(dcol, ah, bl, 1u);
-                    }
-                    tc_commit(&sh.mma_done[buf]);
-                    if (last && k == d3 - 1) tc_commit(&sh.acc_done[nblock & 1u]);
-                }
-                ++step;
-            }
-            if (last) {
-                // epilogue of the output block: accumulators -> z
-                if (!dead && !tc_mbar_wait(&sh.acc_done[nblock & 1u], (nblock >> 1) & 1u, abortf, p.status, 32)) dead = true;
-                if (!dead) {
+    if (warp == TC_CW) {
+        // ---- the issuing warp: for every step, wait for its operands, issue 12 MMAs (4 k-steps x 3 split terms), commit
+        for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
+            for (int q = 0; q < NINS && !dead; ++q) {
+                const int d3 = TC_D3[q], first = TC_FIRST[q], last = TC_LAST[q];
+                for (int k = 0; k < d3 && !dead; ++k) {
+                    const unsigned buf = step & 1u;
+                    if (!tc_mbar_wait(&sh.a_full[buf], (step >> 1) & 1u, abortf, p.status, 35)) { dead = true; break; }
                     tc_fence_after();
-                    const int qd = warp & 3, half = warp >> 2;          // TMEM lane quarter, column half
-                    const long long b = item0 + qd * 32 + lane;
-                    const unsigned tbase = tmem + ((unsigned)(qd * 32) << 16) + (nblock & 1u) * 256u + 16u * half;
-                    if (TC_MODE != 2) {
-                        float* zdst = p.z + (b < p.batch ? b : 0) * TC_OUT_DIM + zoff + 16 * half * d3;
-                        const bool live = b < p.batch;
-                        if (d3 == 1) tc_epilogue<1>(tbase, zdst, live, p.accum != 0);
-                        else if (d3 == 3) tc_epilogue<3>(tbase, zdst, live, p.accum != 0);
-                        else if (d3 == 5) tc_epilogue<5>(tbase, zdst, live, p.accum != 0);
-                        else tc_epilogue<7>(tbase, zdst, live, p.accum != 0);
-                    } else {
-                        // mode 2: the accumulators are g'[b][u, k] = sum_w W_p[u, w] g[b, o][w, k]; this thread folds its item's
-                        // 16 channels into dy[b][j] += c * sum_u x[b][u, i] g'[b][u, k], term by term
-                        float* dyp = sh.dys + tid * TC_DYS;
-                        const float* xb = sh.xs + (qd * 32 + lane) * TC_XSTRIDE + 16 * half * d1;
-                        for (int k = 0; k < d3; ++k) {
-                            unsigned r[16];
-                            asm volatile(
-                                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                                : "r"(tbase + 32u * (unsigned)k) : "memory");
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
-                            for (int t = t0; t < t1; ++t) {
-                                const float* px = xb + TC_TI[t];
-                                float dot = 0.f;
+                    if (lane == 0) {
+                        const unsigned bbuf = npath & 1u;
+                        const unsigned dcol = tmem + (nblock & 1u) * 256u + 32u * (unsigned)k;
 #pragma unroll
-                                for (int u = 0; u < 16; ++u) dot = fmaf(px[u * d1], __uint_as_float(r[u]), dot);
-                                dyp[TC_TJ[t]] = fmaf(TC_TC[t], dot, dyp[TC_TJ[t]]);
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const unsigned long long ah = tc_desc(&sh.a[buf][0][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
+                            const unsigned long long al = tc_desc(&sh.a[buf][1][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
+                            const unsigned long long bh = tc_desc(&sh.b[bbuf][0][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
+                            const unsigned long long bl = tc_desc(&sh.b[bbuf][1][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
+                            tc_mma(dcol, ah, bh, (first && ks == 0) ? 0u : 1u);
+                            tc_mma(dcol, al, bh, 1u);
+                            tc_mma(dcol, ah, bl, 1u);
+                        }
+                        tc_commit(&sh.mma_done[buf]);
+                        if (last && k == d3 - 1) tc_commit(&sh.acc_done[nblock & 1u]);
+                    }
+                    __syncwarp();
+                    ++step;
+                }
+                if (last) ++nblock;
+                ++npath;
+            }
+        }
+    } else {
+        // ---- compute warps.  This thread's 8 elements of every A chunk: item brow, channels ucol + 4 * uu, uu < 8
+        const int brow = warp * 8 + (lane >> 2);
+        const int ucol = lane & 3;
+        for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            const long long item0 = tile * 128;
+            tc_compute_sync();   // previous tile's readers of xs / ys / dys are done
+            if (TC_MODE != 2) {
+                for (int r = warp; r < 128; r += TC_CW)          // one warp per row: no index division
+                    for (int j = lane; j < L2_DIM; j += 32)
+                        sh.ys[r * TC_YSTRIDE + j] = (item0 + r < p.batch) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
+            } else {
+                for (int j = 0; j < TC_DYS; ++j) sh.dys[tid * TC_DYS + j] = 0.f;   // read and written by this thread only
+            }
+            for (int q = 0; q < NINS; ++q) {
+                const int d1 = TC_D1[q], d3 = TC_D3[q], xoff = TC_XOFF[q], zoff = TC_ZOFF[q], woff = TC_WOFF[q];
+                const int last = TC_LAST[q];
+                // stage the path's input block by asynchronous row copies; the block stays when the previous path of this
+                // tile read the same one
+                const bool restage = q == 0 || TC_XOFF[q - 1] != xoff;
+                tc_compute_sync();   // readers of the previous path's block are done
+                if (restage && !dead) {   // warp w copies rows w, w + 16, ...
+                    for (int r = warp; r < 128; r += TC_CW) {
+                        const long long b = item0 + r;
+                        const bool live = b < p.batch;
+                        const float* src = p.x + (live ? b : 0) * TC_IN_DIM + xoff;
+                        float* dst = sh.xs + r * TC_XSTRIDE;
+                        if (TC_MODE != 2) { for (int c = lane; c < 8 * d1; c += 32) tc_cp16(dst + 4 * c, src + 4 * c, live); }
+                        else { for (int c = lane; c < 32 * d1; c += 32) tc_cp4(dst + c, src + c, live); }
+                    }
+                    tc_cp_wait_all();
+                }
+                tc_compute_sync();
+                const float* xrow = sh.xs + brow * TC_XSTRIDE + ucol * d1;
+                const int ustride = 4 * d1;                 // distance between this thread's consecutive channels
+                const float* yrow = sh.ys + brow * TC_YSTRIDE;
+                for (int k = 0; k < d3; ++k) {
+                    const unsigned buf = step & 1u;
+                    float acc[8];
+#pragma unroll
+                    for (int uu = 0; uu < 8; ++uu) acc[uu] = 0.f;
+                    if (TC_MODE != 2) {
+                        // Clebsch-Gordan stage for component k, term by term
+                        const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
+                        for (int t = t0; t < t1; ++t) {
+                            const float cy = TC_TC[t] * yrow[TC_TJ[t]];
+                            const float* px = xrow + TC_TI[t];
+#pragma unroll
+                            for (int uu = 0; uu < 8; ++uu) acc[uu] = fmaf(cy, px[uu * ustride], acc[uu]);
+                        }
+                    } else {
+                        // mode 2: the A operand is component k of the cotangent's block itself, A[b][w] = g[b, o][w, k]
+                        const long long b0 = item0 + brow;
+                        const float* g0 = p.g + (b0 < p.batch ? b0 : 0) * L3_DIM + zoff + ucol * d3 + k;
+#pragma unroll
+                        for (int uu = 0; uu < 8; ++uu) acc[uu] = (b0 < p.batch) ? __ldg(g0 + uu * 4 * d3) : 0.f;
+                    }
+                    // the operand buffer was last read by the MMAs of step - 2 (a commit covers every MMA issued before it)
+                    if (!dead && step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 31)) dead = true;
+                    if (!dead) {
+                        if (k == 0) {   // weight block of the path: B[n, kk] = W_p[kk, n] (forward: n = w, kk = u) or
+                                        // W_p[n, kk] (gradients: n = u, kk = w); its buffer was last read two paths ago
+#pragma unroll
+                            for (int r = 0; r < 1024 / TC_CT; ++r) {
+                                const int e = tid + TC_CT * r;          // e = u * 32 + w
+                                const int u = e >> 5, w = e & 31;
+                                const float v = __ldg(p.W + woff + e);
+                                const float hi = tc_tf32(v);
+                                const int off = TC_WT ? tc_elem(u, w) : tc_elem(w, u);
+                                sh.b[npath & 1u][0][off] = hi;
+                                sh.b[npath & 1u][1][off] = tc_tf32(v - hi);
                             }
                         }
+#pragma unroll
+                        for (int uu = 0; uu < 8; ++uu) {
+                            const int off = tc_elem(brow, ucol + 4 * uu);
+                            const float h = tc_tf32(acc[uu]);
+                            sh.a[buf][0][off] = h;
+                            sh.a[buf][1][off] = tc_tf32(acc[uu] - h);
+                        }
+                        tc_fence_async_smem();
+                        tc_fence_before();
+                        tc_mbar_arrive(&sh.a_full[buf]);
                     }
-                    tc_fence_before();
+                    ++step;
                 }
-                ++nblock;
-                __syncthreads();                      // keeps the give-up decision uniform across the CTA
-                if (sh.abort_flag) dead = true;
+                if (last) {
+                    // epilogue of the output block: accumulators -> z
+                    if (!dead && !tc_mbar_wait(&sh.acc_done[nblock & 1u], (nblock >> 1) & 1u, abortf, p.status, 32)) dead = true;
+                    if (!dead) {
+                        tc_fence_after();
+                        const int qd = warp & 3, part = warp >> 2;          // TMEM lane quarter, column part
+                        const long long b = item0 + qd * 32 + lane;
+                        const unsigned tbase = tmem + ((unsigned)(qd * 32) << 16) + (nblock & 1u) * 256u + (unsigned)(TC_EC * part);
+                        if (TC_MODE != 2) {
+                            float* zdst = p.z + (b < p.batch ? b : 0) * TC_OUT_DIM + zoff + TC_EC * part * d3;
+                            const bool live = b < p.batch;
+                            if (d3 == 1) tc_epilogue<1>(tbase, zdst, live, p.accum != 0);
+                            else if (d3 == 3) tc_epilogue<3>(tbase, zdst, live, p.accum != 0);
+                            else if (d3 == 5) tc_epilogue<5>(tbase, zdst, live, p.accum != 0);
+                            else tc_epilogue<7>(tbase, zdst, live, p.accum != 0);
+                        } else {
+                            // mode 2: the accumulators are g'[b][u, k] = sum_w W_p[u, w] g[b, o][w, k]; this thread folds its
+                            // item's TC_EC channels into dy[b][j] += c * sum_u x[b][u, i] g'[b][u, k], term by term
+                            float* dyp = sh.dys + tid * TC_DYS;
+                            const float* xb = sh.xs + (qd * 32 + lane) * TC_XSTRIDE + TC_EC * part * d1;
+                            for (int k = 0; k < d3; ++k) {
+                                unsigned r[8];
+                                tc_ld8(tbase + 32u * (unsigned)k, r);
+                                const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
+                                for (int t = t0; t < t1; ++t) {
+                                    const float* px = xb + TC_TI[t];
+                                    float dot = 0.f;
+#pragma unroll
+                                    for (int u = 0; u < TC_EC; ++u) dot = fmaf(px[u * d1], __uint_as_float(r[u]), dot);
+                                    dyp[TC_TJ[t]] = fmaf(TC_TC[t], dot, dyp[TC_TJ[t]]);
+                                }
+                            }
+                        }
+                        tc_fence_before();
+                    }
+                    ++nblock;
+                }
+                ++npath;
             }
-            ++npath;
-        }
-        if (TC_MODE == 2) {
-            // dy of the tile: threads t and t + 128 hold the two channel halves of item t (warps 0-3 / 4-7 above)
-            __syncthreads();
-            const long long b = item0 + tid;
-            if (tid < 128 && b < p.batch && !dead)
-                for (int j = 0; j < L2_DIM; ++j) {
-                    const float v = sh.dys[tid * TC_DYS + j] + sh.dys[(tid + 128) * TC_DYS + j];
-                    p.z[b * L2_DIM + j] = p.accum ? p.z[b * L2_DIM + j] + v : v;
-                }
+            if (TC_MODE == 2) {
+                // dy of the tile: threads t, t + 128, ... hold the channel parts of item t
+                tc_compute_sync();
+                const long long b = item0 + tid;
+                if (tid < 128 && b < p.batch && !sh.abort_flag)
+                    for (int j = 0; j < L2_DIM; ++j) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int part = 0; part < TC_CW / 4; ++part) v += sh.dys[(tid + 128 * part) * TC_DYS + j];
+                        p.z[b * L2_DIM + j] = p.accum ? p.z[b * L2_DIM + j] + v : v;
+                    }
+            }
         }
     }
     tc_fence_before();
@@ -362,26 +386,29 @@ extern "C" __global__ void __launch_bounds__(256, 1) TC_KERNEL_NAME(const TcPara
 // ---- gradient of the shared weights ---------------------------------------------------------------------------
 //   dW_p[u, w] = sum_b sum_k T_p[b][u, k] * g[b, o][w, k],     T_p as in the forward (Clebsch-Gordan stage, CUDA cores)
 // A GEMM whose reduction runs over the batch.  Up to four paths into the same output block o are stacked on M (they share
-// the B operand): per step (group of paths, component k, tile of 128 items)
-//   D[(slot, u), w] += A[(slot, u), b] * B[w, b],   A = T (128 x 128), B = component k of the cotangent block (32 x 128),
-// both K-major with the items on K (16 tcgen05.mma of K = 8, three split terms each).  The accumulators of every group
+// the B operand): per step (group of paths, component k, tile of 64 items)
+//   D[(slot, u), w] += A[(slot, u), b] * B[w, b],   A = T (128 x 64), B = component k of the cotangent block (32 x 64),
+// both K-major with the items on K (8 tcgen05.mma of K = 8, three split terms each).  The accumulators of every group
 // stay in tensor memory (32 columns per group) over all tiles of the CTA; at the end the CTA stores them as one row of
 // a partials matrix that a second kernel sums in row order (bitwise reproducible).
-// Thread roles (256 threads): warp w computes T for slot w % 4 and the 64 items of half w / 4.  A lane covers channels
-// lane / 4 + 8 uu (uu < 4) and items lane % 4 + 4 bb (bb < 16): one load or store of the warp then touches 8 channels of
-// 4 items, which is 4 short runs in global memory and 32 different banks of the canonical layout.
+// The input blocks of a group's slots are staged in shared memory once per (tile, group) by coalesced row copies and serve
+// all components k.  Thread roles (256 threads): warp w computes T for slot w % 4 and the 32 items of half w / 4.  A
+// lane covers channels lane / 4 + 8 uu (uu < 4) and items lane % 4 + 4 bb (bb < 8): with staged rows of 32 d1 + 8 floats
+// its reads, and in the canonical operand layout its writes, fall into 32 different banks.
 struct TcDwParams {
     const float* x; const float* y; const float* g; float* part;
     long long batch;
     int* status;
 };
-constexpr unsigned TCW_LBO = 128, TCW_SBO = 4096;   // 128 K-columns: 32 core matrices of 128 bytes per 8-row group
-constexpr int TCW_A_FLOATS = 128 * 128, TCW_B_FLOATS = 32 * 128;
+constexpr int TCW_TILE = 64;
+constexpr unsigned TCW_LBO = 128, TCW_SBO = 2048;   // 64 K-columns: 16 core matrices of 128 bytes per 8-row group
+constexpr int TCW_A_FLOATS = 128 * TCW_TILE, TCW_B_FLOATS = 32 * TCW_TILE;
 constexpr int TCW_YS = L2_DIM | 1;
 struct __align__(128) TcDwShared {
     float a[2][TCW_A_FLOATS];         // [hi, lo]
     float b[2][TCW_B_FLOATS];
-    float ys[128 * TCW_YS];           // harmonics of the tile's items
+    float xs[TCW_XS_FLOATS];          // the input blocks of the group's slots for the tile's items (TCW_XSOFF, TCW_XS)
+    float ys[TCW_TILE * TCW_YS];      // harmonics of the tile's items
     unsigned long long mma_done;
     unsigned tmem_base;
     int abort_flag;
@@ -411,52 +438,60 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(cons
 
     const int slot = warp & 3, ihalf = warp >> 2, r8 = lane >> 2, b4 = lane & 3;
     unsigned nstep = 0;    // steps issued so far
-    const long long ntiles = (p.batch + 127) / 128;
+    const long long ntiles = (p.batch + TCW_TILE - 1) / TCW_TILE;
     bool dead = false;
 
     for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
-        const long long item0 = tile * 128;
-        __syncthreads();   // the previous tile's readers of ys are done
-        for (int r = warp; r < 128; r += 8)
-            for (int j = lane; j < L2_DIM; j += 32)
-                sh.ys[r * TCW_YS + j] = (item0 + r < p.batch) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
-        __syncthreads();
-        // rows of this thread's items; items past the end of the batch read row 0 and are multiplied by y = 0
-        const int ib = 64 * ihalf + b4;                  // first of this thread's 16 items of the A operand
+        const long long item0 = tile * TCW_TILE;
         const long long nlive = p.batch - item0;         // items of the tile that exist
         const bool first_tile = tile == blockIdx.x;
+        __syncthreads();   // the previous tile's readers of ys are done
+        for (int r = warp; r < TCW_TILE; r += 8)
+            for (int j = lane; j < L2_DIM; j += 32)
+                sh.ys[r * TCW_YS + j] = (r < nlive) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
         for (int grp = 0; grp < TCW_NGRP && !dead; ++grp) {
-            const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp];
+            const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp], ns = TCW_NS[grp];
+            // stage the slots' input blocks: warp w copies rows w, w + 8, ... (rows past the batch are zero)
+            __syncthreads();   // readers of the previous group's blocks are done
+            for (int sl = 0; sl < ns; ++sl) {
+                const int q = grp * 4 + sl, chunks = 8 * TCW_D1[q], xs_stride = 4 * chunks + 8;
+                for (int r = warp; r < TCW_TILE; r += 8) {
+                    const bool live = r < nlive;
+                    const float* src = p.x + (live ? item0 + r : 0) * L1_DIM + TCW_XOFF[q];
+                    float* dst = sh.xs + TCW_XSOFF[q] + r * xs_stride;
+                    for (int c = lane; c < chunks; c += 32) tc_cp16(dst + 4 * c, src + 4 * c, live);
+                }
+            }
+            tc_cp_wait_all();
+            __syncthreads();
+            const int q = grp * 4 + slot;
+            const int d1 = TCW_D1[q], xs_stride = 32 * d1 + 8;
+            const int ib = 32 * ihalf + b4;                  // first of this thread's 8 items of the A operand
+            const float* xt = sh.xs + TCW_XSOFF[q] + ib * xs_stride + r8 * d1;
             for (int k = 0; k < d3 && !dead; ++k) {
                 // Clebsch-Gordan stage: acc[uu][bb] = T[item ib + 4 bb][channel r8 + 8 uu] of this warp's slot
-                float acc[4][16];
+                float acc[4][8];
 #pragma unroll
                 for (int uu = 0; uu < 4; ++uu)
 #pragma unroll
-                    for (int bb = 0; bb < 16; ++bb) acc[uu][bb] = 0.f;
-                {
-                    const int q = grp * 4 + slot;
-                    const int d1 = TCW_D1[q];
-                    const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
-                    for (int t = t0; t < t1; ++t) {
-                        const float c = TCW_TC[t];
-                        const int tj = TCW_TJ[t];
-                        const float* px = p.x + TCW_XOFF[q] + r8 * d1 + TCW_TI[t];
+                    for (int bb = 0; bb < 8; ++bb) acc[uu][bb] = 0.f;
+                const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
+                for (int t = t0; t < t1; ++t) {
+                    const float c = TCW_TC[t];
+                    const float* py = sh.ys + ib * TCW_YS + TCW_TJ[t];
+                    const float* px = xt + TCW_TI[t];
 #pragma unroll
-                        for (int bb = 0; bb < 16; ++bb) {
-                            const int bi = ib + 4 * bb;
-                            const float cy = c * sh.ys[bi * TCW_YS + tj];
-                            const float* pb = px + (bi < nlive ? item0 + bi : 0) * L1_DIM;
+                    for (int bb = 0; bb < 8; ++bb) {
+                        const float cy = c * py[4 * bb * TCW_YS];
 #pragma unroll
-                            for (int uu = 0; uu < 4; ++uu) acc[uu][bb] = fmaf(cy, __ldg(pb + 8 * uu * d1), acc[uu][bb]);
-                        }
+                        for (int uu = 0; uu < 4; ++uu) acc[uu][bb] = fmaf(cy, px[4 * bb * xs_stride + 8 * uu * d1], acc[uu][bb]);
                     }
                 }
-                // this thread's 16 entries of B: rows w = r8 + 8 ww (ww < 4), items 16 * warp + b4 + 4 bb (bb < 4)
-                float gv[4][4];
+                // this thread's 8 entries of B: rows w = r8 + 8 ww (ww < 4), items 8 * warp + b4 + 4 bb (bb < 2)
+                float gv[4][2];
 #pragma unroll
-                for (int bb = 0; bb < 4; ++bb) {
-                    const int bi = 16 * warp + b4 + 4 * bb;
+                for (int bb = 0; bb < 2; ++bb) {
+                    const int bi = 8 * warp + b4 + 4 * bb;
                     const float* pg = p.g + (bi < nlive ? item0 + bi : 0) * L3_DIM + zoff + r8 * d3 + k;
 #pragma unroll
                     for (int ww = 0; ww < 4; ++ww) gv[ww][bb] = (bi < nlive) ? __ldg(pg + 8 * ww * d3) : 0.f;
@@ -467,7 +502,7 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(cons
 #pragma unroll
                     for (int uu = 0; uu < 4; ++uu)
 #pragma unroll
-                        for (int bb = 0; bb < 16; ++bb) {
+                        for (int bb = 0; bb < 8; ++bb) {
                             const int off = tcw_elem(slot * 32 + r8 + 8 * uu, ib + 4 * bb);
                             const float v = acc[uu][bb], hi = tc_tf32(v);
                             sh.a[0][off] = hi;
@@ -476,8 +511,8 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(cons
 #pragma unroll
                     for (int ww = 0; ww < 4; ++ww)
 #pragma unroll
-                        for (int bb = 0; bb < 4; ++bb) {
-                            const int off = tcw_elem(r8 + 8 * ww, 16 * warp + b4 + 4 * bb);
+                        for (int bb = 0; bb < 2; ++bb) {
+                            const int off = tcw_elem(r8 + 8 * ww, 8 * warp + b4 + 4 * bb);
                             const float hi = tc_tf32(gv[ww][bb]);
                             sh.b[0][off] = hi;
                             sh.b[1][off] = tc_tf32(gv[ww][bb] - hi);
@@ -491,7 +526,7 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(cons
                 if (!dead && tid == 0) {
                     const unsigned dcol = tmem + 32u * (unsigned)grp;
 #pragma unroll 4
-                    for (int ks = 0; ks < 16; ++ks) {
+                    for (int ks = 0; ks < TCW_TILE / 8; ++ks) {
                         const unsigned long long ah = tc_desc(&sh.a[0][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
                         const unsigned long long al = tc_desc(&sh.a[1][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
                         const unsigned long long bh = tc_desc(&sh.b[0][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);

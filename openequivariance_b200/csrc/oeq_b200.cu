@@ -115,6 +115,8 @@ struct Desc {
     size_t elt() const { return dtype == 2 ? 8 : 4; }
 };
 
+std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats);
+
 bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     std::istringstream in(std::string(text, len));
     std::string tok;
@@ -256,9 +258,8 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         for (auto& I : d.ins) read[I.a] = 1;
         d.tc_bwd = ok;
         for (int h : read) d.tc_bwd = d.tc_bwd && h;
-        int groups = 0;   // the weight-gradient kernel keeps one 32-column accumulator per group of four paths into a block
-        for (int h : hit) groups += (h + 3) / 4;
-        d.tc_bwd = d.tc_bwd && groups <= 16;
+        // the weight-gradient kernel keeps one 32-column accumulator per group of paths into a block
+        if (d.tc_bwd) d.tc_bwd = tc_dw_groups(d, nullptr).size() <= 16;
     }
     return true;
 }
@@ -568,7 +569,7 @@ std::string emit_tc(const Desc& d, int mode = 0) {
     }
     // run-time tables, one entry per path in schedule order
     auto ilist = [&](const char* name, const std::vector<long long>& v) {
-        s << "__device__ const int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
+        s << "__constant__ int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
         for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
         if (v.empty()) s << "0";
         s << "};\n";
@@ -594,11 +595,40 @@ std::string emit_tc(const Desc& d, int mode = 0) {
     s << "constexpr int TC_MAXD1 = " << maxd1 << ";\n";
     ilist("TC_D1", vd1); ilist("TC_D3", vd3); ilist("TC_XOFF", vx); ilist("TC_ZOFF", vz); ilist("TC_WOFF", vw);
     ilist("TC_FIRST", vf); ilist("TC_LAST", vl); ilist("TC_KBEG", kbeg); ilist("TC_TI", ti); ilist("TC_TJ", tj);
-    s << "__device__ const float TC_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
+    s << "__constant__ float TC_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
     for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
     if (tcf.empty()) s << "0";
     s << "};\n";
     return s.str();
+}
+
+// Groups of the tensor-core weight-gradient kernel: paths into the same output block, at most four per group and as many
+// as have room for their staged input blocks (64 rows of 32 d1 + 8 floats each) beside the operand buffers.
+std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats) {
+    const size_t fixed = 4 * (size_t)(2 * 128 * 64 + 2 * 32 * 64 + 64 * (d.dim[1] | 1)) + 512;
+    const size_t cap = (232448 - fixed) / 4 / 64;   // floats per staged row, summed over the slots
+    auto rowlen = [&](int q) { return (size_t)(32 * d.L[0][d.ins[q].a].d() + 8); };
+    std::vector<std::vector<int>> groups;
+    size_t most = 0;
+    for (size_t o = 0; o < d.L[2].size(); ++o) {
+        std::vector<int> cur;
+        size_t used = 0;
+        for (size_t q = 0; q < d.ins.size(); ++q)
+            if (d.ins[q].o == (int)o) {
+                if (!cur.empty() && (cur.size() == 4 || used + rowlen((int)q) > cap)) { groups.push_back(cur); cur.clear(); used = 0; }
+                cur.push_back((int)q);
+                used += rowlen((int)q);
+                most = std::max(most, used);
+            }
+        if (!cur.empty()) groups.push_back(cur);
+    }
+    if (xs_floats) *xs_floats = most * 64;
+    return groups;
+}
+size_t tc_dw_smem_bytes(const Desc& d) {
+    size_t xs_floats = 0;
+    tc_dw_groups(d, &xs_floats);
+    return 4 * (size_t)(2 * 128 * 64 + 2 * 32 * 64 + 64 * (d.dim[1] | 1) + xs_floats) + 512;
 }
 
 // Tables for the tensor-core weight-gradient kernel: the paths of an output block in groups of up to four slots.
@@ -606,32 +636,27 @@ std::string emit_tc_dw(const Desc& d) {
     std::ostringstream s;
     s << "#define OEQ_TC 1\n#define TC_MODE 3\n#define TC_WT 0\n#define TC_KERNEL_NAME oeq_uvw_tc_unused\n";
     s << "constexpr int TC_IN_DIM = " << d.dim[0] << ", TC_OUT_DIM = " << d.dim[2] << ";\n";
-    std::vector<std::vector<int>> groups;
-    for (size_t o = 0; o < d.L[2].size(); ++o) {
-        std::vector<int> cur;
-        for (size_t q = 0; q < d.ins.size(); ++q)
-            if (d.ins[q].o == (int)o) {
-                cur.push_back((int)q);
-                if (cur.size() == 4) { groups.push_back(cur); cur.clear(); }
-            }
-        if (!cur.empty()) groups.push_back(cur);
-    }
+    size_t xs_floats = 0;
+    const std::vector<std::vector<int>> groups = tc_dw_groups(d, &xs_floats);
     auto ilist = [&](const char* name, const std::vector<long long>& v) {
-        s << "__device__ const int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
+        s << "__constant__ int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
         for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
         if (v.empty()) s << "0";
         s << "};\n";
     };
-    std::vector<long long> ns, gd3, gz, sd1, sx, sw, kbeg, ti, tj;
+    std::vector<long long> ns, gd3, gz, sd1, sx, sw, sxs, kbeg, ti, tj;
     std::vector<double> tcf;
     int maxd1 = 1;
     for (auto& grp : groups) {
         const Block& O = d.L[2][d.ins[grp[0]].o];
         ns.push_back((long long)grp.size()); gd3.push_back(O.d()); gz.push_back(O.off);
+        long long xsoff = 0;
         for (int slot = 0; slot < 4; ++slot) {
             const bool used = slot < (int)grp.size();
             const Instr* I = used ? &d.ins[grp[slot]] : nullptr;
             sd1.push_back(used ? d.L[0][I->a].d() : 1); sx.push_back(used ? d.L[0][I->a].off : 0); sw.push_back(used ? I->woff : 0);
+            sxs.push_back(used ? xsoff : 0);
+            if (used) xsoff += 64LL * (32 * d.L[0][I->a].d() + 8);
             if (used) maxd1 = std::max(maxd1, d.L[0][I->a].d());
             for (int k = 0; k < 8; ++k) {
                 kbeg.push_back((long long)ti.size());
@@ -644,9 +669,11 @@ std::string emit_tc_dw(const Desc& d) {
     kbeg.push_back((long long)ti.size());
     s << "constexpr int TC_MAXD1 = " << maxd1 << ";\n";
     s << "constexpr int TCW_NGRP = " << groups.size() << ";\n";
+    s << "constexpr int TCW_XS_FLOATS = " << xs_floats << ";\n";
+    ilist("TCW_XSOFF", sxs);
     ilist("TCW_NS", ns); ilist("TCW_D3", gd3); ilist("TCW_ZOFF", gz); ilist("TCW_D1", sd1); ilist("TCW_XOFF", sx);
     ilist("TCW_WOFF", sw); ilist("TCW_KBEG", kbeg); ilist("TCW_TI", ti); ilist("TCW_TJ", tj);
-    s << "__device__ const float TCW_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
+    s << "__constant__ float TCW_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
     for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
     if (tcf.empty()) s << "0";
     s << "};\n";
@@ -1193,7 +1220,7 @@ struct TcDwParams {
 size_t tc_smem_bytes(const Desc& d, int mode) {
     int maxd1 = 1;
     for (auto& I : d.ins) maxd1 = std::max(maxd1, mode == 1 ? d.L[2][I.o].d() : d.L[0][I.a].d());
-    const size_t dys = mode == 2 ? 256 * (size_t)(d.dim[1] | 1) : 4;
+    const size_t dys = mode == 2 ? 512 * (size_t)(d.dim[1] | 1) : 4;   // TC_CT threads
     return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 128 * (32 * maxd1 + 4) + 128 * (((int)d.dim[1] + 3) & ~3) + dys) + 512;
 }
 
@@ -1211,7 +1238,7 @@ int tc_forward(Entry* e, TcParams p, cudaStream_t st, int mode = 0) {
     long long tiles = (p.batch + 127) / 128, grid = sm_count();
     if (grid > tiles) grid = tiles;
     void* args[] = {&p};
-    return launch(k, (unsigned)grid, 256, smem, args, st);
+    return launch(k, (unsigned)grid, 16 * 32 + 32, smem, args, st);   // TC_THREADS: sixteen compute warps + the issuing warp
 }
 
 // Keep freed stream-ordered scratch in the device's pool: by default the pool gives memory back to the driver at every
@@ -1241,10 +1268,10 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
     if ((rc = get_program(e, FAM_UVW_TC_DW, &prog))) return rc;
     if ((rc = get_program(e, FAM_GENERIC, &gen))) return rc;
     cudaKernel_t k, kr;
-    const size_t smem = 4 * (size_t)(2 * 128 * 128 + 2 * 32 * 128 + 128 * (d.dim[1] | 1)) + 256;
+    const size_t smem = tc_dw_smem_bytes(d);
     if ((rc = get_kernel(prog, "oeq_uvw_tc_backward_dw", smem, &k))) return rc;
     if ((rc = get_kernel(gen, "oeq_generic_dw_reduce", 0, &kr))) return rc;
-    long long tiles = (batch + 127) / 128, grid = sm_count();
+    long long tiles = (batch + 63) / 64, grid = sm_count();
     if (grid > tiles) grid = tiles;
     if ((rc = keep_pool_memory())) return rc;
     void* part = nullptr;
@@ -1434,7 +1461,7 @@ int oeqb_tp_forward(const void* desc, size_t desc_len, int64_t key, int64_t batc
         FastParams f{x, y, W, nullptr, z, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, batch, batch, nullptr};
         return fast_launch(e, 0, f, (cudaStream_t)stream);
     }
-    if (e->d.tc && !g_force_generic && !g_no_tc) {
+    if (e->d.tc && !g_force_generic && !g_no_tc && aligned16({x, z})) {
         TcParams t{x, y, W, z, nullptr, batch, 0, nullptr};
         return tc_forward(e, t, (cudaStream_t)stream);
     }
@@ -1457,7 +1484,7 @@ int oeqb_tp_backward(const void* desc, size_t desc_len, int64_t key, int64_t bat
         FastParams f{x, y, W, g, nullptr, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, nullptr};
         return fast_launch(e, 3, f, st);
     }
-    const int tcb = (d.tc_bwd && !g_force_generic && !g_no_tc && aligned16({dx, g})) ? g_tc_backward : 0;
+    const int tcb = (d.tc_bwd && !g_force_generic && !g_no_tc && aligned16({x, dx, g})) ? g_tc_backward : 0;
     if (tcb != 7) {
         CUDA_TRY(cudaMemsetAsync(dy, 0, batch * d.dim[1] * d.elt(), st));
         BwdParams p{x, y, y, W, g, dx, dy, dW, nullptr, nullptr, nullptr, batch, batch, UNIT_ITEM, 0};
@@ -1498,7 +1525,7 @@ int oeqb_tp_double_backward(const void* desc, size_t desc_len, int64_t key, int6
         b.X2 = x2; b.Y2 = y2; b.W2 = W2;   // both second-order backward terms in one pass
         return fast_launch(e, 3, b, st, nullptr, true);
     }
-    if (d.tc_bwd && !g_force_generic && !g_no_tc && g_tc_backward == 7 && aligned16({dx, dg, g})) {
+    if (d.tc_bwd && !g_force_generic && !g_no_tc && g_tc_backward == 7 && aligned16({x, x2, dx, dg, g})) {
         // the same five passes on the tensor-core kernels (the second and later ones add to their outputs)
         TcParams t{x2, y, W, dg, nullptr, batch, 0, nullptr};
         if ((rc = tc_forward(e, t, st, 0))) return rc;
