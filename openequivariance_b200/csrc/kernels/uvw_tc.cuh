@@ -115,7 +115,7 @@ struct __align__(128) TcShared {
     float a[2][2][TC_A_FLOATS];       // [buffer][hi, lo]
     float b[2][2][TC_B_FLOATS];
     float xs[128 * TC_XSTRIDE];       // input block a(p) of the 128 items of the tile
-    float ys[128 * TC_YSTRIDE];       // harmonics of the 128 items
+    float ys[TC_MODE == 2 ? 4 : 128 * TC_YSTRIDE];   // harmonics of the 128 items (mode 2 does not read them)
     float dys[TC_MODE == 2 ? TC_CT * TC_DYS : 4];   // mode 2: per-thread partial sums of dy (TC_CW / 4 threads per item)
     unsigned long long a_full[2];     // the operands of a step are in place (every compute thread arrives)
     unsigned long long mma_done[2];   // a buffer may be rewritten
@@ -206,7 +206,12 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
     bool dead = false;
 
     if (warp == TC_CW) {
-        // ---- the issuing warp: for every step, wait for its operands, issue 12 MMAs (4 k-steps x 3 split terms), commit
+        // ---- the issuing warp: for every step, wait for its operands, issue 12 MMAs (4 k-steps x 3 split terms), commit.
+        // The operand descriptors are built once; a k-step further along K is 256 bytes (16 in the address field) on.
+        const unsigned long long da0h = tc_desc(&sh.a[0][0][0], TC_LBO, TC_SBO), da0l = tc_desc(&sh.a[0][1][0], TC_LBO, TC_SBO);
+        const unsigned long long da1h = tc_desc(&sh.a[1][0][0], TC_LBO, TC_SBO), da1l = tc_desc(&sh.a[1][1][0], TC_LBO, TC_SBO);
+        const unsigned long long db0h = tc_desc(&sh.b[0][0][0], TC_LBO, TC_SBO), db0l = tc_desc(&sh.b[0][1][0], TC_LBO, TC_SBO);
+        const unsigned long long db1h = tc_desc(&sh.b[1][0][0], TC_LBO, TC_SBO), db1l = tc_desc(&sh.b[1][1][0], TC_LBO, TC_SBO);
         for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
             for (int q = 0; q < NINS && !dead; ++q) {
                 const int d3 = TC_D3[q], first = TC_FIRST[q], last = TC_LAST[q];
@@ -217,12 +222,12 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                     if (lane == 0) {
                         const unsigned bbuf = npath & 1u;
                         const unsigned dcol = tmem + (nblock & 1u) * 256u + 32u * (unsigned)k;
+                        const unsigned long long ah0 = buf ? da1h : da0h, al0 = buf ? da1l : da0l;
+                        const unsigned long long bh0 = bbuf ? db1h : db0h, bl0 = bbuf ? db1l : db0l;
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
-                            const unsigned long long ah = tc_desc(&sh.a[buf][0][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                            const unsigned long long al = tc_desc(&sh.a[buf][1][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                            const unsigned long long bh = tc_desc(&sh.b[bbuf][0][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
-                            const unsigned long long bl = tc_desc(&sh.b[bbuf][1][ks * 2 * (TC_LBO / 4)], TC_LBO, TC_SBO);
+                            const unsigned long long ah = ah0 + 16ull * ks, al = al0 + 16ull * ks;
+                            const unsigned long long bh = bh0 + 16ull * ks, bl = bl0 + 16ull * ks;
                             tc_mma(dcol, ah, bh, (first && ks == 0) ? 0u : 1u);
                             tc_mma(dcol, al, bh, 1u);
                             tc_mma(dcol, ah, bl, 1u);
@@ -386,44 +391,45 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
 // ---- gradient of the shared weights ---------------------------------------------------------------------------
 //   dW_p[u, w] = sum_b sum_k T_p[b][u, k] * g[b, o][w, k],     T_p as in the forward (Clebsch-Gordan stage, CUDA cores)
 // A GEMM whose reduction runs over the batch.  Up to four paths into the same output block o are stacked on M (they share
-// the B operand): per step (group of paths, component k, tile of 64 items)
-//   D[(slot, u), w] += A[(slot, u), b] * B[w, b],   A = T (128 x 64), B = component k of the cotangent block (32 x 64),
-// both K-major with the items on K (8 tcgen05.mma of K = 8, three split terms each).  The accumulators of every group
-// stay in tensor memory (32 columns per group) over all tiles of the CTA; at the end the CTA stores them as one row of
-// a partials matrix that a second kernel sums in row order (bitwise reproducible).
-// The input blocks of a group's slots are staged in shared memory once per (tile, group) by coalesced row copies and serve
-// all components k.  Thread roles (256 threads): warp w computes T for slot w % 4 and the 32 items of half w / 4.  A
-// lane covers channels lane / 4 + 8 uu (uu < 4) and items lane % 4 + 4 bb (bb < 8): with staged rows of 32 d1 + 8 floats
-// its reads, and in the canonical operand layout its writes, fall into 32 different banks.
+// the B operand): per step (group of paths, component k, 32 items)
+//   D[(slot, u), w] += A[(slot, u), b] * B[w, b],   A = T (128 x 32), B = component k of the cotangent block (32 x 32),
+// both K-major with the items on K (4 tcgen05.mma of K = 8, three split terms each; the chunk geometry of the forward).
+// The accumulators of every group stay in tensor memory (32 columns per group) over all tiles of the CTA; at the end
+// the CTA stores them as one row of a partials matrix that a second kernel sums in row order (bitwise reproducible).
+// The input blocks of a group's slots are staged in shared memory once per (tile of 64 items, group) by asynchronous row
+// copies and serve all components k and both halves of the tile.
+// Sixteen compute warps and one issuing warp, coupled through mbarriers like the forward.  Compute warp w works on slot
+// w % 4 and items 8 (w / 4) ... + 8 of the step's 32; a lane covers channels lane / 4 + 8 uu (uu < 4) and items lane % 4 + 4 bb
+// (bb < 2): with staged rows of 32 d1 + 8 floats its reads, and in the canonical operand layout its writes, fall into 32
+// different banks.
 struct TcDwParams {
     const float* x; const float* y; const float* g; float* part;
     long long batch;
     int* status;
 };
 constexpr int TCW_TILE = 64;
-constexpr unsigned TCW_LBO = 128, TCW_SBO = 2048;   // 64 K-columns: 16 core matrices of 128 bytes per 8-row group
-constexpr int TCW_A_FLOATS = 128 * TCW_TILE, TCW_B_FLOATS = 32 * TCW_TILE;
 constexpr int TCW_YS = L2_DIM | 1;
 struct __align__(128) TcDwShared {
-    float a[2][TCW_A_FLOATS];         // [hi, lo]
-    float b[2][TCW_B_FLOATS];
-    float xs[TCW_XS_FLOATS];          // the input blocks of the group's slots for the tile's items (TCW_XSOFF, TCW_XS)
+    float a[2][2][TC_A_FLOATS];       // [buffer][hi, lo]
+    float b[2][2][TC_B_FLOATS];
+    float xs[TCW_XS_FLOATS];          // the input blocks of the group's slots for the tile's items (TCW_XSOFF)
     float ys[TCW_TILE * TCW_YS];      // harmonics of the tile's items
-    unsigned long long mma_done;
+    unsigned long long a_full[2];
+    unsigned long long mma_done[2];
     unsigned tmem_base;
     int abort_flag;
 };
 static_assert(sizeof(TcDwShared) > 116 * 1024 && sizeof(TcDwShared) <= 232448, "one CTA per SM is assumed (it owns all of TMEM)");
 static_assert(TCW_NGRP * 32 <= 512, "one 32-column accumulator per group of paths");
-OEQ_DEV int tcw_elem(int row, int kcol) { return (row >> 3) * (TCW_SBO / 4) + (kcol >> 2) * (TCW_LBO / 4) + (row & 7) * 4 + (kcol & 3); }
 
-extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(const TcDwParams p) {
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_dw(const TcDwParams p) {
     extern __shared__ __align__(128) unsigned char tc_smem_raw[];
     TcDwShared& sh = *reinterpret_cast<TcDwShared*>(tc_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     volatile int* abortf = &sh.abort_flag;
     if (tid == 0) {
-        tc_mbar_init(&sh.mma_done, 1);
+        tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
+        tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -435,135 +441,143 @@ extern "C" __global__ void __launch_bounds__(256, 1) oeq_uvw_tc_backward_dw(cons
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sh.tmem_base;
-
-    const int slot = warp & 3, ihalf = warp >> 2, r8 = lane >> 2, b4 = lane & 3;
-    unsigned nstep = 0;    // steps issued so far
     const long long ntiles = (p.batch + TCW_TILE - 1) / TCW_TILE;
+    unsigned step = 0;     // steps so far: operand buffer = step & 1
     bool dead = false;
 
-    for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
-        const long long item0 = tile * TCW_TILE;
-        const long long nlive = p.batch - item0;         // items of the tile that exist
-        const bool first_tile = tile == blockIdx.x;
-        __syncthreads();   // the previous tile's readers of ys are done
-        for (int r = warp; r < TCW_TILE; r += 8)
-            for (int j = lane; j < L2_DIM; j += 32)
-                sh.ys[r * TCW_YS + j] = (r < nlive) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
-        for (int grp = 0; grp < TCW_NGRP && !dead; ++grp) {
-            const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp], ns = TCW_NS[grp];
-            // stage the slots' input blocks: warp w copies rows w, w + 8, ... (rows past the batch are zero)
-            __syncthreads();   // readers of the previous group's blocks are done
-            for (int sl = 0; sl < ns; ++sl) {
-                const int q = grp * 4 + sl, chunks = 8 * TCW_D1[q], xs_stride = 4 * chunks + 8;
-                for (int r = warp; r < TCW_TILE; r += 8) {
-                    const bool live = r < nlive;
-                    const float* src = p.x + (live ? item0 + r : 0) * L1_DIM + TCW_XOFF[q];
-                    float* dst = sh.xs + TCW_XSOFF[q] + r * xs_stride;
-                    for (int c = lane; c < chunks; c += 32) tc_cp16(dst + 4 * c, src + 4 * c, live);
+    if (warp == TC_CW) {
+        // ---- the issuing warp (operand descriptors built once, see the forward)
+        const unsigned long long da0h = tc_desc(&sh.a[0][0][0], TC_LBO, TC_SBO), da0l = tc_desc(&sh.a[0][1][0], TC_LBO, TC_SBO);
+        const unsigned long long da1h = tc_desc(&sh.a[1][0][0], TC_LBO, TC_SBO), da1l = tc_desc(&sh.a[1][1][0], TC_LBO, TC_SBO);
+        const unsigned long long db0h = tc_desc(&sh.b[0][0][0], TC_LBO, TC_SBO), db0l = tc_desc(&sh.b[0][1][0], TC_LBO, TC_SBO);
+        const unsigned long long db1h = tc_desc(&sh.b[1][0][0], TC_LBO, TC_SBO), db1l = tc_desc(&sh.b[1][1][0], TC_LBO, TC_SBO);
+        for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
+            const bool first_tile = tile == blockIdx.x;
+            for (int grp = 0; grp < TCW_NGRP && !dead; ++grp) {
+                const int d3 = TCW_D3[grp];
+                for (int kh = 0; kh < 2 * d3 && !dead; ++kh) {   // (component k, half of the tile)
+                    const unsigned buf = step & 1u;
+                    if (!tc_mbar_wait(&sh.a_full[buf], (step >> 1) & 1u, abortf, p.status, 36)) { dead = true; break; }
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const unsigned dcol = tmem + 32u * (unsigned)grp;
+                        const unsigned long long ah0 = buf ? da1h : da0h, al0 = buf ? da1l : da0l;
+                        const unsigned long long bh0 = buf ? db1h : db0h, bl0 = buf ? db1l : db0l;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const unsigned long long ah = ah0 + 16ull * ks, al = al0 + 16ull * ks;
+                            const unsigned long long bh = bh0 + 16ull * ks, bl = bl0 + 16ull * ks;
+                            tc_mma(dcol, ah, bh, (first_tile && kh == 0 && ks == 0) ? 0u : 1u);
+                            tc_mma(dcol, al, bh, 1u);
+                            tc_mma(dcol, ah, bl, 1u);
+                        }
+                        tc_commit(&sh.mma_done[buf]);
+                    }
+                    __syncwarp();
+                    ++step;
                 }
             }
-            tc_cp_wait_all();
-            __syncthreads();
-            const int q = grp * 4 + slot;
-            const int d1 = TCW_D1[q], xs_stride = 32 * d1 + 8;
-            const int ib = 32 * ihalf + b4;                  // first of this thread's 8 items of the A operand
-            const float* xt = sh.xs + TCW_XSOFF[q] + ib * xs_stride + r8 * d1;
-            for (int k = 0; k < d3 && !dead; ++k) {
-                // Clebsch-Gordan stage: acc[uu][bb] = T[item ib + 4 bb][channel r8 + 8 uu] of this warp's slot
-                float acc[4][8];
-#pragma unroll
-                for (int uu = 0; uu < 4; ++uu)
-#pragma unroll
-                    for (int bb = 0; bb < 8; ++bb) acc[uu][bb] = 0.f;
-                const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
-                for (int t = t0; t < t1; ++t) {
-                    const float c = TCW_TC[t];
-                    const float* py = sh.ys + ib * TCW_YS + TCW_TJ[t];
-                    const float* px = xt + TCW_TI[t];
-#pragma unroll
-                    for (int bb = 0; bb < 8; ++bb) {
-                        const float cy = c * py[4 * bb * TCW_YS];
-#pragma unroll
-                        for (int uu = 0; uu < 4; ++uu) acc[uu][bb] = fmaf(cy, px[4 * bb * xs_stride + 8 * uu * d1], acc[uu][bb]);
-                    }
-                }
-                // this thread's 8 entries of B: rows w = r8 + 8 ww (ww < 4), items 8 * warp + b4 + 4 bb (bb < 2)
-                float gv[4][2];
-#pragma unroll
-                for (int bb = 0; bb < 2; ++bb) {
-                    const int bi = 8 * warp + b4 + 4 * bb;
-                    const float* pg = p.g + (bi < nlive ? item0 + bi : 0) * L3_DIM + zoff + r8 * d3 + k;
-#pragma unroll
-                    for (int ww = 0; ww < 4; ++ww) gv[ww][bb] = (bi < nlive) ? __ldg(pg + 8 * ww * d3) : 0.f;
-                }
-                // the operand buffers were last read by the MMAs of the previous step
-                if (nstep >= 1 && !tc_mbar_wait(&sh.mma_done, (nstep - 1) & 1u, abortf, p.status, 33)) dead = true;
+        }
+    } else {
+        const int slot = warp & 3, sub = warp >> 2, r8 = lane >> 2, b4 = lane & 3;
+        for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            const long long item0 = tile * TCW_TILE;
+            const long long nlive = p.batch - item0;         // items of the tile that exist
+            tc_compute_sync();   // the previous tile's readers of ys are done
+            for (int r = warp; r < TCW_TILE; r += TC_CW)
+                for (int j = lane; j < L2_DIM; j += 32)
+                    sh.ys[r * TCW_YS + j] = (r < nlive) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
+            for (int grp = 0; grp < TCW_NGRP; ++grp) {
+                const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp], ns = TCW_NS[grp];
+                // stage the slots' input blocks: warp w copies rows w, w + 16, ... (rows past the batch are zero)
+                tc_compute_sync();   // readers of the previous group's blocks are done
                 if (!dead) {
-#pragma unroll
-                    for (int uu = 0; uu < 4; ++uu)
-#pragma unroll
-                        for (int bb = 0; bb < 8; ++bb) {
-                            const int off = tcw_elem(slot * 32 + r8 + 8 * uu, ib + 4 * bb);
-                            const float v = acc[uu][bb], hi = tc_tf32(v);
-                            sh.a[0][off] = hi;
-                            sh.a[1][off] = tc_tf32(v - hi);
+                    for (int sl = 0; sl < ns; ++sl) {
+                        const int q = grp * 4 + sl, chunks = 8 * TCW_D1[q], xs_stride = 4 * chunks + 8;
+                        for (int r = warp; r < TCW_TILE; r += TC_CW) {
+                            const bool live = r < nlive;
+                            const float* src = p.x + (live ? item0 + r : 0) * L1_DIM + TCW_XOFF[q];
+                            float* dst = sh.xs + TCW_XSOFF[q] + r * xs_stride;
+                            for (int c = lane; c < chunks; c += 32) tc_cp16(dst + 4 * c, src + 4 * c, live);
                         }
+                    }
+                    tc_cp_wait_all();
+                }
+                tc_compute_sync();
+                const int q = grp * 4 + slot;
+                const int d1 = TCW_D1[q], xs_stride = 32 * d1 + 8;
+                for (int kh = 0; kh < 2 * d3; ++kh) {
+                    const int k = kh >> 1, half = kh & 1;
+                    const unsigned buf = step & 1u;
+                    const int ic = 8 * sub + b4;                     // this thread's first column (item of the step's 32)
+                    const int ib = 32 * half + ic;                   // ... and its item of the tile; the second is 4 further
+                    // Clebsch-Gordan stage: acc[uu][bb] = T[item ib + 4 bb][channel r8 + 8 uu] of this warp's slot
+                    float acc[4][2];
 #pragma unroll
-                    for (int ww = 0; ww < 4; ++ww)
+                    for (int uu = 0; uu < 4; ++uu) { acc[uu][0] = 0.f; acc[uu][1] = 0.f; }
+                    const float* xt = sh.xs + TCW_XSOFF[q] + ib * xs_stride + r8 * d1;
+                    const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
+                    for (int t = t0; t < t1; ++t) {
+                        const float c = TCW_TC[t];
+                        const float* py = sh.ys + ib * TCW_YS + TCW_TJ[t];
+                        const float* px = xt + TCW_TI[t];
+                        const float cy0 = c * py[0], cy1 = c * py[4 * TCW_YS];
+#pragma unroll
+                        for (int uu = 0; uu < 4; ++uu) {
+                            acc[uu][0] = fmaf(cy0, px[8 * uu * d1], acc[uu][0]);
+                            acc[uu][1] = fmaf(cy1, px[4 * xs_stride + 8 * uu * d1], acc[uu][1]);
+                        }
+                    }
+                    // this thread's 2 entries of B: row w = r8 + 8 * slot, the same two items
+                    float gv[2];
+#pragma unroll
+                    for (int bb = 0; bb < 2; ++bb) {
+                        const int bi = ib + 4 * bb;
+                        gv[bb] = (bi < nlive) ? __ldg(p.g + (item0 + bi) * L3_DIM + zoff + (r8 + 8 * slot) * d3 + k) : 0.f;
+                    }
+                    if (!dead && step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 33)) dead = true;
+                    if (!dead) {
+#pragma unroll
+                        for (int uu = 0; uu < 4; ++uu)
+#pragma unroll
+                            for (int bb = 0; bb < 2; ++bb) {
+                                const int off = tc_elem(slot * 32 + r8 + 8 * uu, ic + 4 * bb);
+                                const float v = acc[uu][bb], hi = tc_tf32(v);
+                                sh.a[buf][0][off] = hi;
+                                sh.a[buf][1][off] = tc_tf32(v - hi);
+                            }
 #pragma unroll
                         for (int bb = 0; bb < 2; ++bb) {
-                            const int off = tcw_elem(r8 + 8 * ww, 8 * warp + b4 + 4 * bb);
-                            const float hi = tc_tf32(gv[ww][bb]);
-                            sh.b[0][off] = hi;
-                            sh.b[1][off] = tc_tf32(gv[ww][bb] - hi);
+                            const int off = tc_elem(r8 + 8 * slot, ic + 4 * bb);
+                            const float hi = tc_tf32(gv[bb]);
+                            sh.b[buf][0][off] = hi;
+                            sh.b[buf][1][off] = tc_tf32(gv[bb] - hi);
                         }
-                    tc_fence_async_smem();
-                }
-                tc_fence_before();
-                __syncthreads();
-                tc_fence_after();
-                if (sh.abort_flag) dead = true;
-                if (!dead && tid == 0) {
-                    const unsigned dcol = tmem + 32u * (unsigned)grp;
-#pragma unroll 4
-                    for (int ks = 0; ks < TCW_TILE / 8; ++ks) {
-                        const unsigned long long ah = tc_desc(&sh.a[0][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
-                        const unsigned long long al = tc_desc(&sh.a[1][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
-                        const unsigned long long bh = tc_desc(&sh.b[0][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
-                        const unsigned long long blo = tc_desc(&sh.b[1][ks * 2 * (TCW_LBO / 4)], TCW_LBO, TCW_SBO);
-                        tc_mma(dcol, ah, bh, (first_tile && k == 0 && ks == 0) ? 0u : 1u);
-                        tc_mma(dcol, al, bh, 1u);
-                        tc_mma(dcol, ah, blo, 1u);
+                        tc_fence_async_smem();
+                        tc_fence_before();
+                        tc_mbar_arrive(&sh.a_full[buf]);
                     }
-                    tc_commit(&sh.mma_done);
+                    ++step;
                 }
-                ++nstep;
             }
         }
-    }
-    // the CTA's sums: row blockIdx.x of the partials matrix.  TMEM lane = (slot, u), column = 32 * group + w.
-    if (!dead && nstep >= 1 && !tc_mbar_wait(&sh.mma_done, (nstep - 1) & 1u, abortf, p.status, 34)) dead = true;
-    if (!dead && nstep >= 1) {
-        tc_fence_after();
-        const int half = warp >> 2;
-        float* prow = p.part + (long long)blockIdx.x * WN;
-        for (int grp = 0; grp < TCW_NGRP; ++grp) {
-            if (slot >= TCW_NS[grp]) continue;   // uniform in the warp
-            unsigned r[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)grp + 16u * half) : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            float4* dst = reinterpret_cast<float4*>(prow + TCW_WOFF[grp * 4 + slot] + lane * 32 + 16 * half);
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                dst[c] = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),
-                                     __uint_as_float(r[4 * c + 3]));
+        // the CTA's sums: row blockIdx.x of the partials matrix.  TMEM lane = (slot, u), column = 32 * group + w.
+        if (!dead && step >= 1 && !tc_mbar_wait(&sh.mma_done[(step - 1) & 1u], ((step - 1) >> 1) & 1u, abortf, p.status, 34)) dead = true;
+        if (!dead && step >= 1) {
+            tc_fence_after();
+            float* prow = p.part + (long long)blockIdx.x * WN;
+            for (int grp = 0; grp < TCW_NGRP; ++grp) {
+                if (slot >= TCW_NS[grp]) continue;   // uniform in the warp
+                unsigned r[8];
+                tc_ld8(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)grp + (unsigned)(TC_EC * sub), r);
+                float4* dst = reinterpret_cast<float4*>(prow + TCW_WOFF[grp * 4 + slot] + lane * 32 + TC_EC * sub);
+                dst[0] = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
+                dst[1] = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+            }
+            tc_fence_before();
         }
-        tc_fence_before();
     }
+    tc_fence_before();
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }

@@ -116,6 +116,7 @@ struct Desc {
 };
 
 std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats);
+size_t tc_smem_bytes(const Desc& d, int mode);
 
 bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     std::istringstream in(std::string(text, len));
@@ -260,6 +261,8 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         for (int h : read) d.tc_bwd = d.tc_bwd && h;
         // the weight-gradient kernel keeps one 32-column accumulator per group of paths into a block
         if (d.tc_bwd) d.tc_bwd = tc_dw_groups(d, nullptr).size() <= 16;
+        d.tc = d.tc && tc_smem_bytes(d, 0) <= 232448;
+        d.tc_bwd = d.tc_bwd && d.tc && tc_smem_bytes(d, 1) <= 232448 && tc_smem_bytes(d, 2) <= 232448;
     }
     return true;
 }
@@ -605,7 +608,7 @@ std::string emit_tc(const Desc& d, int mode = 0) {
 // Groups of the tensor-core weight-gradient kernel: paths into the same output block, at most four per group and as many
 // as have room for their staged input blocks (64 rows of 32 d1 + 8 floats each) beside the operand buffers.
 std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats) {
-    const size_t fixed = 4 * (size_t)(2 * 128 * 64 + 2 * 32 * 64 + 64 * (d.dim[1] | 1)) + 512;
+    const size_t fixed = 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 64 * (d.dim[1] | 1)) + 512;
     const size_t cap = (232448 - fixed) / 4 / 64;   // floats per staged row, summed over the slots
     auto rowlen = [&](int q) { return (size_t)(32 * d.L[0][d.ins[q].a].d() + 8); };
     std::vector<std::vector<int>> groups;
@@ -628,7 +631,7 @@ std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats) {
 size_t tc_dw_smem_bytes(const Desc& d) {
     size_t xs_floats = 0;
     tc_dw_groups(d, &xs_floats);
-    return 4 * (size_t)(2 * 128 * 64 + 2 * 32 * 64 + 64 * (d.dim[1] | 1) + xs_floats) + 512;
+    return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 64 * (d.dim[1] | 1) + xs_floats) + 512;
 }
 
 // Tables for the tensor-core weight-gradient kernel: the paths of an output block in groups of up to four slots.
@@ -1221,7 +1224,9 @@ size_t tc_smem_bytes(const Desc& d, int mode) {
     int maxd1 = 1;
     for (auto& I : d.ins) maxd1 = std::max(maxd1, mode == 1 ? d.L[2][I.o].d() : d.L[0][I.a].d());
     const size_t dys = mode == 2 ? 512 * (size_t)(d.dim[1] | 1) : 4;   // TC_CT threads
-    return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 128 * (32 * maxd1 + 4) + 128 * (((int)d.dim[1] + 3) & ~3) + dys) + 512;
+    const size_t ys = mode == 2 ? 4 : 128 * (size_t)(((int)d.dim[1] + 3) & ~3);
+    const size_t xs = 128 * (size_t)(32 * maxd1 + (mode == 2 ? 1 : 4));
+    return 4 * (2 * 2 * 4096 + 2 * 2 * 1024 + xs + ys + dys) + 256;
 }
 
 // mode 0: z from (x, y, W); mode 1: the gradient of x from (g, y, W), passed in the places of x and z; mode 2: the
@@ -1278,7 +1283,7 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
     CUDA_TRY(cudaMallocAsync(&part, (size_t)grid * d.wn * sizeof(float), st));
     p.part = part;
     void* args[] = {&p};
-    rc = launch(k, (unsigned)grid, 256, smem, args, st);
+    rc = launch(k, (unsigned)grid, 16 * 32 + 32, smem, args, st);   // TC_THREADS
     if (!rc) {
         void* rargs[] = {&part, &grid, &dW, &accum};
         rc = launch(kr, (unsigned)((d.wn + 31) / 32), 256, 0, rargs, st);

@@ -189,3 +189,66 @@ def test_uvw_tensor_core_forward_is_used_and_matches_general_kernel():
             native.set_option("no_tc", "0")
         assert rel_l2(got, ref) <= 2e-6
         assert rel_l2(got, tp_oracle.forward(p, x, y, tp.reorder_weights_to_e3nn(w))) <= 1e-5
+
+
+def _l3_uvw_problem():
+    """32 channels of l = 0 ... 3 with parities, shared weights: 7-component blocks on the tensor-core path."""
+    from openequivariance_b200.core import problems as P
+    feats = "32x0e+32x1o+32x2e+32x3o"
+    return P.FullyConnectedTPProblem(feats, "1x0e+1x1o+1x2e+1x3o", feats, shared_weights=True, label="uvw-l3",
+                                     irrep_dtype=np.float32, weight_dtype=np.float32)
+
+
+@pytest.mark.parametrize("which", ["nequip_like", "l3"])
+def test_uvw_tensor_core_backward_is_used_and_matches_general_kernel_and_oracle(which):
+    """Backward of the shared-weight 'uvw' problems on the tcgen05 kernels (gradient of x: the forward kernel on transposed
+    tables; gradient of y: g W^T on the tensor cores folded with x; gradient of W: a GEMM over the batch with ordered
+    partial sums): four launches, results equal to the general CUDA-core kernels to rounding and to the fp64 oracle to
+    the fp32 tolerance, on ragged batches around the 64- and 128-item tiles; dW is bitwise reproducible."""
+    from openequivariance_b200 import native
+    p = dict(MATRIX)["nequip_like"] if which == "nequip_like" else _l3_uvw_problem()
+    tp = _module(p)
+    assert native.query(tp.kernel_string.encode(), tp.hash).fast_path == 2
+    ops = torch.ops.libtorch_tp_jit
+    for B in (1, 63, 65, 129, 1000, 6000):
+        x, y, w, g, *_ = uniform_inputs(p, B, seed=B)
+        args = [torch.tensor(a, device="cuda") for a in (x, y, w, g)]
+        before = native.launch_count()
+        got = [t.cpu().numpy() for t in ops.jit_tp_backward(tp.kernel, tp.hash, *args)]
+        assert native.launch_count() == before + 4
+        again = ops.jit_tp_backward(tp.kernel, tp.hash, *args)
+        assert all(np.array_equal(a, b.cpu().numpy()) for a, b in zip(got, again))
+        native.set_option("tc_backward", "0")
+        try:
+            ref = [t.cpu().numpy() for t in ops.jit_tp_backward(tp.kernel, tp.hash, *args)]
+        finally:
+            native.set_option("tc_backward", "7")
+        for a, b, what in zip(got, ref, ("dx", "dy", "dW")):
+            assert rel_l2(a, b) <= 5e-6, (B, what)
+        if B <= 1000:
+            want = tp_oracle.backward(p, x, y, tp.reorder_weights_to_e3nn(w), g)
+            want = (want[0], want[1], tp.reorder_weights_from_e3nn(want[2]))
+            for a, b, what in zip(got, want, ("dx", "dy", "dW")):
+                assert rel_l2(a, b) <= 1e-5, (B, what)
+    native.check(native.load().oeqb_check_status(), "status")
+
+
+def test_uvw_tensor_core_double_backward_matches_general_kernels():
+    """The second-order pass of the shared-weight 'uvw' problem runs its five terms on the tensor-core kernels (the later
+    ones add to their outputs): same results as the general kernels, to rounding."""
+    from openequivariance_b200 import native
+    p = dict(MATRIX)["nequip_like"]
+    tp = _module(p)
+    ops = torch.ops.libtorch_tp_jit
+    for B in (77, 1500):
+        x, y, w, g, *_ = uniform_inputs(p, B, seed=B)
+        x2, y2, w2, *_ = uniform_inputs(p, B, seed=B + 1)
+        args = [torch.tensor(a, device="cuda") for a in (x, y, w, g, x2, y2, w2)]
+        got = [t.cpu().numpy() for t in ops.jit_tp_double_backward(tp.kernel, tp.hash, *args)]
+        native.set_option("tc_backward", "0")
+        try:
+            ref = [t.cpu().numpy() for t in ops.jit_tp_double_backward(tp.kernel, tp.hash, *args)]
+        finally:
+            native.set_option("tc_backward", "7")
+        for a, b, what in zip(got, ref, ("dx", "dy", "dW", "dg")):
+            assert rel_l2(a, b) <= 5e-6, (B, what)
