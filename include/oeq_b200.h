@@ -232,7 +232,9 @@ OEQB_API int oeqb_emit_source(const void* desc, size_t desc_len, const char* kin
  * constructors (tensorproducts.hpp:32-46, convolution.hpp:36-56). */
 OEQB_API int oeqb_precompile(const void* desc, size_t desc_len, int64_t key);
 
-/* String options: "cache_dir" (cubin cache directory), "force_generic" ("0"/"1"), "log" ("0"/"1"). */
+/* String options: "cache_dir" (cubin cache directory), "log" ("0"/"1"), "validate" ("0"/"1"/"2": index checks), and the
+ * tuning aids "force_generic", "single_group", "single_producer", "no_tc", "tc_backward" ("0".."7"), "streams",
+ * "streams_forward".  Unknown names are refused with OEQB_EINVAL. */
 OEQB_API int oeqb_set_option(const char* name, const char* value);
 
 /* Number of kernel launches issued by this library since load (all threads). */
