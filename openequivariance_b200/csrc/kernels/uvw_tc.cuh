@@ -64,6 +64,15 @@ OEQ_DEV void tc_cp4(void* dst_smem, const void* src, bool live) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(tc_smem_u32(dst_smem)), "l"(src), "r"(live ? 4u : 0u) : "memory");
 }
 OEQ_DEV void tc_cp_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// One row by a bulk copy (TMA, untiled): 16-byte aligned addresses, a multiple of 16 bytes; completion is counted in
+// bytes on the mbarrier.
+OEQ_DEV void tc_bulk_row(void* dst_smem, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(tc_smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(tc_smem_u32(bar)) : "memory");
+}
+OEQ_DEV void tc_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(tc_smem_u32(bar)), "r"(bytes) : "memory");
+}
 OEQ_DEV float tc_tf32(float v) {   // round to tf32 (10-bit mantissa), result is a valid fp32 bit pattern
     unsigned r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
@@ -120,6 +129,7 @@ struct __align__(128) TcShared {
     unsigned long long a_full[2];     // the operands of a step are in place (every compute thread arrives)
     unsigned long long mma_done[2];   // a buffer may be rewritten
     unsigned long long acc_done[2];   // accumulators of an output block are complete
+    unsigned long long xs_full;       // the staged input block has arrived (bytes of the bulk copies)
     unsigned tmem_base;
     int abort_flag;
 };
@@ -168,6 +178,18 @@ OEQ_DEV void tc_epilogue(unsigned tbase, float* zdst, bool live, bool accum) {
 static_assert(TC_EC == 8, "the epilogues read eight accumulator columns per thread");
 
 #if TC_MODE != 3
+// Clebsch-Gordan stage of one step for one thread: its 8 channels are 4 * D1 floats apart in the staged row (D1 at
+// compile time makes those offsets immediates).
+template <int D1>
+OEQ_DEV void tc_cg(const float* xrow, const float* yrow, int t0, int t1, float (&acc)[8]) {
+    for (int t = t0; t < t1; ++t) {
+        const float cy = TC_TC[t] * yrow[TC_TJ[t]];
+        const float* px = xrow + TC_TI[t];
+#pragma unroll
+        for (int uu = 0; uu < 8; ++uu) acc[uu] = fmaf(cy, px[uu * 4 * D1], acc[uu]);
+    }
+}
+
 // The loops over paths, output components and Clebsch-Gordan terms are run-time loops over the TC_* tables of the
 // problem header (not unrolled): the whole kernel is a few KB of code and stays in the instruction cache.
 // The same kernel computes the gradient of the first input when it is compiled with the transposed tables (TC_WT = 1:
@@ -188,6 +210,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
         tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
         tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
         tc_mbar_init(&sh.acc_done[0], 1); tc_mbar_init(&sh.acc_done[1], 1);
+        tc_mbar_init(&sh.xs_full, 1);
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -246,6 +269,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
         // ---- compute warps.  This thread's 8 elements of every A chunk: item brow, channels ucol + 4 * uu, uu < 8
         const int brow = warp * 8 + (lane >> 2);
         const int ucol = lane & 3;
+        unsigned nstage = 0;   // staged blocks so far (phase of xs_full)
+        float gnext[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // mode 2: the next step's cotangent values
         for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             const long long item0 = tile * 128;
             tc_compute_sync();   // previous tile's readers of xs / ys / dys are done
@@ -263,18 +288,31 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                 // tile read the same one
                 const bool restage = q == 0 || TC_XOFF[q - 1] != xoff;
                 tc_compute_sync();   // readers of the previous path's block are done
-                if (restage && !dead) {   // warp w copies rows w, w + 16, ...
-                    for (int r = warp; r < 128; r += TC_CW) {
-                        const long long b = item0 + r;
-                        const bool live = b < p.batch;
-                        const float* src = p.x + (live ? b : 0) * TC_IN_DIM + xoff;
-                        float* dst = sh.xs + r * TC_XSTRIDE;
-                        if (TC_MODE != 2) { for (int c = lane; c < 8 * d1; c += 32) tc_cp16(dst + 4 * c, src + 4 * c, live); }
-                        else { for (int c = lane; c < 32 * d1; c += 32) tc_cp4(dst + c, src + c, live); }
+                if (TC_MODE != 2) {
+                    // one bulk copy per row, issued by the first 128 threads; everybody waits for the bytes to arrive.  Rows past
+                    // the end of the batch read row 0: their results are never stored.
+                    if (restage && !dead) {
+                        if (tid == 0) tc_mbar_expect_tx(&sh.xs_full, 128u * 128u * (unsigned)d1);
+                        if (tid < 128) {
+                            const long long b = item0 + tid;
+                            tc_bulk_row(sh.xs + tid * TC_XSTRIDE, p.x + (b < p.batch ? b : 0) * TC_IN_DIM + xoff, 128u * (unsigned)d1, &sh.xs_full);
+                        }
+                        if (!tc_mbar_wait(&sh.xs_full, nstage & 1u, abortf, p.status, 37)) dead = true;
+                        ++nstage;
                     }
-                    tc_cp_wait_all();
+                } else {
+                    if (restage && !dead) {   // warp w copies rows w, w + 16, ... (odd row stride: 4-byte pieces)
+                        for (int r = warp; r < 128; r += TC_CW) {
+                            const long long b = item0 + r;
+                            const bool live = b < p.batch;
+                            const float* src = p.x + (live ? b : 0) * TC_IN_DIM + xoff;
+                            float* dst = sh.xs + r * TC_XSTRIDE;
+                            for (int c = lane; c < 32 * d1; c += 32) tc_cp4(dst + c, src + c, live);
+                        }
+                        tc_cp_wait_all();
+                    }
+                    tc_compute_sync();
                 }
-                tc_compute_sync();
                 const float* xrow = sh.xs + brow * TC_XSTRIDE + ucol * d1;
                 const int ustride = 4 * d1;                 // distance between this thread's consecutive channels
                 const float* yrow = sh.ys + brow * TC_YSTRIDE;
@@ -286,18 +324,30 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                     if (TC_MODE != 2) {
                         // Clebsch-Gordan stage for component k, term by term
                         const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
-                        for (int t = t0; t < t1; ++t) {
-                            const float cy = TC_TC[t] * yrow[TC_TJ[t]];
-                            const float* px = xrow + TC_TI[t];
-#pragma unroll
-                            for (int uu = 0; uu < 8; ++uu) acc[uu] = fmaf(cy, px[uu * ustride], acc[uu]);
-                        }
+                        if (d1 == 1) tc_cg<1>(xrow, yrow, t0, t1, acc);
+                        else if (d1 == 3) tc_cg<3>(xrow, yrow, t0, t1, acc);
+                        else if (d1 == 5) tc_cg<5>(xrow, yrow, t0, t1, acc);
+                        else tc_cg<7>(xrow, yrow, t0, t1, acc);
                     } else {
-                        // mode 2: the A operand is component k of the cotangent's block itself, A[b][w] = g[b, o][w, k]
+                        // mode 2: the A operand is component k of the cotangent's block itself, A[b][w] = g[b, o][w, k].  The values
+                        // were requested one step ahead (gnext); now request those of the next step: the next component of this
+                        // path, or component 0 of the next path.
                         const long long b0 = item0 + brow;
-                        const float* g0 = p.g + (b0 < p.batch ? b0 : 0) * L3_DIM + zoff + ucol * d3 + k;
+                        const bool live = b0 < p.batch;
+                        const float* grow = p.g + (live ? b0 : 0) * L3_DIM;
+                        if (q == 0 && k == 0) {
 #pragma unroll
-                        for (int uu = 0; uu < 8; ++uu) acc[uu] = (b0 < p.batch) ? __ldg(g0 + uu * 4 * d3) : 0.f;
+                            for (int uu = 0; uu < 8; ++uu) gnext[uu] = live ? __ldg(grow + zoff + (ucol + 4 * uu) * d3) : 0.f;
+                        }
+#pragma unroll
+                        for (int uu = 0; uu < 8; ++uu) acc[uu] = gnext[uu];
+                        const bool more = k + 1 < d3;
+                        if (more || q + 1 < NINS) {
+                            const int nd3 = more ? d3 : TC_D3[q + 1];
+                            const float* gn = grow + (more ? zoff + k + 1 : TC_ZOFF[q + 1]) + ucol * nd3;
+#pragma unroll
+                            for (int uu = 0; uu < 8; ++uu) gnext[uu] = live ? __ldg(gn + uu * 4 * nd3) : 0.f;
+                        }
                     }
                     // the operand buffer was last read by the MMAs of step - 2 (a commit covers every MMA issued before it)
                     if (!dead && step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 31)) dead = true;
@@ -320,7 +370,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                             const int off = tc_elem(brow, ucol + 4 * uu);
                             const float h = tc_tf32(acc[uu]);
                             sh.a[buf][0][off] = h;
-                            sh.a[buf][1][off] = tc_tf32(acc[uu] - h);
+                            sh.a[buf][1][off] = acc[uu] - h;   // the tensor core reads the top 19 bits: truncation of the low part is below 2^-21
                         }
                         tc_fence_async_smem();
                         tc_fence_before();
@@ -416,9 +466,27 @@ struct __align__(128) TcDwShared {
     float ys[TCW_TILE * TCW_YS];      // harmonics of the tile's items
     unsigned long long a_full[2];
     unsigned long long mma_done[2];
+    unsigned long long xs_full;       // the staged input blocks have arrived (bytes of the bulk copies)
     unsigned tmem_base;
     int abort_flag;
 };
+// Clebsch-Gordan stage of one step for one thread (two items, four channels each); D1 at compile time makes the offsets
+// in the staged rows immediates.
+template <int D1>
+OEQ_DEV void tcw_cg(const float* xt, const float* yb, int t0, int t1, float (&acc)[4][2]) {
+    constexpr int XS = 32 * D1 + 8;
+    for (int t = t0; t < t1; ++t) {
+        const float c = TCW_TC[t];
+        const float* py = yb + TCW_TJ[t];
+        const float* px = xt + TCW_TI[t];
+        const float cy0 = c * py[0], cy1 = c * py[4 * TCW_YS];
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+            acc[uu][0] = fmaf(cy0, px[8 * uu * D1], acc[uu][0]);
+            acc[uu][1] = fmaf(cy1, px[4 * XS + 8 * uu * D1], acc[uu][1]);
+        }
+    }
+}
 static_assert(sizeof(TcDwShared) > 116 * 1024 && sizeof(TcDwShared) <= 232448, "one CTA per SM is assumed (it owns all of TMEM)");
 static_assert(TCW_NGRP * 32 <= 512, "one 32-column accumulator per group of paths");
 
@@ -430,6 +498,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
     if (tid == 0) {
         tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
         tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
+        tc_mbar_init(&sh.xs_full, 1);
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -480,6 +549,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
         }
     } else {
         const int slot = warp & 3, sub = warp >> 2, r8 = lane >> 2, b4 = lane & 3;
+        unsigned nstage = 0;   // staged groups so far (phase of xs_full)
         for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             const long long item0 = tile * TCW_TILE;
             const long long nlive = p.batch - item0;         // items of the tile that exist
@@ -489,21 +559,23 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                     sh.ys[r * TCW_YS + j] = (r < nlive) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
             for (int grp = 0; grp < TCW_NGRP; ++grp) {
                 const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp], ns = TCW_NS[grp];
-                // stage the slots' input blocks: warp w copies rows w, w + 16, ... (rows past the batch are zero)
+                // stage the slots' input blocks: one bulk copy per (slot, row), issued by the first 64 * ns threads; everybody
+                // waits for the bytes.  Rows past the end of the batch read row 0 and meet y = 0.
                 tc_compute_sync();   // readers of the previous group's blocks are done
                 if (!dead) {
-                    for (int sl = 0; sl < ns; ++sl) {
-                        const int q = grp * 4 + sl, chunks = 8 * TCW_D1[q], xs_stride = 4 * chunks + 8;
-                        for (int r = warp; r < TCW_TILE; r += TC_CW) {
-                            const bool live = r < nlive;
-                            const float* src = p.x + (live ? item0 + r : 0) * L1_DIM + TCW_XOFF[q];
-                            float* dst = sh.xs + TCW_XSOFF[q] + r * xs_stride;
-                            for (int c = lane; c < chunks; c += 32) tc_cp16(dst + 4 * c, src + 4 * c, live);
-                        }
+                    if (tid == 0) {
+                        int sumd1 = 0;
+                        for (int sl = 0; sl < ns; ++sl) sumd1 += TCW_D1[grp * 4 + sl];
+                        tc_mbar_expect_tx(&sh.xs_full, 64u * 128u * (unsigned)sumd1);
                     }
-                    tc_cp_wait_all();
+                    if (tid < 64 * ns) {
+                        const int sl = tid >> 6, r = tid & 63, qs = grp * 4 + sl, ds = TCW_D1[qs];
+                        tc_bulk_row(sh.xs + TCW_XSOFF[qs] + r * (32 * ds + 8),
+                                    p.x + (r < nlive ? item0 + r : 0) * L1_DIM + TCW_XOFF[qs], 128u * (unsigned)ds, &sh.xs_full);
+                    }
+                    if (!tc_mbar_wait(&sh.xs_full, nstage & 1u, abortf, p.status, 38)) dead = true;
+                    ++nstage;
                 }
-                tc_compute_sync();
                 const int q = grp * 4 + slot;
                 const int d1 = TCW_D1[q], xs_stride = 32 * d1 + 8;
                 for (int kh = 0; kh < 2 * d3; ++kh) {
@@ -517,17 +589,11 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                     for (int uu = 0; uu < 4; ++uu) { acc[uu][0] = 0.f; acc[uu][1] = 0.f; }
                     const float* xt = sh.xs + TCW_XSOFF[q] + ib * xs_stride + r8 * d1;
                     const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
-                    for (int t = t0; t < t1; ++t) {
-                        const float c = TCW_TC[t];
-                        const float* py = sh.ys + ib * TCW_YS + TCW_TJ[t];
-                        const float* px = xt + TCW_TI[t];
-                        const float cy0 = c * py[0], cy1 = c * py[4 * TCW_YS];
-#pragma unroll
-                        for (int uu = 0; uu < 4; ++uu) {
-                            acc[uu][0] = fmaf(cy0, px[8 * uu * d1], acc[uu][0]);
-                            acc[uu][1] = fmaf(cy1, px[4 * xs_stride + 8 * uu * d1], acc[uu][1]);
-                        }
-                    }
+                    const float* yb = sh.ys + ib * TCW_YS;
+                    if (d1 == 1) tcw_cg<1>(xt, yb, t0, t1, acc);
+                    else if (d1 == 3) tcw_cg<3>(xt, yb, t0, t1, acc);
+                    else if (d1 == 5) tcw_cg<5>(xt, yb, t0, t1, acc);
+                    else tcw_cg<7>(xt, yb, t0, t1, acc);
                     // this thread's 2 entries of B: row w = r8 + 8 * slot, the same two items
                     float gv[2];
 #pragma unroll
@@ -544,7 +610,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                                 const int off = tc_elem(slot * 32 + r8 + 8 * uu, ic + 4 * bb);
                                 const float v = acc[uu][bb], hi = tc_tf32(v);
                                 sh.a[buf][0][off] = hi;
-                                sh.a[buf][1][off] = tc_tf32(v - hi);
+                                sh.a[buf][1][off] = v - hi;   // truncated by the tensor core: below 2^-21
                             }
 #pragma unroll
                         for (int bb = 0; bb < 2; ++bb) {
