@@ -232,6 +232,28 @@ OEQB_API int oeqb_emit_source(const void* desc, size_t desc_len, const char* kin
  * constructors (tensorproducts.hpp:32-46, convolution.hpp:36-56). */
 OEQB_API int oeqb_precompile(const void* desc, size_t desc_len, int64_t key);
 
+/* Planning for the partitioned / streamed convolution drivers, on the device (csrc/partition_plan.cuh).  From a globally
+ * (row, col)-sorted int64 edge list: what the holder of receivers [recv_begin, recv_end), who owns the rows
+ * [own_begin, own_end) as senders (may be empty), needs.  `bounds` [world + 1] are the owners' node ranges (NULL = one
+ * owner).  No reference counterpart: the reference has no multi-GPU path.
+ *
+ * oeqb_plan_count leaves in `counts` (device, int64 [8 + 2 world]): [0] e0, [1] e1 (edges into the receivers), [2] number
+ * of halo senders (senders of those edges outside the owned range), [3] a, [4] b (longest middle run of receivers without a
+ * halo sender, relative to recv_begin), [5] ea, [6] eb (its edges, relative to e0), [8 + q] halo senders owned by q,
+ * [8 + world + q] owned nodes that owner q's receivers read.  The caller reads them back (the one synchronisation),
+ * allocates, and calls oeqb_plan_fill with the same arguments and workspace: halo_ids [n_halo] ascending, send_ids
+ * (concatenated by owner, local numbering, ascending), rows_local / cols_local [e1 - e0] (owned senders first, halo senders
+ * after them in halo order) and perm_local (the sender-major order of the local list).  Any output pointer may be NULL
+ * when its size is zero. */
+OEQB_API int64_t oeqb_plan_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t n_receivers, int64_t n_owned, int32_t world);
+OEQB_API int oeqb_plan_count(int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols, int64_t recv_begin,
+                             int64_t recv_end, int64_t own_begin, int64_t own_end, int32_t world, int32_t rank,
+                             const int64_t* bounds, void* workspace, int64_t workspace_bytes, int64_t* counts, void* stream);
+OEQB_API int oeqb_plan_fill(int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols, int64_t recv_begin,
+                            int64_t recv_end, int64_t own_begin, int64_t own_end, int32_t world, const int64_t* bounds,
+                            int64_t e0, int64_t e1, int64_t n_halo, void* workspace, int64_t workspace_bytes, void* halo_ids,
+                            void* send_ids, void* rows_local, void* cols_local, void* perm_local, void* stream);
+
 /* String options: "cache_dir" (cubin cache directory), "log" ("0"/"1"), "validate" ("0"/"1"/"2": index checks), and the
  * tuning aids "force_generic", "single_group", "single_producer", "no_tc", "tc_backward" ("0".."7"), "streams",
  * "streams_forward".  Unknown names are refused with OEQB_EINVAL. */

@@ -33,7 +33,8 @@
 
 #include "../../include/oeq_b200.h"
 #include "kernels_embed.inc"  // generated at build time: K_COMMON, K_GENERIC, K_FAST_UVU as raw strings
-#include "graph_prep.cuh"     // problem-independent kernels: grouping / sorting of edge lists
+#include "graph_prep.cuh"         // problem-independent kernels: grouping / sorting of edge lists
+#include "partition_plan.cuh"     // ... and the plans of the partitioned / streamed drivers
 #include "group_mm.cuh"       // problem-independent kernels: ragged grouped products of the symmetric contraction
 
 namespace {
@@ -1908,6 +1909,68 @@ int oeqb_prepare_graph(int idx_dtype, int64_t n_nodes, int64_t n_edges, const vo
     }
     g_launches.fetch_add(launches, std::memory_order_relaxed);
     if (!ok) return fail(OEQB_ECUDA, "oeqb_prepare_graph: kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return OEQB_OK;
+}
+
+namespace {
+int plan_bounds(const char* who, int32_t world, const int64_t* bounds, int64_t n_nodes, pplan::Bounds* B) {
+    if (world < 1 || world > pplan::MAX_WORLD) return fail(OEQB_EINVAL, "%s: world must be 1 ... %d", who, pplan::MAX_WORLD);
+    B->world = world;
+    for (int q = 0; q <= world; ++q) {
+        B->b[q] = bounds ? bounds[q] : (q == 0 ? 0 : n_nodes);
+        if (B->b[q] < 0 || B->b[q] > n_nodes || (q > 0 && B->b[q] < B->b[q - 1])) return fail(OEQB_EINVAL, "%s: bounds must ascend within [0, n_nodes]", who);
+    }
+    return OEQB_OK;
+}
+}  // namespace
+
+int64_t oeqb_plan_workspace_bytes(int64_t n_nodes, int64_t n_edges, int64_t n_receivers, int64_t n_owned, int32_t world) {
+    if (n_nodes < 0 || n_edges < 0 || n_receivers < 0 || n_owned < 0 || world < 1) return -(int64_t)fail(OEQB_EINVAL, "oeqb_plan_workspace_bytes: bad argument");
+    return (int64_t)pplan::layout(n_nodes, n_edges, n_receivers, n_owned, world).total;
+}
+
+int oeqb_plan_count(int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols, int64_t recv_begin, int64_t recv_end,
+                    int64_t own_begin, int64_t own_end, int32_t world, int32_t rank, const int64_t* bounds, void* workspace,
+                    int64_t workspace_bytes, int64_t* counts, void* stream) {
+    pplan::Bounds B;
+    if (int rc = plan_bounds("oeqb_plan_count", world, bounds, n_nodes, &B)) return rc;
+    if (n_nodes < 0 || n_edges < 0 || recv_begin < 0 || recv_end < recv_begin || recv_end > n_nodes || own_begin < 0 || own_end < own_begin ||
+        own_end > n_nodes || rank < 0 || rank >= world)
+        return fail(OEQB_EINVAL, "oeqb_plan_count: bad range");
+    if (int rc = check_ptrs({workspace, counts}, "oeqb_plan_count")) return rc;
+    if (n_edges > 0) if (int rc = check_ptrs({rows, cols}, "oeqb_plan_count")) return rc;
+    const size_t need = pplan::layout(n_nodes, n_edges, recv_end - recv_begin, own_end - own_begin, world).total;
+    if (workspace_bytes < (int64_t)need || ((uintptr_t)workspace & 15u))
+        return fail(OEQB_EINVAL, "oeqb_plan_count: workspace of %lld bytes is smaller than the %zu required (or not 16-byte aligned)",
+                    (long long)workspace_bytes, need);
+    long long launches = 0;
+    const bool ok = pplan::count((const long long*)rows, (const long long*)cols, n_nodes, n_edges, recv_begin, recv_end, own_begin, own_end, B,
+                                 rank, workspace, (long long*)counts, (cudaStream_t)stream, &launches);
+    g_launches.fetch_add(launches, std::memory_order_relaxed);
+    if (!ok) return fail(OEQB_ECUDA, "oeqb_plan_count: %s", cudaGetErrorString(cudaGetLastError()));
+    return OEQB_OK;
+}
+
+int oeqb_plan_fill(int64_t n_nodes, int64_t n_edges, const void* rows, const void* cols, int64_t recv_begin, int64_t recv_end,
+                   int64_t own_begin, int64_t own_end, int32_t world, const int64_t* bounds, int64_t e0, int64_t e1, int64_t n_halo,
+                   void* workspace, int64_t workspace_bytes, void* halo_ids, void* send_ids, void* rows_local, void* cols_local,
+                   void* perm_local, void* stream) {
+    pplan::Bounds B;
+    if (int rc = plan_bounds("oeqb_plan_fill", world, bounds, n_nodes, &B)) return rc;
+    if (e0 < 0 || e1 < e0 || e1 > n_edges || n_halo < 0 || n_halo > n_nodes) return fail(OEQB_EINVAL, "oeqb_plan_fill: bad sizes");
+    if (int rc = check_ptrs({workspace}, "oeqb_plan_fill")) return rc;
+    if (e1 > e0) if (int rc = check_ptrs({rows, cols, rows_local, cols_local, perm_local}, "oeqb_plan_fill")) return rc;
+    const size_t need = pplan::layout(n_nodes, n_edges, recv_end - recv_begin, own_end - own_begin, world).total;
+    if (workspace_bytes < (int64_t)need) return fail(OEQB_EINVAL, "oeqb_plan_fill: workspace too small");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    long long launches = 0;
+    const bool ok = pplan::fill((const long long*)rows, (const long long*)cols, n_nodes, n_edges, recv_begin, recv_end, own_begin, own_end, B, e0,
+                                e1, n_halo, workspace, (long long*)halo_ids, (long long*)send_ids, (long long*)rows_local,
+                                (long long*)cols_local, (long long*)perm_local, status, (cudaStream_t)stream, &launches);
+    g_launches.fetch_add(launches, std::memory_order_relaxed);
+    if (!ok) return fail(OEQB_ECUDA, "oeqb_plan_fill: %s", cudaGetErrorString(cudaGetLastError()));
     return OEQB_OK;
 }
 

@@ -46,6 +46,10 @@ _PROTOTYPES = {
     "oeqb_slow_path_count": (c_int64, []),
     "oeqb_graph_workspace_bytes": (c_int64, [c_int64, c_int64]),
     "oeqb_prepare_graph": (c_int, [c_int, c_int64, c_int64] + [_P] * 7 + [c_int64, _P]),
+    "oeqb_plan_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int]),
+    "oeqb_plan_count": (c_int, [c_int64, c_int64, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int, c_int, _P, _P, c_int64, _P, _P]),
+    "oeqb_plan_fill": (c_int, [c_int64, c_int64, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P, c_int64, c_int64, c_int64,
+                               _P, c_int64, _P, _P, _P, _P, _P, _P]),
     "oeqb_emit_source": (c_int, [c_char_p, c_size_t, c_char_p, c_char_p, c_size_t, POINTER(c_size_t)]),
     "oeqb_precompile": (c_int, _DESC),
     "oeqb_set_option": (c_int, [c_char_p, c_char_p]),

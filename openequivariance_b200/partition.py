@@ -95,9 +95,56 @@ def _halo_of(rows, cols, n_nodes, world, q):
     return n0, n1, e0, e1, torch.unique(outside)
 
 
+def plan_on_device(rows: torch.Tensor, cols: torch.Tensor, n_nodes: int, recv: tuple, own: tuple, bounds: List[int], rank: int):
+    """The library's planning kernels (``oeqb_plan_count`` / ``oeqb_plan_fill``) for the holder of receivers ``recv`` who
+    owns the sender rows ``own`` (may be empty).  One host synchronisation (the sizes of the lists).  Returns a dict with
+    ``e0, e1, a, b, ea, eb, recv_counts, send_counts`` (Python ints / lists) and the tensors ``halo_ids, send_ids``
+    (concatenated by owner), ``rows_local, cols_local, perm_local``."""
+    import ctypes
+
+    from . import native
+    assert rows.is_cuda and rows.dtype == torch.int64 and cols.dtype == torch.int64
+    lib, dev = native.load(), rows.device
+    rows, cols = rows.contiguous(), cols.contiguous()
+    E, world = int(rows.numel()), len(bounds) - 1
+    args = (n_nodes, E, ctypes.c_void_p(rows.data_ptr()), ctypes.c_void_p(cols.data_ptr()), recv[0], recv[1], own[0], own[1], world)
+    barr = (ctypes.c_int64 * (world + 1))(*bounds)
+    with torch.cuda.device(dev):
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        need = int(lib.oeqb_plan_workspace_bytes(n_nodes, E, recv[1] - recv[0], own[1] - own[0], world))
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        counts = torch.empty(8 + 2 * world, dtype=torch.int64, device=dev)
+        native.check(lib.oeqb_plan_count(*args, rank, barr, ctypes.c_void_p(ws.data_ptr()), need, ctypes.c_void_p(counts.data_ptr()), st),
+                     "oeqb_plan_count")
+        c = counts.tolist()                                   # the one synchronisation
+        e0, e1, n_halo = c[0], c[1], c[2]
+        send_counts = c[8 + world:8 + 2 * world]
+        i64 = dict(dtype=torch.int64, device=dev)
+        halo = torch.empty(n_halo, **i64)
+        send = torch.empty(sum(send_counts), **i64)
+        rl, cl, pl = (torch.empty(e1 - e0, **i64) for _ in range(3))
+        p = lambda t: ctypes.c_void_p(t.data_ptr() if t.numel() else 0)
+        native.check(lib.oeqb_plan_fill(*args, barr, e0, e1, n_halo, ctypes.c_void_p(ws.data_ptr()), need, p(halo), p(send), p(rl), p(cl),
+                                        p(pl), st), "oeqb_plan_fill")
+    return dict(e0=e0, e1=e1, a=c[3], b=c[4], ea=c[5], eb=c[6], recv_counts=c[8:8 + world], send_counts=send_counts, halo_ids=halo,
+                send_ids=send, rows_local=rl, cols_local=cl, perm_local=pl)
+
+
 def build_plan(rows: torch.Tensor, cols: torch.Tensor, n_nodes: int, world: int, rank: int) -> PartitionPlan:
     """Pure index arithmetic on the global, (row, col)-sorted edge list; needs no communication because every rank
-    holds the same global ``rows`` / ``cols`` (built from the same seed or broadcast by the caller)."""
+    holds the same global ``rows`` / ``cols`` (built from the same seed or broadcast by the caller).  CUDA int64 lists are
+    planned by the library's kernels (one pass over the edges, one host synchronisation); CPU lists (host-side tests) by
+    the torch restatement below, which is also what the device plan is tested against."""
+    if rows.is_cuda and rows.dtype == torch.int64:
+        n0, n1 = owner_range(n_nodes, world, rank)
+        bounds = [owner_range(n_nodes, world, q)[0] for q in range(world)] + [n_nodes]
+        d = plan_on_device(rows, cols, n_nodes, (n0, n1), (n0, n1), bounds, rank)
+        send_ids = list(torch.split(d["send_ids"], d["send_counts"]))
+        rl, a, b, ea, eb = d["rows_local"], d["a"], d["b"], d["ea"], d["eb"]
+        return PartitionPlan(rank=rank, world=world, n_nodes=n_nodes, n0=n0, n1=n1, e0=d["e0"], e1=d["e1"], halo_ids=d["halo_ids"],
+                             recv_counts=d["recv_counts"], send_ids=send_ids, rows_local=rl, cols_local=d["cols_local"],
+                             perm_local=d["perm_local"], interior=(a, b), interior_edges=(ea, eb),
+                             rows_mid=(rl[ea:eb] - a).contiguous(), rows_right=(rl[eb:] - b).contiguous())
     n0, n1, e0, e1, halo = _halo_of(rows, cols, n_nodes, world, rank)
     dev = rows.device
     bounds = torch.tensor([owner_range(n_nodes, world, q)[0] for q in range(world)] + [n_nodes], device=dev)

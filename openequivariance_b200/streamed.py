@@ -46,6 +46,14 @@ def plan_chunks(rows: torch.Tensor, cols: torch.Tensor, n_receivers: int, chunk_
     assert chunk_nodes > 0
     plans = []
     bounds = list(range(0, n_receivers, chunk_nodes)) + [n_receivers]
+    if rows.is_cuda and rows.dtype == torch.int64 and cols.dtype == torch.int64:
+        # the library's planning kernels: per chunk one pass over the edges and one host synchronisation (the list sizes)
+        from .partition import plan_on_device
+        n_nodes = max(n_receivers, int(cols.max()) + 1 if cols.numel() else 0)
+        for n0, n1 in zip(bounds[:-1], bounds[1:]):
+            d = plan_on_device(rows, cols, n_nodes, (n0, n1), (0, 0), [0, n_nodes], 0)
+            plans.append(ChunkPlan(n0, n1, d["e0"], d["e1"], d["halo_ids"], d["rows_local"], d["cols_local"], d["perm_local"]))
+        return plans
     cuts = torch.searchsorted(rows, torch.tensor(bounds, device=rows.device, dtype=rows.dtype)).tolist()
     for (n0, n1), (e0, e1) in zip(zip(bounds[:-1], bounds[1:]), zip(cuts[:-1], cuts[1:])):
         c = cols[e0:e1]
