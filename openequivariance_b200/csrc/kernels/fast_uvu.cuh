@@ -474,6 +474,15 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
     T acc[FAST_CH * FAST_GPC];
 #pragma unroll
     for (int k = 0; k < FAST_CH * FAST_GPC; ++k) acc[k] = T(0);
+#if OEQ_KAHAN
+    // Compensated summation over a receiver's edges (the reference's Kahan option of the deterministic convolution:
+    // templates/loop_unroll_conv_det.cuh): the edge's message for one output block at a time is formed in msg and added
+    // to (acc, comp).  One channel per thread (the wide configuration), so sum and compensation fit the registers.
+    static_assert(FAST_CH == 1 && !FAST_FWD3, "compensated summation runs on the one-channel first-order kernels");
+    T comp[FAST_GPC];
+#pragma unroll
+    for (int k = 0; k < FAST_GPC; ++k) comp[k] = T(0);
+#endif
     long long next_row = sh.range[2];
     long long nseg = 0;                                // receiver rows this CTA has handed to the bulk reduce
     auto zero_rows = [&](long long a, long long b) {   // receivers without edges
@@ -490,8 +499,40 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
         if (!fast_consumer_fold(sh, st, tab, s, par, tid, abortf, p.status)) return;
         const long long row = st.row;
         const int last = st.last;
-        // Paths are taken input block by input block, so that only one block of the sender row is in registers at a time.
         const T4* cy4 = reinterpret_cast<const T4*>(st.cy);
+#if OEQ_KAHAN
+        // Paths are taken output block by output block: the block's message of this edge is complete before it is added.
+        static_for<0, NB3>([&](auto oc) {
+            constexpr int O = decltype(oc)::value;
+            using B3 = Blk3<O>;
+            if constexpr (FP_Z_OWNER[O] == GRP) {
+                T msg[B3::D];
+#pragma unroll
+                for (int k = 0; k < B3::D; ++k) msg[k] = T(0);
+                static_for<0, NINS>([&](auto ic) {
+                    constexpr int I = decltype(ic)::value;
+                    using F = FIns<I>;
+                    if constexpr (F::OB == O) {
+                        using B1 = Blk1<F::A>;
+                        T xb[B1::D], wv[1];
+                        block_load<B1>(st.x, u, xb);
+                        weight_load<F::WOFF>(st.w, u, wv);
+                        F::fwd(xb, cy4, wv, msg);
+                    }
+                });
+#pragma unroll
+                for (int k = 0; k < B3::D; ++k) {
+                    T& a = acc[B3::OFF / FU + k];
+                    T& c = comp[B3::OFF / FU + k];
+                    const T yk = msg[k] - c;
+                    const T tk = a + yk;
+                    c = (tk - a) - yk;
+                    a = tk;
+                }
+            }
+        });
+#else
+        // Paths are taken input block by input block, so that only one block of the sender row is in registers at a time.
         static_for<0, NB1>([&](auto bc) {
             constexpr int B = decltype(bc)::value;
             using B1 = Blk1<B>;
@@ -529,6 +570,7 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                 });
             }
         });
+#endif
         mbar_arrive(&sh.empty[s]);
         if (last && KIND == FAST_ATOMIC) {
             // The row is added to Z[row] by one bulk reduce (cp.reduce.async.bulk) out of shared memory: far fewer
@@ -579,6 +621,10 @@ OEQ_DEV void fast_forward_group(const FastParams& p, FastShared& sh, const int t
                     for (int ch = 0; ch < FAST_CH; ++ch)
 #pragma unroll
                         for (int k = 0; k < B3::D; ++k) acc[ch * FAST_GPC + B3::OFF / FU + k] = T(0);
+#if OEQ_KAHAN
+#pragma unroll
+                    for (int k = 0; k < B3::D; ++k) comp[B3::OFF / FU + k] = T(0);
+#endif
                 }
             });
         }
@@ -805,10 +851,24 @@ extern "C" __global__ void __launch_bounds__(256) oeq_fixup_backward_reduce(cons
             Piece acc;
 #pragma unroll
             for (int t = 0; t < VE; ++t) acc.v[t] = T(0);
+#if OEQ_KAHAN
+            Piece comp;   // compensated summation over the sender's edges
+#pragma unroll
+            for (int t = 0; t < VE; ++t) comp.v[t] = T(0);
+#endif
             auto add = [&](const float4& raw) {
                 const Piece& pc = reinterpret_cast<const Piece&>(raw);
 #pragma unroll
-                for (int t = 0; t < VE; ++t) acc.v[t] += pc.v[t];
+                for (int t = 0; t < VE; ++t) {
+#if OEQ_KAHAN
+                    const T yk = pc.v[t] - comp.v[t];
+                    const T tk = acc.v[t] + yk;
+                    comp.v[t] = (tk - acc.v[t]) - yk;
+                    acc.v[t] = tk;
+#else
+                    acc.v[t] += pc.v[t];
+#endif
+                }
             };
             long long k = k0;
             for (; k + 4 <= k1; k += 4) {

@@ -179,12 +179,14 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     if (d.dim[0] * 1LL > (1LL << 24) || d.dim[2] > (1LL << 24) || d.wn > (1LL << 30)) return bad("problem too large");
 
     // Fast path: fp32 or fp64, either layout, uvu, per-item weights, every in2 multiplicity 1, one common in1 multiplicity
-    // that is a multiple of 32, l <= 4 everywhere, no Kahan, rows small enough to live in registers.
+    // that is a multiple of 32, l <= 4 everywhere, rows small enough to live in registers; Kahan summation for the
+    // deterministic convolution only (the only place the reference offers it).
     // fp64 takes the "wide" configuration: one channel per thread in two block-owning thread groups (forward and
     // backward), so that half a gradient row of doubles fits a thread's registers, and one CTA per SM for the doubled stages.
     d.fast = false;
-    if ((d.dtype == 1 || d.dtype == 2) && !d.uvw && !d.shared && !d.kahan && !d.L[0].empty()) {
-        const bool wide = d.dtype == 2;
+    if ((d.dtype == 1 || d.dtype == 2) && !d.uvw && !d.shared && (!d.kahan || (d.conv && d.det && d.dtype == 1)) && !d.L[0].empty()) {
+        // compensated summation also takes the wide configuration: sum and compensation of half a row per thread
+        const bool wide = d.dtype == 2 || d.kahan;
         bool ok = true;
         int U = d.L[0][0].mul;
         for (auto& b : d.L[0]) ok = ok && b.mul == U && b.l <= 4;
@@ -388,7 +390,7 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
         const int D1 = A.d(), D3 = O.d(), np = (int)P.size(), nq = (np + 3) / 4;
         auto C = [&](int z) { std::ostringstream t; t << "c" << (z / 4) << "." << comp[z % 4]; return t.str(); };
         s << "template <> struct FIns<" << n << "> {\n";
-        s << "  static constexpr int A = " << I.a << ", XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
+        s << "  static constexpr int A = " << I.a << ", OB = " << I.o << ", XO = " << A.off / d.fast_U << ", GO = " << O.off / d.fast_U << ", Y0 = " << B.off
           << ", CY4 = " << cyoff[n] / 4 << ", WOFF = " << I.woff << ", D1 = " << D1 << ", D3 = " << D3 << ";\n";
         // ---- forward: FAST_CH channels per thread share the coefficient loads
         s << "  static OEQ_DEV void fwd(const T* x, const T4* cy, const T* w, T* acc) {\n";

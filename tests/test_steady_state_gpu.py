@@ -58,15 +58,15 @@ def _second_order(conv, X, Y, W, G, X2, Y2, W2, rows, cols, perm):
 
 
 @pytest.mark.parametrize("name,mode", [("mace_like", "deterministic"), ("mace_like", "atomic"),
-                                       ("mace_medium", "deterministic")])
+                                       ("mace_medium", "deterministic"), ("mace_like", "kahan")])
 def test_first_order_at_steady_state(name, mode):
     import openequivariance_b200 as oeq
     from openequivariance_b200 import native
     problem, X, Y, W, G, rows, cols, perm = _workload(name, N_NODES, 21, shuffle=mode == "atomic")
-    conv = oeq.TensorProductConv(problem, deterministic=mode == "deterministic")
+    conv = oeq.TensorProductConv(problem, deterministic=mode != "atomic", kahan=mode == "kahan")
     assert native.query(conv.kernel_string.encode(), conv.hash).fast_path == 1
     fast = _first_order(conv, X, Y, W, G, rows, cols, perm)
-    if mode == "deterministic":     # and reproducible at this size too
+    if mode != "atomic":     # and reproducible at this size too
         again = _first_order(conv, X, Y, W, G, rows, cols, perm)
         for k in fast:
             assert torch.equal(fast[k], again[k]), k
