@@ -236,7 +236,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
         const unsigned long long db0h = tc_desc(&sh.b[0][0][0], TC_LBO, TC_SBO), db0l = tc_desc(&sh.b[0][1][0], TC_LBO, TC_SBO);
         const unsigned long long db1h = tc_desc(&sh.b[1][0][0], TC_LBO, TC_SBO), db1l = tc_desc(&sh.b[1][1][0], TC_LBO, TC_SBO);
         for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
-            for (int q = 0; q < NINS && !dead; ++q) {
+            for (int q = 0; q < TC_NPATH && !dead; ++q) {
                 const int d3 = TC_D3[q], first = TC_FIRST[q], last = TC_LAST[q];
                 for (int k = 0; k < d3 && !dead; ++k) {
                     const unsigned buf = step & 1u;
@@ -281,8 +281,9 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
             } else {
                 for (int j = 0; j < TC_DYS; ++j) sh.dys[tid * TC_DYS + j] = 0.f;   // read and written by this thread only
             }
-            for (int q = 0; q < NINS; ++q) {
+            for (int q = 0; q < TC_NPATH; ++q) {
                 const int d1 = TC_D1[q], d3 = TC_D3[q], xoff = TC_XOFF[q], zoff = TC_ZOFF[q], woff = TC_WOFF[q];
+                const int tq = TC_INS[q] * 8;   // this path's instruction: start of its term ranges
                 const int last = TC_LAST[q];
                 // stage the path's input block by asynchronous row copies; the block stays when the previous path of this
                 // tile read the same one
@@ -323,7 +324,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                     for (int uu = 0; uu < 8; ++uu) acc[uu] = 0.f;
                     if (TC_MODE != 2) {
                         // Clebsch-Gordan stage for component k, term by term
-                        const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
+                        const int t0 = TC_KBEG[tq + k], t1 = TC_KBEG[tq + k + 1];
                         if (d1 == 1) tc_cg<1>(xrow, yrow, t0, t1, acc);
                         else if (d1 == 3) tc_cg<3>(xrow, yrow, t0, t1, acc);
                         else if (d1 == 5) tc_cg<5>(xrow, yrow, t0, t1, acc);
@@ -342,7 +343,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
 #pragma unroll
                         for (int uu = 0; uu < 8; ++uu) acc[uu] = gnext[uu];
                         const bool more = k + 1 < d3;
-                        if (more || q + 1 < NINS) {
+                        if (more || q + 1 < TC_NPATH) {
                             const int nd3 = more ? d3 : TC_D3[q + 1];
                             const float* gn = grow + (more ? zoff + k + 1 : TC_ZOFF[q + 1]) + ucol * nd3;
 #pragma unroll
@@ -401,7 +402,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                             for (int k = 0; k < d3; ++k) {
                                 unsigned r[8];
                                 tc_ld8(tbase + 32u * (unsigned)k, r);
-                                const int t0 = TC_KBEG[q * 8 + k], t1 = TC_KBEG[q * 8 + k + 1];
+                                const int t0 = TC_KBEG[tq + k], t1 = TC_KBEG[tq + k + 1];
                                 for (int t = t0; t < t1; ++t) {
                                     const float* px = xb + TC_TI[t];
                                     float dot = 0.f;
@@ -455,6 +456,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
 struct TcDwParams {
     const float* x; const float* y; const float* g; float* part;
     long long batch;
+    int grp_begin, grp_end;   // this launch's groups (at most 16: one 32-column accumulator each)
     int* status;
 };
 constexpr int TCW_TILE = 64;
@@ -488,7 +490,6 @@ OEQ_DEV void tcw_cg(const float* xt, const float* yb, int t0, int t1, float (&ac
     }
 }
 static_assert(sizeof(TcDwShared) > 116 * 1024 && sizeof(TcDwShared) <= 232448, "one CTA per SM is assumed (it owns all of TMEM)");
-static_assert(TCW_NGRP * 32 <= 512, "one 32-column accumulator per group of paths");
 
 extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_dw(const TcDwParams p) {
     extern __shared__ __align__(128) unsigned char tc_smem_raw[];
@@ -522,14 +523,14 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
         const unsigned long long db1h = tc_desc(&sh.b[1][0][0], TC_LBO, TC_SBO), db1l = tc_desc(&sh.b[1][1][0], TC_LBO, TC_SBO);
         for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
             const bool first_tile = tile == blockIdx.x;
-            for (int grp = 0; grp < TCW_NGRP && !dead; ++grp) {
+            for (int grp = p.grp_begin; grp < p.grp_end && !dead; ++grp) {
                 const int d3 = TCW_D3[grp];
                 for (int kh = 0; kh < 2 * d3 && !dead; ++kh) {   // (component k, half of the tile)
                     const unsigned buf = step & 1u;
                     if (!tc_mbar_wait(&sh.a_full[buf], (step >> 1) & 1u, abortf, p.status, 36)) { dead = true; break; }
                     tc_fence_after();
                     if (lane == 0) {
-                        const unsigned dcol = tmem + 32u * (unsigned)grp;
+                        const unsigned dcol = tmem + 32u * (unsigned)(grp - p.grp_begin);
                         const unsigned long long ah0 = buf ? da1h : da0h, al0 = buf ? da1l : da0l;
                         const unsigned long long bh0 = buf ? db1h : db0h, bl0 = buf ? db1l : db0l;
 #pragma unroll
@@ -557,7 +558,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
             for (int r = warp; r < TCW_TILE; r += TC_CW)
                 for (int j = lane; j < L2_DIM; j += 32)
                     sh.ys[r * TCW_YS + j] = (r < nlive) ? __ldg(p.y + (item0 + r) * L2_DIM + j) : 0.f;
-            for (int grp = 0; grp < TCW_NGRP; ++grp) {
+            for (int grp = p.grp_begin; grp < p.grp_end; ++grp) {
                 const int d3 = TCW_D3[grp], zoff = TCW_ZOFF[grp], ns = TCW_NS[grp];
                 // stage the slots' input blocks: one bulk copy per (slot, row), issued by the first 64 * ns threads; everybody
                 // waits for the bytes.  Rows past the end of the batch read row 0 and meet y = 0.
@@ -588,7 +589,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
 #pragma unroll
                     for (int uu = 0; uu < 4; ++uu) { acc[uu][0] = 0.f; acc[uu][1] = 0.f; }
                     const float* xt = sh.xs + TCW_XSOFF[q] + ib * xs_stride + r8 * d1;
-                    const int t0 = TCW_KBEG[q * 8 + k], t1 = TCW_KBEG[q * 8 + k + 1];
+                    const int tq = TCW_INS[q] < 0 ? 0 : TCW_INS[q] * 8;
+                    const int t0 = TCW_KBEG[tq + k], t1 = TCW_INS[q] < 0 ? t0 : TCW_KBEG[tq + k + 1];
                     const float* yb = sh.ys + ib * TCW_YS;
                     if (d1 == 1) tcw_cg<1>(xt, yb, t0, t1, acc);
                     else if (d1 == 3) tcw_cg<3>(xt, yb, t0, t1, acc);
@@ -632,10 +634,10 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
         if (!dead && step >= 1) {
             tc_fence_after();
             float* prow = p.part + (long long)blockIdx.x * WN;
-            for (int grp = 0; grp < TCW_NGRP; ++grp) {
+            for (int grp = p.grp_begin; grp < p.grp_end; ++grp) {
                 if (slot >= TCW_NS[grp]) continue;   // uniform in the warp
                 unsigned r[8];
-                tc_ld8(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)grp + (unsigned)(TC_EC * sub), r);
+                tc_ld8(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)(grp - p.grp_begin) + (unsigned)(TC_EC * sub), r);
                 float4* dst = reinterpret_cast<float4*>(prow + TCW_WOFF[grp * 4 + slot] + lane * 32 + TC_EC * sub);
                 dst[0] = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
                 dst[1] = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));

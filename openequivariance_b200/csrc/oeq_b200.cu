@@ -105,7 +105,8 @@ struct Desc {
     int fast_bwd_ng = 1; // thread groups of the backward kernels (2 in the fp64 configuration)
     size_t fast_smem = 0;
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
-    bool tc_bwd = false;     // ... and the tensor-core backward kernels (every input block is read by some path)
+    bool tc_bwd = false;     // ... and the tensor-core backward kernels
+    bool tc_zero_z = false, tc_zero_dx = false;   // some output / input block has no path: zero the result first
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
     int fast_S4 = 0;         // stages of the second-order kernels (their stage carries a second coefficient table)
@@ -244,26 +245,27 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
             }
         }
     }
-    // Tensor-core path for 'uvw': shared fp32 weights, every in1 / out multiplicity 32, in2 multiplicity 1, l <= 3.
+    // Tensor-core path for 'uvw': shared fp32 weights, every in1 / out multiplicity a multiple of 32 (up to 128: the weight
+    // blocks are walked in 32 x 32 tiles), in2 multiplicity 1, l <= 3.
     d.tc = false;
     d.tc_bwd = false;
     if (d.dtype == 1 && d.layout == 0 && d.uvw && d.shared && !d.L[0].empty()) {
         bool ok = d.dim[1] <= 16;
-        for (auto& b : d.L[0]) ok = ok && b.mul == 32 && b.l <= 3;
+        for (auto& b : d.L[0]) ok = ok && b.mul % 32 == 0 && b.mul <= 128 && b.l <= 3;
         for (auto& b : d.L[1]) ok = ok && b.mul == 1 && b.l <= 3;
-        for (auto& b : d.L[2]) ok = ok && b.mul == 32 && b.l <= 3;
-        // every output block must be written by at least one path (the kernel stores only blocks it accumulates)
-        std::vector<int> hit(d.L[2].size(), 0);
-        for (auto& I : d.ins) hit[I.o] += 1;
-        for (int h : hit) ok = ok && h;
+        for (auto& b : d.L[2]) ok = ok && b.mul % 32 == 0 && b.mul <= 128 && b.l <= 3;
+        // the kernels store only the blocks they accumulate: an output block without a path (or, for the gradient, an input
+        // block that no path reads) is zeroed by the host first
+        std::vector<int> hit(d.L[2].size(), 0), read(d.L[0].size(), 0);
+        for (auto& I : d.ins) { hit[I.o] = 1; read[I.a] = 1; }
+        d.tc_zero_z = d.tc_zero_dx = false;
+        for (int h : hit) d.tc_zero_z = d.tc_zero_z || !h;
+        for (int h : read) d.tc_zero_dx = d.tc_zero_dx || !h;
+        long long npath = 0;   // 32 x 32 weight tiles: the per-path tables live in constant memory
+        if (ok) for (auto& I : d.ins) npath += (long long)(d.L[0][I.a].mul / 32) * (d.L[2][I.o].mul / 32);
+        ok = ok && npath <= 1024 && !d.ins.empty();
         d.tc = ok;
-        // the backward kernels likewise store only the input blocks that some path reads
-        std::vector<int> read(d.L[0].size(), 0);
-        for (auto& I : d.ins) read[I.a] = 1;
         d.tc_bwd = ok;
-        for (int h : read) d.tc_bwd = d.tc_bwd && h;
-        // the weight-gradient kernel keeps one 32-column accumulator per group of paths into a block
-        if (d.tc_bwd) d.tc_bwd = tc_dw_groups(d, nullptr).size() <= 16;
         d.tc = d.tc && tc_smem_bytes(d, 0) <= 232448;
         d.tc_bwd = d.tc_bwd && d.tc && tc_smem_bytes(d, 1) <= 232448 && tc_smem_bytes(d, 2) <= 232448;
     }
@@ -537,6 +539,46 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
 //   mode 1, dx:       dx[b, a][u, i] = sum_p sum_w W_p[u, w] * (sum_{k,j} C[i,j,k] g[b, o][w, k] y[b][j])
 // The second is the first with the roles of the input and output blocks exchanged and the weight block transposed, so
 // the same kernel serves both from two sets of tables.
+// A path of the tensor-core kernels: one 32 x 32 tile of an instruction's weight block (multiplicities are multiples of
+// 32; the kernel weight order keeps such a tile contiguous: kernels/common.cuh::widx_uvw).
+struct TcSub { int ins, uc, wc; };
+std::vector<TcSub> tc_subpaths(const Desc& d) {
+    std::vector<TcSub> subs;
+    for (size_t n = 0; n < d.ins.size(); ++n)
+        for (int uc = 0; uc < d.L[0][d.ins[n].a].mul / 32; ++uc)
+            for (int wc = 0; wc < d.L[2][d.ins[n].o].mul / 32; ++wc) subs.push_back({(int)n, uc, wc});
+    return subs;
+}
+int tc_sub_woff(const Desc& d, const TcSub& t) { return d.ins[t.ins].woff + t.uc * 32 * d.L[2][d.ins[t.ins].o].mul + t.wc * 1024; }
+
+// Clebsch-Gordan terms of every instruction, by the component they produce: `by_i` = by component of the first input
+// (gradient of x), else by output component.  TC_KBEG[8 n + k] .. TC_KBEG[8 n + k + 1] are the terms of instruction n.
+void emit_tc_terms(std::ostringstream& s, const Desc& d, bool by_i, const char* prefix) {
+    std::vector<long long> kbeg, ti, tj;
+    std::vector<double> tcf;
+    for (auto& I : d.ins) {
+        const int dk = by_i ? d.L[0][I.a].d() : d.L[2][I.o].d();
+        for (int k = 0; k < 8; ++k) {
+            kbeg.push_back((long long)ti.size());
+            if (k < dk)
+                for (auto& z : I.nz)
+                    if ((by_i ? z.i : z.k) == k) { ti.push_back(by_i ? z.k : z.i); tj.push_back(d.L[1][I.b].off + z.j); tcf.push_back(z.c); }
+        }
+    }
+    kbeg.push_back((long long)ti.size());
+    auto ilist = [&](const char* name, const std::vector<long long>& v) {
+        s << "__constant__ int " << prefix << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
+        for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
+        if (v.empty()) s << "0";
+        s << "};\n";
+    };
+    ilist("KBEG", kbeg); ilist("TI", ti); ilist("TJ", tj);
+    s << "__constant__ float " << prefix << "TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
+    for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
+    if (tcf.empty()) s << "0";
+    s << "};\n";
+}
+
 std::string emit_tc_dw(const Desc& d);
 std::string emit_tc(const Desc& d, int mode = 0) {
     std::ostringstream s;
@@ -548,16 +590,19 @@ std::string emit_tc(const Desc& d, int mode = 0) {
     s << "#define TC_WT " << (mode != 0 ? 1 : 0) << "\n";
     s << "#define TC_KERNEL_NAME " << (dx ? "oeq_uvw_tc_backward_dx" : dy ? "oeq_uvw_tc_backward_dy" : "oeq_uvw_tc_forward") << "\n";
     s << "constexpr int TC_IN_DIM = " << (dx ? d.dim[2] : d.dim[0]) << ", TC_OUT_DIM = " << (dx ? d.dim[0] : d.dim[2]) << ";\n";
+    const std::vector<TcSub> subs = tc_subpaths(d);
     // mode 2 (dy) accumulates nowhere across paths: every path is its own group; the paths are ordered by the input
-    // block they stage
-    auto dst = [&](int q) { return dx ? d.ins[q].a : dy ? q : d.ins[q].o; };   // block the path accumulates into
-    auto src = [&](int q) { return dx ? d.ins[q].o : d.ins[q].a; };           // block the path stages
-    std::vector<int> order(d.ins.size());
+    // tile they stage
+    auto in_tile = [&](int q) { return d.ins[subs[q].ins].a * 64 + subs[q].uc; };
+    auto out_tile = [&](int q) { return d.ins[subs[q].ins].o * 64 + subs[q].wc; };
+    auto dst = [&](int q) { return dx ? in_tile(q) : dy ? q : out_tile(q); };   // tile the path accumulates into
+    auto src = [&](int q) { return dx ? out_tile(q) : in_tile(q); };           // tile the path stages
+    std::vector<int> order(subs.size());
     for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return dy ? src(a) < src(b) : dst(a) < dst(b); });
-    // Inside a destination block the order of the paths is free.  Paths that read the same block are put next to each
-    // other, and a group starts with the block the previous group ended with where it can: the kernel keeps the
-    // staged block when the next path reads the same one.
+    // Inside a destination tile the order of the paths is free.  Paths that read the same tile are put next to each
+    // other, and a group starts with the tile the previous group ended with where it can: the kernel keeps the
+    // staged tile when the next path reads the same one.
     for (size_t g0 = 0; g0 < order.size();) {
         size_t g1 = g0;
         while (g1 < order.size() && dst(order[g1]) == dst(order[g0])) ++g1;
@@ -568,7 +613,7 @@ std::string emit_tc(const Desc& d, int mode = 0) {
         }
         g0 = g1;
     }
-    std::vector<int> first(d.ins.size(), 0), last(d.ins.size(), 0);
+    std::vector<int> first(subs.size(), 0), last(subs.size(), 0);
     for (size_t q = 0; q < order.size(); ++q) {
         if (q == 0 || dst(order[q - 1]) != dst(order[q])) first[order[q]] = 1;
         if (q + 1 == order.size() || dst(order[q + 1]) != dst(order[q])) last[order[q]] = 1;
@@ -580,54 +625,49 @@ std::string emit_tc(const Desc& d, int mode = 0) {
         if (v.empty()) s << "0";
         s << "};\n";
     };
-    std::vector<long long> vd1, vd3, vx, vz, vw, vf, vl, kbeg, ti, tj;
-    std::vector<double> tcf;
+    std::vector<long long> vd1, vd3, vx, vz, vw, vf, vl, vi;
     int maxd1 = 1;
     for (size_t q = 0; q < order.size(); ++q) {
-        const Instr& I = d.ins[order[q]];
-        const Block &A = d.L[0][I.a], &B = d.L[1][I.b], &O = d.L[2][I.o];
+        const TcSub& t = subs[order[q]];
+        const Instr& I = d.ins[t.ins];
+        const Block &A = d.L[0][I.a], &O = d.L[2][I.o];
         const Block &S = dx ? O : A, &D = dx ? A : O;   // block read, block accumulated into
-        vd1.push_back(S.d()); vd3.push_back(D.d()); vx.push_back(S.off); vz.push_back(D.off); vw.push_back(I.woff);
-        vf.push_back(first[order[q]]); vl.push_back(last[order[q]]);
+        const int ts = dx ? t.wc : t.uc, td = dx ? t.uc : t.wc;
+        vd1.push_back(S.d()); vd3.push_back(D.d());
+        vx.push_back(S.off + ts * 32 * S.d()); vz.push_back(D.off + td * 32 * D.d()); vw.push_back(tc_sub_woff(d, t));
+        vf.push_back(first[order[q]]); vl.push_back(last[order[q]]); vi.push_back(t.ins);
         if (S.d() > maxd1) maxd1 = S.d();
-        for (int k = 0; k < 8; ++k) {
-            kbeg.push_back((long long)ti.size());
-            if (k < D.d())
-                for (auto& z : I.nz)
-                    if ((dx ? z.i : z.k) == k) { ti.push_back(dx ? z.k : z.i); tj.push_back(B.off + z.j); tcf.push_back(z.c); }
-        }
     }
-    kbeg.push_back((long long)ti.size());
-    s << "constexpr int TC_MAXD1 = " << maxd1 << ";\n";
+    s << "constexpr int TC_MAXD1 = " << maxd1 << ", TC_NPATH = " << order.size() << ";\n";
     ilist("TC_D1", vd1); ilist("TC_D3", vd3); ilist("TC_XOFF", vx); ilist("TC_ZOFF", vz); ilist("TC_WOFF", vw);
-    ilist("TC_FIRST", vf); ilist("TC_LAST", vl); ilist("TC_KBEG", kbeg); ilist("TC_TI", ti); ilist("TC_TJ", tj);
-    s << "__constant__ float TC_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
-    for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
-    if (tcf.empty()) s << "0";
-    s << "};\n";
+    ilist("TC_FIRST", vf); ilist("TC_LAST", vl); ilist("TC_INS", vi);
+    emit_tc_terms(s, d, dx, "TC_");
     return s.str();
 }
 
-// Groups of the tensor-core weight-gradient kernel: paths into the same output block, at most four per group and as many
-// as have room for their staged input blocks (64 rows of 32 d1 + 8 floats each) beside the operand buffers.
+// Groups of the tensor-core weight-gradient kernel: paths (32 x 32 weight tiles) into the same tile of an output block, at
+// most four per group and as many as have room for their staged input tiles (64 rows of 32 d1 + 8 floats each) beside
+// the operand buffers.  Entries index tc_subpaths(d).
 std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats) {
     const size_t fixed = 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 64 * (d.dim[1] | 1)) + 512;
     const size_t cap = (232448 - fixed) / 4 / 64;   // floats per staged row, summed over the slots
-    auto rowlen = [&](int q) { return (size_t)(32 * d.L[0][d.ins[q].a].d() + 8); };
+    const std::vector<TcSub> subs = tc_subpaths(d);
+    auto rowlen = [&](int q) { return (size_t)(32 * d.L[0][d.ins[subs[q].ins].a].d() + 8); };
     std::vector<std::vector<int>> groups;
     size_t most = 0;
-    for (size_t o = 0; o < d.L[2].size(); ++o) {
-        std::vector<int> cur;
-        size_t used = 0;
-        for (size_t q = 0; q < d.ins.size(); ++q)
-            if (d.ins[q].o == (int)o) {
-                if (!cur.empty() && (cur.size() == 4 || used + rowlen((int)q) > cap)) { groups.push_back(cur); cur.clear(); used = 0; }
-                cur.push_back((int)q);
-                used += rowlen((int)q);
-                most = std::max(most, used);
-            }
-        if (!cur.empty()) groups.push_back(cur);
-    }
+    for (size_t o = 0; o < d.L[2].size(); ++o)
+        for (int wc = 0; wc < d.L[2][o].mul / 32; ++wc) {
+            std::vector<int> cur;
+            size_t used = 0;
+            for (size_t q = 0; q < subs.size(); ++q)
+                if (d.ins[subs[q].ins].o == (int)o && subs[q].wc == wc) {
+                    if (!cur.empty() && (cur.size() == 4 || used + rowlen((int)q) > cap)) { groups.push_back(cur); cur.clear(); used = 0; }
+                    cur.push_back((int)q);
+                    used += rowlen((int)q);
+                    most = std::max(most, used);
+                }
+            if (!cur.empty()) groups.push_back(cur);
+        }
     if (xs_floats) *xs_floats = most * 64;
     return groups;
 }
@@ -637,52 +677,44 @@ size_t tc_dw_smem_bytes(const Desc& d) {
     return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 64 * (d.dim[1] | 1) + xs_floats) + 512;
 }
 
-// Tables for the tensor-core weight-gradient kernel: the paths of an output block in groups of up to four slots.
+// Tables for the tensor-core weight-gradient kernel: the paths of an output tile in groups of up to four slots.
 std::string emit_tc_dw(const Desc& d) {
     std::ostringstream s;
     s << "#define OEQ_TC 1\n#define TC_MODE 3\n#define TC_WT 0\n#define TC_KERNEL_NAME oeq_uvw_tc_unused\n";
     s << "constexpr int TC_IN_DIM = " << d.dim[0] << ", TC_OUT_DIM = " << d.dim[2] << ";\n";
     size_t xs_floats = 0;
     const std::vector<std::vector<int>> groups = tc_dw_groups(d, &xs_floats);
+    const std::vector<TcSub> subs = tc_subpaths(d);
     auto ilist = [&](const char* name, const std::vector<long long>& v) {
         s << "__constant__ int " << name << "[" << (v.empty() ? 1 : v.size()) << "] = {";
         for (size_t i = 0; i < v.size(); ++i) s << v[i] << (i + 1 < v.size() ? ", " : "");
         if (v.empty()) s << "0";
         s << "};\n";
     };
-    std::vector<long long> ns, gd3, gz, sd1, sx, sw, sxs, kbeg, ti, tj;
-    std::vector<double> tcf;
+    std::vector<long long> ns, gd3, gz, sd1, sx, sw, sxs, si;
     int maxd1 = 1;
     for (auto& grp : groups) {
-        const Block& O = d.L[2][d.ins[grp[0]].o];
-        ns.push_back((long long)grp.size()); gd3.push_back(O.d()); gz.push_back(O.off);
+        const TcSub& t0 = subs[grp[0]];
+        const Block& O = d.L[2][d.ins[t0.ins].o];
+        ns.push_back((long long)grp.size()); gd3.push_back(O.d()); gz.push_back(O.off + t0.wc * 32 * O.d());
         long long xsoff = 0;
         for (int slot = 0; slot < 4; ++slot) {
             const bool used = slot < (int)grp.size();
-            const Instr* I = used ? &d.ins[grp[slot]] : nullptr;
-            sd1.push_back(used ? d.L[0][I->a].d() : 1); sx.push_back(used ? d.L[0][I->a].off : 0); sw.push_back(used ? I->woff : 0);
+            const TcSub* t = used ? &subs[grp[slot]] : nullptr;
+            const Block* A = used ? &d.L[0][d.ins[t->ins].a] : nullptr;
+            sd1.push_back(used ? A->d() : 1); sx.push_back(used ? A->off + t->uc * 32 * A->d() : 0);
+            sw.push_back(used ? tc_sub_woff(d, *t) : 0); si.push_back(used ? t->ins : -1);
             sxs.push_back(used ? xsoff : 0);
-            if (used) xsoff += 64LL * (32 * d.L[0][I->a].d() + 8);
-            if (used) maxd1 = std::max(maxd1, d.L[0][I->a].d());
-            for (int k = 0; k < 8; ++k) {
-                kbeg.push_back((long long)ti.size());
-                if (used && k < O.d())
-                    for (auto& z : I->nz)
-                        if (z.k == k) { ti.push_back(z.i); tj.push_back(d.L[1][I->b].off + z.j); tcf.push_back(z.c); }
-            }
+            if (used) { xsoff += 64LL * (32 * A->d() + 8); maxd1 = std::max(maxd1, A->d()); }
         }
     }
-    kbeg.push_back((long long)ti.size());
-    s << "constexpr int TC_MAXD1 = " << maxd1 << ";\n";
+    s << "constexpr int TC_MAXD1 = " << maxd1 << ", TC_NPATH = 1;\n";
     s << "constexpr int TCW_NGRP = " << groups.size() << ";\n";
     s << "constexpr int TCW_XS_FLOATS = " << xs_floats << ";\n";
     ilist("TCW_XSOFF", sxs);
     ilist("TCW_NS", ns); ilist("TCW_D3", gd3); ilist("TCW_ZOFF", gz); ilist("TCW_D1", sd1); ilist("TCW_XOFF", sx);
-    ilist("TCW_WOFF", sw); ilist("TCW_KBEG", kbeg); ilist("TCW_TI", ti); ilist("TCW_TJ", tj);
-    s << "__constant__ float TCW_TC[" << (tcf.empty() ? 1 : tcf.size()) << "] = {";
-    for (size_t i = 0; i < tcf.size(); ++i) s << hexf(tcf[i]) << (i + 1 < tcf.size() ? ", " : "");
-    if (tcf.empty()) s << "0";
-    s << "};\n";
+    ilist("TCW_WOFF", sw); ilist("TCW_INS", si);
+    emit_tc_terms(s, d, false, "TCW_");
     return s.str();
 }
 
@@ -1219,6 +1251,7 @@ struct TcParams {
 struct TcDwParams {
     const void* x; const void* y; const void* g; void* part;
     long long batch;
+    int grp_begin, grp_end;
     int* status;
 };
 // sizeof(TcShared) in kernels/uvw_tc.cuh, rounded up: operand buffers + staged block + harmonics (+ the dy partials);
@@ -1237,6 +1270,8 @@ size_t tc_smem_bytes(const Desc& d, int mode) {
 int tc_forward(Entry* e, TcParams p, cudaStream_t st, int mode = 0) {
     static const char* names[3] = {"oeq_uvw_tc_forward", "oeq_uvw_tc_backward_dx", "oeq_uvw_tc_backward_dy"};
     int rc;
+    if (!p.accum && ((mode == 0 && e->d.tc_zero_z) || (mode == 1 && e->d.tc_zero_dx)))
+        CUDA_TRY(cudaMemsetAsync(p.z, 0, (size_t)p.batch * e->d.dim[mode == 0 ? 2 : 0] * sizeof(float), st));
     if ((rc = status_word(&p.status))) return rc;
     Program* prog;
     if ((rc = get_program(e, mode == 0 ? FAM_UVW_TC : FAM_UVW_TC_DX + (mode - 1), &prog))) return rc;
@@ -1270,7 +1305,7 @@ int keep_pool_memory() {
 int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* dW, long long batch, int accum, cudaStream_t st) {
     int rc;
     const Desc& d = e->d;
-    TcDwParams p{x, y, g, nullptr, batch, nullptr};
+    TcDwParams p{x, y, g, nullptr, batch, 0, 0, nullptr};
     if ((rc = status_word(&p.status))) return rc;
     Program *prog, *gen;
     if ((rc = get_program(e, FAM_UVW_TC_DW, &prog))) return rc;
@@ -1285,8 +1320,15 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
     void* part = nullptr;
     CUDA_TRY(cudaMallocAsync(&part, (size_t)grid * d.wn * sizeof(float), st));
     p.part = part;
-    void* args[] = {&p};
-    rc = launch(k, (unsigned)grid, 16 * 32 + 32, smem, args, st);   // TC_THREADS
+    // the accumulators of 16 groups fill the tensor memory: more groups take more launches (each writes its groups' part
+    // of every CTA's row)
+    const int ngrp = (int)tc_dw_groups(d, nullptr).size();
+    for (int g0 = 0; g0 < ngrp && !rc; g0 += 16) {
+        p.grp_begin = g0;
+        p.grp_end = std::min(ngrp, g0 + 16);
+        void* args[] = {&p};
+        rc = launch(k, (unsigned)grid, 16 * 32 + 32, smem, args, st);   // TC_THREADS
+    }
     if (!rc) {
         void* rargs[] = {&part, &grid, &dW, &accum};
         rc = launch(kr, (unsigned)((d.wn + 31) / 32), 256, 0, rargs, st);
