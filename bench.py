@@ -56,6 +56,7 @@ def parse_args():
     ap.add_argument("--strong-nodes", type=int, default=2_000_000,
                     help="size of the fixed graph of the strong_scaling object (split over the GPUs)")
     ap.add_argument("--no-strong", action="store_true", help="skip the strong_scaling object")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the tensor-product workloads beside the headline")
     ap.add_argument("--batch", type=int, default=0)
     return ap.parse_args()
 
@@ -230,6 +231,8 @@ def run_ours(args):
         gc.collect()
         torch.cuda.empty_cache()
         result["strong_scaling"] = strong_scaling_object(args, dev, rank, world)
+    if args.workload == "conv" and world == 1 and not args.no_secondary:
+        result["secondary"] = secondary_object(args, dev)
 
     if rank == 0:
         print(json.dumps(result), flush=True)
@@ -713,8 +716,9 @@ def bench_streamed(args, dev, rank, world):
     }
 
 
-def bench_tp(args):
-    """Secondary lines: batched tensor product, forward / backward / double backward, in items/s per pass."""
+def tp_passes(workload, batch, steps, warmup, dev):
+    """Batched tensor product of one secondary workload: forward / backward / double backward, CUDA events per pass with a
+    buffer larger than L2 written between iterations.  Returns (per-pass dict, batch, dtype name, launches, fast_path)."""
     import numpy as np
     import torch
     import openequivariance_b200 as oeq
@@ -722,8 +726,10 @@ def bench_tp(args):
     from openequivariance_b200.core import problems as P
     from openequivariance_b200.core.graph import spherical_harmonics
 
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    class _A:   # the names the body below reads
+        pass
+    args = _A()
+    args.workload, args.batch, args.steps, args.warmup = workload, batch, steps, warmup
     if args.workload == "tp_uvu":
         problem, B, lmax, dt = P.mace_like_problem(), args.batch or 200000, 3, torch.float32
     elif args.workload == "tp_uvw":
@@ -790,13 +796,37 @@ def bench_tp(args):
         torch.cuda.synchronize(dev)
         out[name] = {"ms": ms, "items_per_s": B / (ms * 1e-3), "algorithmic_gbs": gbs, "hbm_frac": gbs / peak,
                      "host_us_per_call": host_us}
+    return (out, B, "f64" if dt == torch.float64 else "f32", native.launch_count() - launches0,
+            int(native.query(tp.kernel_string.encode(), tp.hash).fast_path))
+
+
+def bench_tp(args):
+    """Secondary lines (``--workload tp_*``): batched tensor product in items/s per pass."""
+    import torch
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    out, B, dtype, launches, fast_path = tp_passes(args.workload, args.batch, args.steps, args.warmup, dev)
     line = {"metric": "tp_items_per_s", "value": out["forward"]["items_per_s"], "unit": "items/s", "n_gpus": 1,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": out["forward"]["ms"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64" if dt == torch.float64 else "f32",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype,
             "data": "synthetic", "config": {"workload": args.workload, "batch": B, "l2_policy": "256 MB buffer written between iterations"},
-            "passes": out, "gpu_launches": native.launch_count() - launches0,
-            "fast_path": int(native.query(tp.kernel_string.encode(), tp.hash).fast_path)}
+            "passes": out, "gpu_launches": launches, "fast_path": fast_path}
     print(json.dumps(line), flush=True)
+
+
+def secondary_object(args, dev):
+    """The batched tensor-product workloads beside the headline, in the same JSON line (ms per pass; same timing rules)."""
+    import gc
+
+    import torch
+    sec = {}
+    for workload in ("tp_uvu", "tp_uvw"):
+        gc.collect()
+        torch.cuda.empty_cache()
+        out, B, dtype, _, fast_path = tp_passes(workload, 0, min(args.steps, 5), args.warmup, dev)
+        sec[workload] = {"batch": B, "dtype": dtype, "fast_path": fast_path,
+                         **{name: round(v["ms"], 4) for name, v in out.items()}, "unit": "ms per pass"}
+    return sec
 
 
 def main():
