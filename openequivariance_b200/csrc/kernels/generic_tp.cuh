@@ -54,7 +54,9 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_forward(const FwdP
         static_for<0, NB3>([&](auto oc) {
             constexpr int O = decltype(oc)::value;
             using B3 = Blk3<O>;
-            for (int c = lane; c < B3::MUL; c += 32) {  // c: channel u (uvu) or w (uvw) of the output block
+            constexpr int MULPAD3 = (B3::MUL + 31) & ~31;   // every lane walks the loop: the 'uvw' branch shuffles
+            for (int c = lane; c < MULPAD3; c += 32) {  // c: channel u (uvu) or w (uvw) of the output block
+                const bool live = c < B3::MUL;
                 T acc[B3::D], comp[B3::D];
 #pragma unroll
                 for (int k = 0; k < B3::D; ++k) { acc[k] = T(0); comp[k] = T(0); }
@@ -74,7 +76,7 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_forward(const FwdP
 #if !OEQ_UVW
                             T xv[In::D1];
 #pragma unroll
-                            for (int i = 0; i < In::D1; ++i) xv[i] = xrow[feat_idx<B1::OFF, B1::MUL, B1::D>(c, i)];
+                            for (int i = 0; i < In::D1; ++i) xv[i] = live ? xrow[feat_idx<B1::OFF, B1::MUL, B1::D>(c, i)] : T(0);
                             for (int v = 0; v < In::V; ++v) {
                                 T yv[In::D2], t[In::D3];
 #pragma unroll
@@ -82,15 +84,20 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_forward(const FwdP
 #pragma unroll
                                 for (int k = 0; k < In::D3; ++k) t[k] = T(0);
                                 In::fwd(xv, yv, t);
-                                const T w = wrow[widx_uvu<In::U, In::V>(In::WOFF, c, v)];
+                                const T w = live ? wrow[widx_uvu<In::U, In::V>(In::WOFF, c, v)] : T(0);
 #pragma unroll
                                 for (int k = 0; k < In::D3; ++k) msg[k] += w * t[k];
                             }
 #else
-                            for (int u = 0; u < In::U; ++u) {
+                            // T[u][k] = sum_{i,j} C x[u,i] y[j] does not depend on the output channel: lane l computes it for
+                            // channel u0 + l once, and the u -> w contraction takes it from there by shuffles
+                            for (int u0 = 0; u0 < In::U; u0 += 32) {
+                                const int uo = u0 + lane;
+                                const int ulen = (In::U - u0) < 32 ? (In::U - u0) : 32;
                                 T xv[In::D1];
 #pragma unroll
-                                for (int i = 0; i < In::D1; ++i) xv[i] = xrow[feat_idx<B1::OFF, B1::MUL, B1::D>(u, i)];
+                                for (int i = 0; i < In::D1; ++i)
+                                    xv[i] = (uo < In::U) ? xrow[feat_idx<B1::OFF, B1::MUL, B1::D>(uo, i)] : T(0);
                                 for (int v = 0; v < In::V; ++v) {
                                     T yv[In::D2], t[In::D3];
 #pragma unroll
@@ -98,9 +105,11 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_forward(const FwdP
 #pragma unroll
                                     for (int k = 0; k < In::D3; ++k) t[k] = T(0);
                                     In::fwd(xv, yv, t);
-                                    const T w = wrow[widx_uvw<In::U, In::V, In::WN_>(In::WOFF, u, v, c)];
+                                    for (int ul = 0; ul < ulen; ++ul) {
+                                        const T w = live ? wrow[widx_uvw<In::U, In::V, In::WN_>(In::WOFF, u0 + ul, v, c)] : T(0);
 #pragma unroll
-                                    for (int k = 0; k < In::D3; ++k) msg[k] += w * t[k];
+                                        for (int k = 0; k < In::D3; ++k) msg[k] += w * __shfl_sync(0xffffffffu, t[k], ul);
+                                    }
                                 }
                             }
 #endif
@@ -108,9 +117,11 @@ extern "C" __global__ void __launch_bounds__(128) oeq_generic_forward(const FwdP
                         }
                     });
                 }
+                if (live) {
 #pragma unroll
-                for (int k = 0; k < B3::D; ++k)
-                    emit_out(&zrow[feat_idx<B3::OFF, B3::MUL, B3::D>(c, k)], acc[k], p.out_mode);
+                    for (int k = 0; k < B3::D; ++k)
+                        emit_out(&zrow[feat_idx<B3::OFF, B3::MUL, B3::D>(c, k)], acc[k], p.out_mode);
+                }
             }
         });
     }
