@@ -1481,7 +1481,7 @@ int oeqb_precompile(const void* desc, size_t desc_len, int64_t key) {
     int done = 0;
     for (int fam = 0; fam < FAM_COUNT; ++fam) {
         if (fam == FAM_UVW_TC) { if (!d.tc) continue; }
-        if (fam >= FAM_UVW_TC_DX && fam <= FAM_UVW_TC_DW) { if (!d.tc_bwd) continue; }
+        else if (fam >= FAM_UVW_TC_DX && fam <= FAM_UVW_TC_DW) { if (!d.tc_bwd) continue; }
         else if (fam != FAM_GENERIC && !d.fast) continue;
         if (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC && d.fast_S4 < 3) continue;
         if (fam == FAM_FAST_FWD_ATOMIC && d.fast_S3 < 2) continue;

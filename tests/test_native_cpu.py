@@ -107,3 +107,40 @@ def test_a_key_reused_for_another_problem_is_refused():
     native.query(a.encode(), key)                       # same problem again: fine
     with pytest.raises(RuntimeError, match="different descriptor"):
         native.query(b.encode(), key)
+
+
+def test_planning_entry_points_check_their_arguments():
+    """The device planner refuses inconsistent ranges before it touches the device, and sizes its workspace from the
+    arguments alone."""
+    import ctypes
+    lib = native.load()
+    small = lib.oeqb_plan_workspace_bytes(1000, 8000, 500, 500, 2)
+    large = lib.oeqb_plan_workspace_bytes(100000, 800000, 50000, 50000, 8)
+    assert 0 < small < large
+    assert lib.oeqb_plan_workspace_bytes(-1, 10, 1, 1, 1) < 0
+    null = ctypes.c_void_p(0)
+    bounds = (ctypes.c_int64 * 3)(0, 500, 1000)
+    # receiver range past the end of the nodes; rank outside the world; bounds that do not ascend
+    assert lib.oeqb_plan_count(1000, 0, null, null, 0, 2000, 0, 500, 2, 0, bounds, null, 0, null, null) == 1  # OEQB_EINVAL
+    assert lib.oeqb_plan_count(1000, 0, null, null, 0, 500, 0, 500, 2, 2, bounds, null, 0, null, null) == 1  # OEQB_EINVAL
+    bad = (ctypes.c_int64 * 3)(0, 800, 500)
+    assert lib.oeqb_plan_count(1000, 0, null, null, 0, 500, 0, 500, 2, 0, bad, null, 0, null, null) == 1  # OEQB_EINVAL
+    assert lib.oeqb_plan_fill(1000, 10, null, null, 0, 500, 0, 500, 2, bounds, 5, 3, 0, null, 0, null, null, null, null, null,
+                              null) == 1  # OEQB_EINVAL
+    assert b"oeqb_plan" in lib.oeqb_last_error()
+
+
+def test_tensor_core_programs_compile_for_other_block_shapes():
+    """The tcgen05 'uvw' programs (forward and the three gradients) specialise and compile without a GPU for the
+    NequIP-like problem, for 7-component blocks and for multiplicities above 32."""
+    feats3 = "32x0e+32x1o+32x2e+32x3o"
+    problems = [P.nequip_like_problem(),
+                P.FullyConnectedTPProblem(feats3, "1x0e+1x1o+1x2e+1x3o", feats3, shared_weights=True, label="uvw-l3",
+                                          irrep_dtype=np.float32, weight_dtype=np.float32),
+                P.FullyConnectedTPProblem("64x0e+64x0o+64x1e+64x1o+64x2e+64x2o", "1x0e+1x1o+1x2e", "32x0e+64x1o+96x2e",
+                                          shared_weights=True, label="uvw-mixed", irrep_dtype=np.float32,
+                                          weight_dtype=np.float32)]
+    for problem in problems:
+        text = build_descriptor(problem)
+        assert native.query(text.encode(), descriptor_hash(text)).fast_path == 2
+        assert native.precompile(text.encode()) >= 5      # general + forward + three gradient programs
