@@ -271,6 +271,9 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
         const int ucol = lane & 3;
         unsigned nstage = 0;   // staged blocks so far (phase of xs_full)
         float gnext[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // mode 2: the next step's cotangent values
+        float wnext[1024 / TC_CT];                                    // this thread's entries of the next path's weight block
+#pragma unroll
+        for (int r = 0; r < 1024 / TC_CT; ++r) wnext[r] = __ldg(p.W + TC_WOFF[0] + tid + TC_CT * r);
         for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             const long long item0 = tile * 128;
             tc_compute_sync();   // previous tile's readers of xs / ys / dys are done
@@ -359,12 +362,15 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                             for (int r = 0; r < 1024 / TC_CT; ++r) {
                                 const int e = tid + TC_CT * r;          // e = u * 32 + w
                                 const int u = e >> 5, w = e & 31;
-                                const float v = __ldg(p.W + woff + e);
+                                const float v = wnext[r];               // requested one path ahead
                                 const float hi = tc_tf32(v);
                                 const int off = TC_WT ? tc_elem(u, w) : tc_elem(w, u);
                                 sh.b[npath & 1u][0][off] = hi;
                                 sh.b[npath & 1u][1][off] = tc_tf32(v - hi);
                             }
+                            const int wq = (q + 1 < TC_NPATH) ? TC_WOFF[q + 1] : TC_WOFF[0];   // the next path's (or next tile's first)
+#pragma unroll
+                            for (int r = 0; r < 1024 / TC_CT; ++r) wnext[r] = __ldg(p.W + wq + tid + TC_CT * r);
                         }
 #pragma unroll
                         for (int uu = 0; uu < 8; ++uu) {
