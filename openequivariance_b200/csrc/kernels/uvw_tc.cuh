@@ -133,7 +133,9 @@ struct __align__(128) TcShared {
     unsigned tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(TcShared) > 116 * 1024 && sizeof(TcShared) <= 232448, "one CTA per SM is assumed (it owns all of TMEM)");
+// One CTA per SM is assumed (it owns all of TMEM): the host asks for more than half of the shared memory even when the
+// buffers need less.
+static_assert(sizeof(TcShared) <= 232448, "the buffers exceed shared memory");
 
 // offset (in floats) of element (row, kcol) in a chunk
 OEQ_DEV int tc_elem(int row, int kcol) { return (row >> 3) * (TC_SBO / 4) + (kcol >> 2) * (TC_LBO / 4) + (row & 7) * 4 + (kcol & 3); }
@@ -495,7 +497,7 @@ OEQ_DEV void tcw_cg(const float* xt, const float* yb, int t0, int t1, float (&ac
         }
     }
 }
-static_assert(sizeof(TcDwShared) > 116 * 1024 && sizeof(TcDwShared) <= 232448, "one CTA per SM is assumed (it owns all of TMEM)");
+static_assert(sizeof(TcDwShared) <= 232448, "the buffers exceed shared memory");   // (one CTA per SM: see TcShared)
 
 extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_dw(const TcDwParams p) {
     extern __shared__ __align__(128) unsigned char tc_smem_raw[];

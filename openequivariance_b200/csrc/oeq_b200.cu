@@ -674,7 +674,7 @@ std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats) {
 size_t tc_dw_smem_bytes(const Desc& d) {
     size_t xs_floats = 0;
     tc_dw_groups(d, &xs_floats);
-    return 4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 64 * (d.dim[1] | 1) + xs_floats) + 512;
+    return std::max<size_t>(4 * (size_t)(2 * 2 * 4096 + 2 * 2 * 1024 + 64 * (d.dim[1] | 1) + xs_floats) + 512, 120 * 1024);
 }
 
 // Tables for the tensor-core weight-gradient kernel: the paths of an output tile in groups of up to four slots.
@@ -1262,7 +1262,8 @@ size_t tc_smem_bytes(const Desc& d, int mode) {
     const size_t dys = mode == 2 ? 512 * (size_t)(d.dim[1] | 1) : 4;   // TC_CT threads
     const size_t ys = mode == 2 ? 4 : 128 * (size_t)(((int)d.dim[1] + 3) & ~3);
     const size_t xs = 128 * (size_t)(32 * maxd1 + (mode == 2 ? 1 : 4));
-    return 4 * (2 * 2 * 4096 + 2 * 2 * 1024 + xs + ys + dys) + 256;
+    // never less than half of an SM's shared memory: a CTA allocates all of the tensor memory, so only one may be resident
+    return std::max<size_t>(4 * (2 * 2 * 4096 + 2 * 2 * 1024 + xs + ys + dys) + 256, 120 * 1024);
 }
 
 // mode 0: z from (x, y, W); mode 1: the gradient of x from (g, y, W), passed in the places of x and z; mode 2: the

@@ -288,3 +288,69 @@ def test_uvw_tensor_core_double_backward_matches_general_kernels(which):
             native.set_option("tc_backward", "7")
         for a, b, what in zip(got, ref, ("dx", "dy", "dW", "dg")):
             assert rel_l2(a, b) <= 5e-6, (B, what)
+
+
+def _random_uvw_problem(seed):
+    """A seeded random shared-weight 'uvw' problem the tensor-core kernels accept: 2-4 input and output blocks with
+    multiplicities from {32, 64, 96, 128} and l <= 3, harmonics up to l = 2 or 3; the selection rules leave some blocks
+    without any path (those results are zeroed by the host) and give the paths of a block different shapes."""
+    from openequivariance_b200.core import problems as P
+    rng = np.random.default_rng(seed)
+
+    def blocks(n):
+        out = []
+        for _ in range(n):
+            l = int(rng.integers(0, 4))
+            out.append(f"{int(rng.choice([32, 64, 96, 128]))}x{l}{'e' if rng.integers(0, 2) else 'o'}")
+        return "+".join(out)
+    lmax = int(rng.integers(2, 4))
+    harmonics = "+".join(f"1x{l}{'e' if l % 2 == 0 else 'o'}" for l in range(lmax + 1))
+    return P.FullyConnectedTPProblem(blocks(int(rng.integers(2, 5))), harmonics, blocks(int(rng.integers(2, 5))),
+                                     shared_weights=True, label=f"uvw-random-{seed}", irrep_dtype=np.float32,
+                                     weight_dtype=np.float32)
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 9, 10, 11])
+def test_uvw_tensor_core_kernels_on_random_problems(seed):
+    """Forward, backward and double backward of random tensor-core-eligible problems: tcgen05 kernels against the general
+    kernels (rounding) and the forward / backward against the oracle."""
+    from openequivariance_b200 import native
+    try:
+        p = _random_uvw_problem(seed)
+    except AssertionError:
+        pytest.skip("the random irreps admit no path")
+    if len(p.instructions) == 0:
+        pytest.skip("the random irreps admit no path")
+    tp = _module(p)
+    if native.query(tp.kernel_string.encode(), tp.hash).fast_path != 2:
+        pytest.skip("not on the tensor-core path")
+    ops = torch.ops.libtorch_tp_jit
+    B = 131
+    x, y, w, g, *_ = uniform_inputs(p, B, seed=seed)
+    x2, y2, w2, *_ = uniform_inputs(p, B, seed=seed + 100)
+    a = [torch.tensor(t, device="cuda") for t in (x, y, w, g, x2, y2, w2)]
+
+    def run():
+        z = ops.jit_tp_forward(tp.kernel, tp.hash, a[0], a[1], a[2], p.irreps_out.dim)
+        first = ops.jit_tp_backward(tp.kernel, tp.hash, *a[:4])
+        second = ops.jit_tp_double_backward(tp.kernel, tp.hash, *a)
+        return [t.cpu().numpy() for t in (z, *first, *second)]
+    got = run()
+    native.set_option("no_tc", "1")
+    try:
+        ref = run()
+    finally:
+        native.set_option("no_tc", "0")
+    names = ("z", "dx", "dy", "dW", "ddx", "ddy", "ddW", "ddg")
+    for u, v, what in zip(got, ref, names):
+        scale = max(float(np.linalg.norm(v)), 1e-30)
+        assert float(np.linalg.norm(u - v)) / scale <= 8e-6 or float(np.abs(v).max()) == 0.0 and float(np.abs(u).max()) == 0.0, what
+    we = tp.reorder_weights_to_e3nn(w)
+    assert rel_l2(got[0], tp_oracle.forward(p, x, y, we)) <= 1e-5
+    want = tp_oracle.backward(p, x, y, we, g)
+    want = (want[0], want[1], tp.reorder_weights_from_e3nn(want[2]))
+    for u, v, what in zip(got[1:4], want, names[1:4]):
+        if float(np.abs(v).max()) == 0.0:
+            assert float(np.abs(u).max()) == 0.0, what
+        else:
+            assert rel_l2(u, v) <= 1e-5, what
