@@ -254,6 +254,13 @@ OEQB_API int oeqb_plan_fill(int64_t n_nodes, int64_t n_edges, const void* rows, 
                             int64_t e0, int64_t e1, int64_t n_halo, void* workspace, int64_t workspace_bytes, void* halo_ids,
                             void* send_ids, void* rows_local, void* cols_local, void* perm_local, void* stream);
 
+/* Self-test of the kernels' bounded waits (every spin on a barrier in the pipelined kernels gives up after ~2 s, raises its
+ * CTA's abort flag and stores a code in a host-mapped status word): launches one small CTA that waits for a barrier nobody
+ * arrives at and checks that it returns by itself, that all threads leave and that the code arrives.  Takes ~2 s.  The
+ * descriptor must be one the channel-parallel kernels serve (fast_path = 1).  Returns OEQB_OK when the mechanism works and
+ * leaves the status word clear. */
+OEQB_API int oeqb_selftest_bounded_wait(const void* desc, size_t desc_len, int64_t key, void* stream);
+
 /* String options: "cache_dir" (cubin cache directory), "log" ("0"/"1"), "validate" ("0"/"1"/"2": index checks), and the
  * tuning aids "force_generic", "single_group", "single_producer", "no_tc", "tc_backward" ("0".."7"), "streams",
  * "streams_forward".  Unknown names are refused with OEQB_EINVAL. */

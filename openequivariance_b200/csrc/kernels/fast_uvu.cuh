@@ -829,6 +829,20 @@ FAST_ENTRY(oeq_fast_double_backward_B_det, fast_backward_body<FAST_DET>)
 #elif FAST_KERNEL == 5
 FAST_ENTRY(oeq_fast_double_backward_B_atomic, fast_backward_body<FAST_ATOMIC>)
 #elif FAST_KERNEL == 6
+// Self-test of the bounded wait that every pipeline stage of this file relies on: a CTA waits on a barrier that nobody
+// arrives at.  The wait has to give up by itself, raise the CTA's abort flag and leave its code in the status word; the
+// threads that did not run out themselves leave through the flag.  *left counts the threads that came back.
+extern "C" __global__ void oeq_selftest_starved_wait(int* status, int* left) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!mbar_wait(&bar, 0u, &abort_flag, status, 99)) atomicAdd(left, 1);
+}
 // Deterministic scatter of the per-edge dX rows: colptr[c] = first position k (in sender-major order) whose sender >= c
 extern "C" __global__ void oeq_fixup_backward_offsets(const IDX* cols, const IDX* perm, long long E, long long N, long long* colptr) {
     const long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x;

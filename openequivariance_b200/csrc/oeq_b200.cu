@@ -1911,6 +1911,38 @@ int oeqb_conv_backward_noalloc(const void* desc, size_t desc_len, int64_t key, i
     return fast_scatter(e, base, cols, transpose_perm, n_nodes, n_edges, colptr, dX, st);
 }
 
+int oeqb_selftest_bounded_wait(const void* desc, size_t desc_len, int64_t key, void* stream) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Entry* e;
+    if (int rc = get_entry(desc, desc_len, key, &e)) return rc;
+    if (!use_fast(e->d)) return fail(OEQB_EUNSUPPORTED, "oeqb_selftest_bounded_wait: the descriptor is not served by the channel-parallel kernels");
+    int* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    Program* prog;
+    if (int rc = get_program(e, FAM_FAST_SCATTER, &prog)) return rc;
+    cudaKernel_t k;
+    if (int rc = get_kernel(prog, "oeq_selftest_starved_wait", 0, &k)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int* left = nullptr;
+    CUDA_TRY(cudaMallocAsync((void**)&left, sizeof(int), st));
+    CUDA_TRY(cudaMemsetAsync(left, 0, sizeof(int), st));
+    void* args[] = {&status, &left};
+    int rc = launch(k, 1, 64, 0, args, st);
+    int came_back = 0;
+    if (!rc) {
+        CUDA_TRY(cudaMemcpyAsync(&came_back, left, sizeof(int), cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+    }
+    cudaFreeAsync(left, st);
+    if (rc) return rc;
+    // the kernel must have returned (it did: the synchronisation came back), every thread must have left, and the status
+    // word must carry the code; reading it clears it
+    const int seen = status_word(nullptr);
+    if (came_back != 64) return fail(OEQB_EKERNEL, "oeqb_selftest_bounded_wait: %d of 64 threads came back", came_back);
+    if (seen != OEQB_EKERNEL) return fail(OEQB_EKERNEL, "oeqb_selftest_bounded_wait: the starved wait did not report through the status word");
+    return OEQB_OK;
+}
+
 int oeqb_check_status(void) {
     std::lock_guard<std::mutex> lock(g_mutex);
     return status_word(nullptr);

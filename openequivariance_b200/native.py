@@ -42,6 +42,7 @@ _PROTOTYPES = {
     "oeqb_conv_backward_noalloc": (c_int, _DESC + [c_int64, c_int64] + [_P] * 11),
     "oeqb_noalloc_status": (c_int, []),
     "oeqb_check_status": (c_int, []),
+    "oeqb_selftest_bounded_wait": (c_int, [c_char_p, c_size_t, c_int64, _P]),
     "oeqb_group_mm": (c_int, [c_int, c_int, c_int64, c_int64, c_int64, c_int64, POINTER(c_int64), _P, _P, _P, _P]),
     "oeqb_slow_path_count": (c_int64, []),
     "oeqb_graph_workspace_bytes": (c_int64, [c_int64, c_int64]),

@@ -307,3 +307,25 @@ def test_aoti_package_from_cpp(tmp_path):
     assert got["shape"].split() == [str(want.shape[0]), str(want.shape[1])]
     assert abs(float(got["sum"]) - float(want.sum())) <= 1e-4 * float(want.abs().sum())
     assert abs(float(got["abs"]) - float(want.abs().sum())) <= 1e-5 * float(want.abs().sum())
+
+
+def test_a_starved_wait_gives_up_and_reports():
+    """Every spin on a barrier in the pipelined kernels is bounded.  The library's self-test launches a CTA whose barrier is
+    never arrived at: the kernel has to come back by itself (~2 s), all of its threads have to leave through the abort
+    flag, and the code has to reach the host through the status word; afterwards the context is usable as before."""
+    import ctypes
+    import openequivariance_b200 as oeq
+    from openequivariance_b200 import native
+    p = MATRIX["mace_medium"]
+    conv = oeq.TensorProductConv(p, deterministic=True)
+    desc = conv.kernel_string.encode()
+    lib = native.load()
+    assert lib.oeqb_check_status() == 0
+    with torch.cuda.device(0):
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        native.check(lib.oeqb_selftest_bounded_wait(desc, len(desc), conv.hash, st), "oeqb_selftest_bounded_wait")
+    assert lib.oeqb_check_status() == 0                      # the self-test consumed the code it provoked
+    tp = oeq.TensorProduct(p)
+    x, y, w, *_ = uniform_inputs(p, 16)
+    out = tp(*(torch.tensor(t, device="cuda") for t in (x, y, w)))
+    assert torch.isfinite(out).all()
