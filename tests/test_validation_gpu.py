@@ -329,3 +329,40 @@ def test_a_starved_wait_gives_up_and_reports():
     x, y, w, *_ = uniform_inputs(p, 16)
     out = tp(*(torch.tensor(t, device="cuda") for t in (x, y, w)))
     assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("start", [np.float32, np.float64])
+def test_module_follows_its_parent_to_another_dtype(start):
+    """``parent.to(dtype)`` re-specialises a TensorProduct / TensorProductConv held as a submodule (the reference's
+    tests/batch_test.py:383-451): outputs come back in the new dtype and agree with the oracle."""
+    import openequivariance_b200 as oeq
+    from helpers import with_dtype
+    from oracle import tp_oracle
+    problem = with_dtype(MATRIX["mace_medium"], start)
+
+    class Parent(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tp = oeq.TensorProduct(problem)
+            self.conv = oeq.TensorProductConv(problem, deterministic=False)
+
+        def forward(self, x, y, w):
+            return self.tp(x, y, w)
+
+    parent = Parent()
+    first = torch.float32 if start == np.float32 else torch.float64
+    other = torch.float64 if start == np.float32 else torch.float32
+    for dtype in (first, other):
+        if dtype != first:
+            parent.to(dtype)
+        npdt = np.float32 if dtype == torch.float32 else np.float64
+        x, y, w, *_ = uniform_inputs(with_dtype(problem, npdt), 10, seed=3)
+        out = parent(*(torch.tensor(t, device="cuda") for t in (x, y, w)))
+        assert out.dtype == dtype
+        want = tp_oracle.forward(problem, x, y, parent.tp.reorder_weights_to_e3nn(w))
+        assert np.linalg.norm(out.cpu().numpy() - want) / np.linalg.norm(want) <= (1e-5 if dtype == torch.float32 else 1e-12)
+        rows = torch.tensor([0, 1, 1, 2], device="cuda")
+        cols = torch.tensor([1, 0, 2, 1], device="cuda")
+        xs, ys, ws = (torch.tensor(t[:4] if i else t[:3], device="cuda") for i, t in enumerate((x, y, w)))
+        z = parent.conv(xs, ys, ws, rows, cols)
+        assert z.dtype == dtype and z.shape == (3, problem.irreps_out.dim)
