@@ -113,6 +113,7 @@ constexpr int TC_A_FLOATS = 128 * 32, TC_B_FLOATS = 32 * 32;
 // padded row of the staged input block: conflict-free for the column reads of the Clebsch-Gordan stage (modes 0, 1) or
 // for one thread per row (mode 2)
 constexpr int TC_XSTRIDE = 32 * TC_MAXD1 + (TC_MODE == 2 ? 1 : 4);
+constexpr int TC_XSTRIDE2 = 32 * TC_XS2_D1 + 4;  // row of the second staging buffer (blocks of up to TC_XS2_D1 components)
 constexpr int TC_DYS = L2_DIM | 1;              // mode 2: row of a thread's partial sums of dy
 constexpr int TC_YSTRIDE = (L2_DIM + 3) & ~3;
 constexpr int TC_CW = 16;                       // compute warps
@@ -124,12 +125,13 @@ struct __align__(128) TcShared {
     float a[2][2][TC_A_FLOATS];       // [buffer][hi, lo]
     float b[2][2][TC_B_FLOATS];
     float xs[128 * TC_XSTRIDE];       // input block a(p) of the 128 items of the tile
+    float xs2[TC_XS2_D1 > 0 ? 128 * TC_XSTRIDE2 : 4];   // second staging buffer: the next block arrives while this one is read
     float ys[TC_MODE == 2 ? 4 : 128 * TC_YSTRIDE];   // harmonics of the 128 items (mode 2 does not read them)
     float dys[TC_MODE == 2 ? TC_CT * TC_DYS : 4];   // mode 2: per-thread partial sums of dy (TC_CW / 4 threads per item)
     unsigned long long a_full[2];     // the operands of a step are in place (every compute thread arrives)
     unsigned long long mma_done[2];   // a buffer may be rewritten
     unsigned long long acc_done[2];   // accumulators of an output block are complete
-    unsigned long long xs_full;       // the staged input block has arrived (bytes of the bulk copies)
+    unsigned long long xs_full[2];    // a staged input block has arrived (bytes of the bulk copies), per staging buffer
     unsigned tmem_base;
     int abort_flag;
 };
@@ -212,7 +214,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
         tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
         tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
         tc_mbar_init(&sh.acc_done[0], 1); tc_mbar_init(&sh.acc_done[1], 1);
-        tc_mbar_init(&sh.xs_full, 1);
+        tc_mbar_init(&sh.xs_full[0], 1); tc_mbar_init(&sh.xs_full[1], 1);
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -271,13 +273,15 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
         // ---- compute warps.  This thread's 8 elements of every A chunk: item brow, channels ucol + 4 * uu, uu < 8
         const int brow = warp * 8 + (lane >> 2);
         const int ucol = lane & 3;
-        unsigned nstage = 0;   // staged blocks so far (phase of xs_full)
+        unsigned nfill[2] = {0u, 0u};   // blocks that have arrived in each staging buffer so far (phases of xs_full)
+        int cur = 0;                    // staging buffer that holds the block of the path at hand
         float gnext[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // mode 2: the next step's cotangent values
         float wnext[1024 / TC_CT];                                    // this thread's entries of the next path's weight block
 #pragma unroll
         for (int r = 0; r < 1024 / TC_CT; ++r) wnext[r] = __ldg(p.W + TC_WOFF[0] + tid + TC_CT * r);
         for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             const long long item0 = tile * 128;
+            int pre_q = -1;      // path whose block has been requested ahead (none across tiles)
             tc_compute_sync();   // previous tile's readers of xs / ys / dys are done
             if (TC_MODE != 2) {
                 for (int r = warp; r < 128; r += TC_CW)          // one warp per row: no index division
@@ -295,16 +299,26 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                 const bool restage = q == 0 || TC_XOFF[q - 1] != xoff;
                 tc_compute_sync();   // readers of the previous path's block are done
                 if (TC_MODE != 2) {
-                    // one bulk copy per row, issued by the first 128 threads; everybody waits for the bytes to arrive.  Rows past
-                    // the end of the batch read row 0: their results are never stored.
-                    if (restage && !dead) {
-                        if (tid == 0) tc_mbar_expect_tx(&sh.xs_full, 128u * 128u * (unsigned)d1);
+                    // One bulk copy per row, issued by the first 128 threads; everybody waits for the bytes to arrive.  Rows past
+                    // the end of the batch read row 0: their results are never stored.  While this block is read, the next
+                    // different one of the tile's schedule is already requested into the other staging buffer when that
+                    // buffer can hold it (its readers left before the barrier above).
+                    auto request = [&](int buf, int qq) {
+                        const int dd = TC_D1[qq];
+                        if (tid == 0) tc_mbar_expect_tx(&sh.xs_full[buf], 128u * 128u * (unsigned)dd);
                         if (tid < 128) {
                             const long long b = item0 + tid;
-                            tc_bulk_row(sh.xs + tid * TC_XSTRIDE, p.x + (b < p.batch ? b : 0) * TC_IN_DIM + xoff, 128u * (unsigned)d1, &sh.xs_full);
+                            float* dst = buf ? sh.xs2 + tid * TC_XSTRIDE2 : sh.xs + tid * TC_XSTRIDE;
+                            tc_bulk_row(dst, p.x + (b < p.batch ? b : 0) * TC_IN_DIM + TC_XOFF[qq], 128u * (unsigned)dd, &sh.xs_full[buf]);
                         }
-                        if (!tc_mbar_wait(&sh.xs_full, nstage & 1u, abortf, p.status, 37)) dead = true;
-                        ++nstage;
+                    };
+                    if (restage && !dead) {
+                        if (pre_q == q) cur ^= 1;
+                        else { cur = 0; request(0, q); }
+                        if (!tc_mbar_wait(&sh.xs_full[cur], nfill[cur] & 1u, abortf, p.status, 37)) dead = true;
+                        ++nfill[cur];
+                        const int qn = TC_NEXTX[q];   // first later path of the schedule that stages another block, or -1
+                        if (!dead && qn >= 0 && TC_D1[qn] <= (cur ? TC_MAXD1 : TC_XS2_D1)) { request(cur ^ 1, qn); pre_q = qn; }
                     }
                 } else {
                     if (restage && !dead) {   // warp w copies rows w, w + 16, ... (odd row stride: 4-byte pieces)
@@ -319,7 +333,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                     }
                     tc_compute_sync();
                 }
-                const float* xrow = sh.xs + brow * TC_XSTRIDE + ucol * d1;
+                const float* xrow = (cur ? sh.xs2 + brow * TC_XSTRIDE2 : sh.xs + brow * TC_XSTRIDE) + ucol * d1;
                 const int ustride = 4 * d1;                 // distance between this thread's consecutive channels
                 const float* yrow = sh.ys + brow * TC_YSTRIDE;
                 for (int k = 0; k < d3; ++k) {

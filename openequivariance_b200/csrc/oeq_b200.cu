@@ -119,6 +119,8 @@ struct Desc {
 
 std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats);
 size_t tc_smem_bytes(const Desc& d, int mode);
+size_t tc_smem_base_bytes(const Desc& d, int mode);
+int tc_xs2_d1(const Desc& d, int mode, size_t base);
 
 bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
     std::istringstream in(std::string(text, len));
@@ -639,6 +641,12 @@ std::string emit_tc(const Desc& d, int mode = 0) {
         if (S.d() > maxd1) maxd1 = S.d();
     }
     s << "constexpr int TC_MAXD1 = " << maxd1 << ", TC_NPATH = " << order.size() << ";\n";
+    s << "constexpr int TC_XS2_D1 = " << tc_xs2_d1(d, mode, tc_smem_base_bytes(d, mode)) << ";\n";
+    std::vector<long long> vnext(order.size(), -1);   // the next path of the schedule that stages another block
+    for (size_t q = 0; q < order.size(); ++q)
+        for (size_t r = q + 1; r < order.size(); ++r)
+            if (vx[r] != vx[q]) { vnext[q] = (long long)r; break; }
+    ilist("TC_NEXTX", vnext);
     ilist("TC_D1", vd1); ilist("TC_D3", vd3); ilist("TC_XOFF", vx); ilist("TC_ZOFF", vz); ilist("TC_WOFF", vw);
     ilist("TC_FIRST", vf); ilist("TC_LAST", vl); ilist("TC_INS", vi);
     emit_tc_terms(s, d, dx, "TC_");
@@ -708,7 +716,7 @@ std::string emit_tc_dw(const Desc& d) {
             if (used) { xsoff += 64LL * (32 * A->d() + 8); maxd1 = std::max(maxd1, A->d()); }
         }
     }
-    s << "constexpr int TC_MAXD1 = " << maxd1 << ", TC_NPATH = 1;\n";
+    s << "constexpr int TC_MAXD1 = " << maxd1 << ", TC_NPATH = 1, TC_XS2_D1 = 0;\n";
     s << "constexpr int TCW_NGRP = " << groups.size() << ";\n";
     s << "constexpr int TCW_XS_FLOATS = " << xs_floats << ";\n";
     ilist("TCW_XSOFF", sxs);
@@ -1256,14 +1264,31 @@ struct TcDwParams {
 };
 // sizeof(TcShared) in kernels/uvw_tc.cuh, rounded up: operand buffers + staged block + harmonics (+ the dy partials);
 // mode as in emit_tc
-size_t tc_smem_bytes(const Desc& d, int mode) {
+// Components of the largest block the second staging buffer of the forward / dx kernels can hold beside everything else
+// (0: no second buffer); `base` is the shared memory the kernel needs without it.
+int tc_xs2_d1(const Desc& d, int mode, size_t base) {
+    if (mode == 2) return 0;
     int maxd1 = 1;
     for (auto& I : d.ins) maxd1 = std::max(maxd1, mode == 1 ? d.L[2][I.o].d() : d.L[0][I.a].d());
-    const size_t dys = mode == 2 ? 512 * (size_t)(d.dim[1] | 1) : 4;   // TC_CT threads
+    for (int dd = maxd1; dd >= 1; dd -= 2)
+        if (base + 4 * (size_t)128 * (32 * dd + 4) <= 232448) return dd;
+    return 0;
+}
+
+size_t tc_smem_base_bytes(const Desc& d, int mode);
+size_t tc_smem_bytes(const Desc& d, int mode) {
+    const size_t base = tc_smem_base_bytes(d, mode);
+    const int d2 = tc_xs2_d1(d, mode, base);
+    // never less than half of an SM's shared memory: a CTA allocates all of the tensor memory, so only one may be resident
+    return std::max<size_t>(base + (d2 > 0 ? 4 * (size_t)128 * (32 * d2 + 4) : 0), 120 * 1024);
+}
+size_t tc_smem_base_bytes(const Desc& d, int mode) {   // without the second staging buffer (for tc_xs2_d1)
+    int maxd1 = 1;
+    for (auto& I : d.ins) maxd1 = std::max(maxd1, mode == 1 ? d.L[2][I.o].d() : d.L[0][I.a].d());
+    const size_t dys = mode == 2 ? 512 * (size_t)(d.dim[1] | 1) : 4;
     const size_t ys = mode == 2 ? 4 : 128 * (size_t)(((int)d.dim[1] + 3) & ~3);
     const size_t xs = 128 * (size_t)(32 * maxd1 + (mode == 2 ? 1 : 4));
-    // never less than half of an SM's shared memory: a CTA allocates all of the tensor memory, so only one may be resident
-    return std::max<size_t>(4 * (2 * 2 * 4096 + 2 * 2 * 1024 + xs + ys + dys) + 256, 120 * 1024);
+    return 4 * (2 * 2 * 4096 + 2 * 2 * 1024 + xs + ys + dys) + 256;
 }
 
 // mode 0: z from (x, y, W); mode 1: the gradient of x from (g, y, W), passed in the places of x and z; mode 2: the
