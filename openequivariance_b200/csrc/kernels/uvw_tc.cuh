@@ -128,7 +128,7 @@ struct __align__(128) TcShared {
     float xs2[TC_XS2_D1 > 0 ? 128 * TC_XSTRIDE2 : 4];   // second staging buffer: the next block arrives while this one is read
     float ys[TC_MODE == 2 ? 4 : 128 * TC_YSTRIDE];   // harmonics of the 128 items (mode 2 does not read them)
     float dys[TC_MODE == 2 ? TC_CT * TC_DYS : 4];   // mode 2: per-thread partial sums of dy (TC_CW / 4 threads per item)
-    unsigned long long a_full[2];     // the operands of a step are in place (every compute thread arrives)
+    unsigned long long a_full[2];     // the operands of a step are in place (every compute warp arrives once)
     unsigned long long mma_done[2];   // a buffer may be rewritten
     unsigned long long acc_done[2];   // accumulators of an output block are complete
     unsigned long long xs_full[2];    // a staged input block has arrived (bytes of the bulk copies), per staging buffer
@@ -211,7 +211,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     volatile int* abortf = &sh.abort_flag;
     if (tid == 0) {
-        tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
+        tc_mbar_init(&sh.a_full[0], TC_CW); tc_mbar_init(&sh.a_full[1], TC_CW);   // one arrival per compute warp
         tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
         tc_mbar_init(&sh.acc_done[0], 1); tc_mbar_init(&sh.acc_done[1], 1);
         tc_mbar_init(&sh.xs_full[0], 1); tc_mbar_init(&sh.xs_full[1], 1);
@@ -371,6 +371,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                     }
                     // the operand buffer was last read by the MMAs of step - 2 (a commit covers every MMA issued before it)
                     if (!dead && step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 31)) dead = true;
+                    dead = __any_sync(0xffffffffu, dead);   // a warp gives up as one: its arrival below is a single one
                     if (!dead) {
                         if (k == 0) {   // weight block of the path: B[n, kk] = W_p[kk, n] (forward: n = w, kk = u) or
                                         // W_p[n, kk] (gradients: n = u, kk = w); its buffer was last read two paths ago
@@ -397,7 +398,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
                         }
                         tc_fence_async_smem();
                         tc_fence_before();
-                        tc_mbar_arrive(&sh.a_full[buf]);
+                        __syncwarp();                                   // every lane's stores and fences precede ...
+                        if (lane == 0) tc_mbar_arrive(&sh.a_full[buf]);   // ... the warp's one arrival
                     }
                     ++step;
                 }
@@ -519,7 +521,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     volatile int* abortf = &sh.abort_flag;
     if (tid == 0) {
-        tc_mbar_init(&sh.a_full[0], TC_CT); tc_mbar_init(&sh.a_full[1], TC_CT);
+        tc_mbar_init(&sh.a_full[0], TC_CW); tc_mbar_init(&sh.a_full[1], TC_CW);   // one arrival per compute warp
         tc_mbar_init(&sh.mma_done[0], 1); tc_mbar_init(&sh.mma_done[1], 1);
         tc_mbar_init(&sh.xs_full, 1);
         sh.abort_flag = 0;
@@ -626,6 +628,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                         gv[bb] = (bi < nlive) ? __ldg(p.g + (item0 + bi) * L3_DIM + zoff + (r8 + 8 * slot) * d3 + k) : 0.f;
                     }
                     if (!dead && step >= 2 && !tc_mbar_wait(&sh.mma_done[buf], ((step >> 1) - 1) & 1u, abortf, p.status, 33)) dead = true;
+                    dead = __any_sync(0xffffffffu, dead);   // a warp gives up as one: its arrival below is a single one
                     if (!dead) {
 #pragma unroll
                         for (int uu = 0; uu < 4; ++uu)
@@ -645,7 +648,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                         }
                         tc_fence_async_smem();
                         tc_fence_before();
-                        tc_mbar_arrive(&sh.a_full[buf]);
+                        __syncwarp();                                   // every lane's stores and fences precede ...
+                        if (lane == 0) tc_mbar_arrive(&sh.a_full[buf]);   // ... the warp's one arrival
                     }
                     ++step;
                 }
