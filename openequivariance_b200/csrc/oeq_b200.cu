@@ -107,6 +107,8 @@ struct Desc {
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
     bool tc_bwd = false;     // ... and the tensor-core backward kernels
     bool tc_zero_z = false, tc_zero_dx = false;   // some output / input block has no path: zero the result first
+    int tc_ngrp = 0;         // groups of the tensor-core weight-gradient kernel (16 per launch)
+    size_t tc_smem[3] = {0, 0, 0}, tc_dw_smem = 0;   // dynamic shared memory of the tensor-core programs
     int fast_S3 = 0;         // stages of the atomic forward kernel (it also holds one output row for the bulk reduce)
     size_t fast_smem3 = 0;
     int fast_S4 = 0;         // stages of the second-order kernels (their stage carries a second coefficient table)
@@ -119,6 +121,7 @@ struct Desc {
 
 std::vector<std::vector<int>> tc_dw_groups(const Desc& d, size_t* xs_floats);
 size_t tc_smem_bytes(const Desc& d, int mode);
+size_t tc_dw_smem_bytes(const Desc& d);
 size_t tc_smem_base_bytes(const Desc& d, int mode);
 int tc_xs2_d1(const Desc& d, int mode, size_t base);
 
@@ -268,8 +271,10 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         ok = ok && npath <= 1024 && !d.ins.empty();
         d.tc = ok;
         d.tc_bwd = ok;
-        d.tc = d.tc && tc_smem_bytes(d, 0) <= 232448;
-        d.tc_bwd = d.tc_bwd && d.tc && tc_smem_bytes(d, 1) <= 232448 && tc_smem_bytes(d, 2) <= 232448;
+        for (int m = 0; m < 3; ++m) d.tc_smem[m] = ok ? tc_smem_bytes(d, m) : 0;
+        d.tc = d.tc && d.tc_smem[0] <= 232448;
+        d.tc_bwd = d.tc_bwd && d.tc && d.tc_smem[1] <= 232448 && d.tc_smem[2] <= 232448;
+        if (d.tc_bwd) { d.tc_ngrp = (int)tc_dw_groups(d, nullptr).size(); d.tc_dw_smem = tc_dw_smem_bytes(d); }
     }
     return true;
 }
@@ -1302,7 +1307,7 @@ int tc_forward(Entry* e, TcParams p, cudaStream_t st, int mode = 0) {
     Program* prog;
     if ((rc = get_program(e, mode == 0 ? FAM_UVW_TC : FAM_UVW_TC_DX + (mode - 1), &prog))) return rc;
     cudaKernel_t k;
-    const size_t smem = tc_smem_bytes(e->d, mode);
+    const size_t smem = e->d.tc_smem[mode];
     if ((rc = get_kernel(prog, names[mode], smem, &k))) return rc;
     long long tiles = (p.batch + 127) / 128, grid = sm_count();
     if (grid > tiles) grid = tiles;
@@ -1337,7 +1342,7 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
     if ((rc = get_program(e, FAM_UVW_TC_DW, &prog))) return rc;
     if ((rc = get_program(e, FAM_GENERIC, &gen))) return rc;
     cudaKernel_t k, kr;
-    const size_t smem = tc_dw_smem_bytes(d);
+    const size_t smem = d.tc_dw_smem;
     if ((rc = get_kernel(prog, "oeq_uvw_tc_backward_dw", smem, &k))) return rc;
     if ((rc = get_kernel(gen, "oeq_generic_dw_reduce", 0, &kr))) return rc;
     long long tiles = (batch + 63) / 64, grid = sm_count();
@@ -1348,7 +1353,7 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
     p.part = part;
     // the accumulators of 16 groups fill the tensor memory: more groups take more launches (each writes its groups' part
     // of every CTA's row)
-    const int ngrp = (int)tc_dw_groups(d, nullptr).size();
+    const int ngrp = d.tc_ngrp;
     for (int g0 = 0; g0 < ngrp && !rc; g0 += 16) {
         p.grp_begin = g0;
         p.grp_end = std::min(ngrp, g0 + 16);
