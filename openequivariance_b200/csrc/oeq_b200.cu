@@ -103,6 +103,8 @@ struct Desc {
     int fast_ng = 1;     // thread groups sharing an edge
     int fast_ch = 1;     // channels carried by one consumer thread
     int fast_bwd_ng = 1; // thread groups of the backward kernels (2 in the fp64 configuration)
+    int fastb_S = 0, fastb_ctas = 0;   // stages / resident CTAs of the first-order backward kernels (differ from the forward's
+    size_t fastb_smem = 0;            // only for compensated summation, whose forward alone needs the wide configuration)
     size_t fast_smem = 0;
     bool tc = false;         // tensor-core 'uvw' forward applicable (shared weights, 32-wide multiplicities, fp32)
     bool tc_bwd = false;     // ... and the tensor-core backward kernels
@@ -227,6 +229,25 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
                 d.fast_U = U; d.fast_S = S; d.fast_ctas = ctas; d.fast_ncy = ncy; d.fast_ng = ng; d.fast_ch = ch;
                 d.fast_bwd_ng = bwd_ng;
                 d.fast_smem = (size_t)S * (stage + 32) + 160;
+                d.fastb_S = S; d.fastb_ctas = ctas; d.fastb_smem = d.fast_smem;
+                if (d.kahan && d.dtype == 1) {
+                    // Only the forward accumulates over edges; the backward kernel of the compensated variant is the plain one
+                    // (one channel per thread, one group) in its own, denser configuration.
+                    const int nthreads_b = U;
+                    const size_t stage_b = ((elt * (size_t)(d.dim[0] + d.wn + ncy + ((d.dim[1] + 3) & ~3) + 8 + (nthreads_b / 32) * nyp) + 40) + 15) & ~(size_t)15;
+                    int ctas_b = 256 / U;
+                    ctas_b = ctas_b < 1 ? 1 : (ctas_b > 4 ? 4 : ctas_b);
+                    while (ctas_b > 1 && ctas_b * (nthreads_b + 64) * 168 > 65536) --ctas_b;
+                    int S_b = 0;
+                    for (; ctas_b >= 1; ctas_b /= 2) {
+                        S_b = (int)((232448 / ctas_b - 1024 - 256) / (stage_b + 32));
+                        if (S_b > 6) S_b = 6;
+                        if (S_b >= 3) break;
+                    }
+                    if (S_b >= 3 && ctas_b >= 1) {
+                        d.fast_bwd_ng = 1; d.fastb_S = S_b; d.fastb_ctas = ctas_b; d.fastb_smem = (size_t)S_b * (stage_b + 32) + 160;
+                    }
+                }
                 const size_t stage4 = stage + elt * (size_t)(ncy + ((d.dim[1] + 3) & ~3));
                 int S4 = wide ? 0 : (int)((232448 / ctas - 1024 - 256) / (stage4 + 32));
                 if (S4 > 6) S4 = 6;
@@ -352,7 +373,7 @@ std::string emit_header(const Desc& d) {
 // Producer warps of a kernel with `stages` stages: two from four stages on (its look-ahead is then a multiple of two).
 int fast_producers(int stages) { return (stages >= 4 && !g_single_producer) ? 2 : 1; }
 
-std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_t smem_bytes, int streams) {
+std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_t smem_bytes, int streams, int ctas) {
     std::ostringstream s;
     if (!d.fast) { s << "#define OEQ_FAST 0\n"; return s.str(); }
     s << "#define OEQ_FAST 1\n";
@@ -365,7 +386,7 @@ std::string emit_fast(const Desc& d, int ch, int ng, bool dbl, int stages, size_
     s << "constexpr int FAST_NP = " << (streams > 1 ? 1 : fast_producers(stages)) << ";\n";
     s << "constexpr size_t FAST_SMEM_BYTES = " << smem_bytes << ";\n";
     s << "constexpr int FU = " << d.fast_U << ", NCY = " << d.fast_ncy << ", FAST_S = " << stages
-      << ", FAST_CTAS = " << (streams > 1 ? 1 : d.fast_ctas) << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
+      << ", FAST_CTAS = " << (streams > 1 ? 1 : ctas) << ", FAST_CH = " << ch << ", FAST_XPC = " << d.dim[0] / d.fast_U
       << ", FAST_GPC = " << d.dim[2] / d.fast_U << ";\n";
     // Folded-coefficient table: slot q of an edge holds sum_t FAST_CYC[q][t] * y[FAST_CYJ[q][t]], one slot per (i, k) pair
     std::ostringstream cyc, cyj;
@@ -779,9 +800,10 @@ std::string family_source(const Desc& d, const std::string& header, int fam, boo
         const bool fwd = fwd3 || (fam >= FAM_FAST_FWD_TP && fam <= FAM_FAST_FWD_ATOMIC);
         const bool dbl = fwd3 || (fam >= FAM_FAST_BWD2_TP && fam <= FAM_FAST_BWD2_ATOMIC);
         const int V = family_streams(d, fam, allow_streams);
-        const int stages = V > 1 ? d.fast_SV : dbl ? d.fast_S4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : d.fast_S);
-        const size_t smem = V > 1 ? d.fast_smemV : dbl ? d.fast_smem4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : d.fast_smem);
-        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : d.fast_bwd_ng, dbl, stages, smem, V);
+        const bool bwd1 = !fwd && !dbl;   // first-order backward: its own stage count and residency
+        const int stages = V > 1 ? d.fast_SV : dbl ? d.fast_S4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_S3 : bwd1 ? d.fastb_S : d.fast_S);
+        const size_t smem = V > 1 ? d.fast_smemV : dbl ? d.fast_smem4 : (fam == FAM_FAST_FWD_ATOMIC ? d.fast_smem3 : bwd1 ? d.fastb_smem : d.fast_smem);
+        src += emit_fast(d, fwd ? d.fast_ch : 1, fwd ? d.fast_ng : d.fast_bwd_ng, dbl, stages, smem, V, bwd1 ? d.fastb_ctas : d.fast_ctas);
         // the second-order variants reuse the backward entry points (kernel ids 3..5)
         src += "#define FAST_KERNEL " + std::to_string(fwd3 ? fam - FAM_FAST_FWD3_TP : dbl ? fam - FAM_FAST_BWD2_TP + 3 : fam - FAM_FAST_FWD_TP) + "\n";
         src += K_COMMON;   // (FAST_KERNEL is defined before the kernel file: it sizes the shared-memory layout)
@@ -1187,15 +1209,16 @@ int fast_launch(Entry* e, int kernel, FastParams p, cudaStream_t st, int* status
         void* args[] = {&p};
         return launch(k, (unsigned)grid, (unsigned)(V * 128 + 128), d.fast_smemV, args, st);
     }
-    const size_t smem = dbl ? d.fast_smem4 : (kernel == 2 ? d.fast_smem3 : d.fast_smem);
+    const bool bwd1 = kernel >= 3 && !dbl;   // first-order backward: its own stage count and residency
+    const size_t smem = dbl ? d.fast_smem4 : (kernel == 2 ? d.fast_smem3 : bwd1 ? d.fastb_smem : d.fast_smem);
     if ((rc = get_program(e, fam, &prog, false))) return rc;
     if ((rc = get_kernel(prog, names[kernel], smem, &k))) return rc;
-    long long grid = (long long)sm_count() * d.fast_ctas;
+    long long grid = (long long)sm_count() * (bwd1 ? d.fastb_ctas : d.fast_ctas);
     const long long work = p.E > 0 ? p.E : 1;
     if (grid > work) grid = work;
     void* args[] = {&p};
     const unsigned consumers = kernel < 3 ? (unsigned)(d.fast_ng * d.fast_U / d.fast_ch) : (unsigned)(d.fast_bwd_ng * d.fast_U);
-    const int producers = fast_producers(dbl ? d.fast_S4 : (kernel == 2 ? d.fast_S3 : d.fast_S));
+    const int producers = fast_producers(dbl ? d.fast_S4 : (kernel == 2 ? d.fast_S3 : bwd1 ? d.fastb_S : d.fast_S));
     return launch(k, (unsigned)grid, consumers + 32 * producers, smem, args, st);
 }
 
