@@ -469,8 +469,9 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) TC_KERNEL_NAME(const
 // the B operand): per step (group of paths, component k, 32 items)
 //   D[(slot, u), w] += A[(slot, u), b] * B[w, b],   A = T (128 x 32), B = component k of the cotangent block (32 x 32),
 // both K-major with the items on K (4 tcgen05.mma of K = 8, three split terms each; the chunk geometry of the forward).
-// The accumulators of every group stay in tensor memory (32 columns per group) over all tiles of the CTA; at the end
-// the CTA stores them as one row of a partials matrix that a second kernel sums in row order (bitwise reproducible).
+// The accumulators of every group live in tensor memory (32 columns per group) for one tile of 64 items; after the tile
+// the CTA stores them as row `tile` of a partials matrix that a second kernel sums in row order (bitwise reproducible,
+// and in fp32 with rounding: the tensor cores' own accumulation truncates, so its sums are kept short).
 // The input blocks of a group's slots are staged in shared memory once per (tile of 64 items, group) by asynchronous row
 // copies and serve all components k and both halves of the tile.
 // Sixteen compute warps and one issuing warp, coupled through mbarriers like the forward.  Compute warp w works on slot
@@ -546,7 +547,6 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
         const unsigned long long db0h = tc_desc(&sh.b[0][0][0], TC_LBO, TC_SBO), db0l = tc_desc(&sh.b[0][1][0], TC_LBO, TC_SBO);
         const unsigned long long db1h = tc_desc(&sh.b[1][0][0], TC_LBO, TC_SBO), db1l = tc_desc(&sh.b[1][1][0], TC_LBO, TC_SBO);
         for (long long tile = blockIdx.x; tile < ntiles && !dead; tile += gridDim.x) {
-            const bool first_tile = tile == blockIdx.x;
             for (int grp = p.grp_begin; grp < p.grp_end && !dead; ++grp) {
                 const int d3 = TCW_D3[grp];
                 for (int kh = 0; kh < 2 * d3 && !dead; ++kh) {   // (component k, half of the tile)
@@ -561,7 +561,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                         for (int ks = 0; ks < 4; ++ks) {
                             const unsigned long long ah = ah0 + 16ull * ks, al = al0 + 16ull * ks;
                             const unsigned long long bh = bh0 + 16ull * ks, bl = bl0 + 16ull * ks;
-                            tc_mma(dcol, ah, bh, (first_tile && kh == 0 && ks == 0) ? 0u : 1u);
+                            tc_mma(dcol, ah, bh, (kh == 0 && ks == 0) ? 0u : 1u);   // every tile starts its sums afresh
                             tc_mma(dcol, al, bh, 1u);
                             tc_mma(dcol, ah, bl, 1u);
                         }
@@ -654,21 +654,25 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) oeq_uvw_tc_backward_
                     ++step;
                 }
             }
-        }
-        // the CTA's sums: row blockIdx.x of the partials matrix.  TMEM lane = (slot, u), column = 32 * group + w.
-        if (!dead && step >= 1 && !tc_mbar_wait(&sh.mma_done[(step - 1) & 1u], ((step - 1) >> 1) & 1u, abortf, p.status, 34)) dead = true;
-        if (!dead && step >= 1) {
-            tc_fence_after();
-            float* prow = p.part + (long long)blockIdx.x * WN;
-            for (int grp = p.grp_begin; grp < p.grp_end; ++grp) {
-                if (slot >= TCW_NS[grp]) continue;   // uniform in the warp
-                unsigned r[8];
-                tc_ld8(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)(grp - p.grp_begin) + (unsigned)(TC_EC * sub), r);
-                float4* dst = reinterpret_cast<float4*>(prow + TCW_WOFF[grp * 4 + slot] + lane * 32 + TC_EC * sub);
-                dst[0] = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
-                dst[1] = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+            // The tile's sums: row `tile` of the partials matrix (TMEM lane = (slot, u), column = 32 * group + w).  The
+            // accumulators are emptied after every tile because the tensor cores add into them with truncation: the error of
+            // a sum grows with its length, and a sum over the whole batch would leave the fp32 bound (measured: 1e-5 at
+            // 50,000 items, 8e-5 at 400,000); the rows are added in fp32 with rounding by the ordered reduce.
+            if (!dead && step >= 1 && !tc_mbar_wait(&sh.mma_done[(step - 1) & 1u], ((step - 1) >> 1) & 1u, abortf, p.status, 34)) dead = true;
+            dead = __any_sync(0xffffffffu, dead);
+            if (!dead && step >= 1) {
+                tc_fence_after();
+                float* prow = p.part + tile * WN;
+                for (int grp = p.grp_begin; grp < p.grp_end; ++grp) {
+                    if (slot >= TCW_NS[grp]) continue;   // uniform in the warp
+                    unsigned r[8];
+                    tc_ld8(tmem + ((unsigned)(slot * 32) << 16) + 32u * (unsigned)(grp - p.grp_begin) + (unsigned)(TC_EC * sub), r);
+                    float4* dst = reinterpret_cast<float4*>(prow + TCW_WOFF[grp * 4 + slot] + lane * 32 + TC_EC * sub);
+                    dst[0] = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
+                    dst[1] = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));
+                }
+                tc_fence_before();
             }
-            tc_fence_before();
         }
     }
     tc_fence_before();

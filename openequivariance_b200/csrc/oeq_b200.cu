@@ -290,6 +290,15 @@ bool parse_desc(const char* text, size_t len, Desc& d, std::string& why) {
         long long npath = 0;   // 32 x 32 weight tiles: the per-path tables live in constant memory
         if (ok) for (auto& I : d.ins) npath += (long long)(d.L[0][I.a].mul / 32) * (d.L[2][I.o].mul / 32);
         ok = ok && npath <= 1024 && !d.ins.empty();
+        // The tensor cores add into their accumulators with truncation: measured ~1e-6 + 5.5e-9 per accumulated product.  The
+        // sums of the forward (per output channel: the channels of every path into its block) and of the gradient of x (per
+        // input channel) are kept below 1,280 products, which stays inside the 1e-5 bound.
+        if (ok) {
+            std::vector<long long> into(d.L[2].size(), 0), from(d.L[0].size(), 0);
+            for (auto& I : d.ins) { into[I.o] += d.L[0][I.a].mul; from[I.a] += d.L[2][I.o].mul; }
+            for (long long v : into) ok = ok && v <= 1280;
+            for (long long v : from) ok = ok && v <= 1280;
+        }
         d.tc = ok;
         d.tc_bwd = ok;
         for (int m = 0; m < 3; ++m) d.tc_smem[m] = ok ? tc_smem_bytes(d, m) : 0;
@@ -1354,8 +1363,8 @@ int keep_pool_memory() {
     return OEQB_OK;
 }
 
-// dW = sum over the batch, on the tensor cores: every CTA writes the sums of its tiles as one row of a partials matrix,
-// oeq_generic_dw_reduce adds the rows in order.
+// dW = sum over the batch, on the tensor cores: the sums of every tile of 64 items are one row of a partials matrix (the
+// tensor cores' accumulation truncates, so it is kept that short), oeq_generic_dw_reduce adds the rows in order.
 int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* dW, long long batch, int accum, cudaStream_t st) {
     int rc;
     const Desc& d = e->d;
@@ -1372,10 +1381,10 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
     if (grid > tiles) grid = tiles;
     if ((rc = keep_pool_memory())) return rc;
     void* part = nullptr;
-    CUDA_TRY(cudaMallocAsync(&part, (size_t)grid * d.wn * sizeof(float), st));
+    CUDA_TRY(cudaMallocAsync(&part, (size_t)tiles * d.wn * sizeof(float), st));   // one row per tile of 64 items
     p.part = part;
     // the accumulators of 16 groups fill the tensor memory: more groups take more launches (each writes its groups' part
-    // of every CTA's row)
+    // of every tile's row)
     const int ngrp = d.tc_ngrp;
     for (int g0 = 0; g0 < ngrp && !rc; g0 += 16) {
         p.grp_begin = g0;
@@ -1384,7 +1393,7 @@ int tc_backward_dw(Entry* e, const void* x, const void* y, const void* g, void* 
         rc = launch(k, (unsigned)grid, 16 * 32 + 32, smem, args, st);   // TC_THREADS
     }
     if (!rc) {
-        void* rargs[] = {&part, &grid, &dW, &accum};
+        void* rargs[] = {&part, &tiles, &dW, &accum};
         rc = launch(kr, (unsigned)((d.wn + 31) / 32), 256, 0, rargs, st);
     }
     cudaFreeAsync(part, st);

@@ -354,3 +354,22 @@ def test_uvw_tensor_core_kernels_on_random_problems(seed):
             assert float(np.abs(u).max()) == 0.0, what
         else:
             assert rel_l2(u, v) <= 1e-5, what
+
+
+def test_uvw_tensor_core_weight_gradient_keeps_its_accuracy_on_long_batches():
+    """The tensor cores add into their accumulators with truncation, so a sum over the whole batch loses accuracy with its
+    length (it reached 1e-5 at 50,000 items and 8e-5 at 400,000 before the accumulators were emptied per tile).  The weight
+    gradient of a 200,000-item batch must stay as accurate as that of a short one: against this library's fp64 kernels."""
+    from openequivariance_b200.core import problems as P
+    p32, p64 = P.nequip_like_problem(), P.nequip_like_problem(np.float64)
+    tp32, tp64 = _module(p32), _module(p64)
+    ops = torch.ops.libtorch_tp_jit
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    B = 200000
+    x, y, g = (torch.randn(B, n, device="cuda", generator=gen) for n in (576, 9, 576))
+    w = torch.randn(p32.weight_numel, device="cuda", generator=gen) / 12.6
+    want = ops.jit_tp_backward(tp64.kernel, tp64.hash, x.double(), y.double(), w.double(), g.double())
+    got = ops.jit_tp_backward(tp32.kernel, tp32.hash, x, y, w, g)
+    for a, b, what in zip(got, want, ("dx", "dy", "dW")):
+        err = float((a.double() - b).norm() / b.norm())
+        assert err <= 4e-6, (what, err)
