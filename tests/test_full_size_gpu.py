@@ -1,7 +1,6 @@
 """The batched tensor-product configurations at their full benchmark sizes (MACE-like uvu, 200,000 items; NequIP-like uvw,
 50,000 items), where the fp64 oracle is too slow to run over the whole batch: the specialised kernels against the general
 kernels over every item, the oracle on a slice of items, and linearity of the product in its first argument."""
-import numpy as np
 import pytest
 import torch
 

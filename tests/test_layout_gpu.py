@@ -1,7 +1,6 @@
 """The ``ir_mul`` layout both ways, as the reference tests it (tests/batch_test.py:309-380): a module built for ``ir_mul``
 directly, and a ``mul_ir`` module wrapped in ``transpose_irreps`` on its inputs and output; forward and gradients agree,
 and both agree with the oracle evaluated on the transposed data."""
-import numpy as np
 import pytest
 import torch
 
